@@ -1,0 +1,114 @@
+// Shared host-side plumbing of the library: status and per-thread error text, the exception
+// barrier every entry point runs behind, device switching, the context object and the hooks that
+// let tests inject failures without touching a GPU.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <exception>
+#include <new>
+#include <string>
+
+#include "../../include/homura_cuda.h"
+
+#define HMC_API extern "C" __attribute__((visibility("default")))
+
+struct hmc_context {
+    int32_t device;
+    cudaStream_t stream;
+    int32_t sm_count;
+};
+
+struct hmc_event {
+    int32_t device;
+    cudaEvent_t event;
+};
+
+namespace hmc {
+
+// ---- per-thread state ----
+struct ThreadState {
+    std::string message;
+    int fail_stream_create = 0;
+    int fail_after_probe = 0;
+    int fail_properties = 0;
+    int fail_data = 0;
+    bool fail_data_oom = false;
+    int live_streams = 0;
+};
+ThreadState &thread_state();
+
+// Records `message` for the calling thread and returns `status`.
+hmc_status fail(hmc_status status, const std::string &message);
+
+// Turns a CUDA error into a status (out of memory is its own status), records "<what>: <text>" and
+// clears the runtime's sticky last-error so that the failure does not resurface in a later,
+// unrelated call of the user's program.
+hmc_status cuda_fail(cudaError_t err, const char *what);
+
+#define HMC_CUDA(call, what)                                      \
+    do {                                                          \
+        cudaError_t hmc_err_ = (call);                            \
+        if (hmc_err_ != cudaSuccess) return ::hmc::cuda_fail(hmc_err_, what); \
+    } while (0)
+
+// Runs `body` (returning hmc_status) so that no C++ exception reaches the caller.
+template <class Body>
+hmc_status guarded(Body &&body) noexcept {
+    try {
+        return body();
+    } catch (const std::bad_alloc &) {
+        try {
+            return fail(HMC_OUT_OF_MEMORY, "out of host memory");
+        } catch (...) {
+            return HMC_OUT_OF_MEMORY;
+        }
+    } catch (const std::exception &e) {
+        try {
+            return fail(HMC_INTERNAL_ERROR, std::string("internal error: ") + e.what());
+        } catch (...) {
+            return HMC_INTERNAL_ERROR;
+        }
+    } catch (...) {
+        return HMC_INTERNAL_ERROR;
+    }
+}
+
+// Makes `device` current for its lifetime and restores whatever was current before.
+class DeviceGuard {
+  public:
+    explicit DeviceGuard(int device);
+    ~DeviceGuard();
+    DeviceGuard(const DeviceGuard &) = delete;
+    DeviceGuard &operator=(const DeviceGuard &) = delete;
+    hmc_status status() const { return status_; }
+
+  private:
+    int previous_ = -1;
+    bool switched_ = false;
+    hmc_status status_ = HMC_OK;
+};
+
+// The injected failure of a data operation, if one is armed for this thread: returns true and sets
+// `status`. Called before anything is queued.
+bool injected_data_failure(hmc_status &status);
+
+// Checks the context pointer, arms the device guard, consumes an injected failure. Expands in an
+// entry point body (which returns hmc_status).
+#define HMC_ENTER(ctx)                                                              \
+    if ((ctx) == nullptr) return ::hmc::fail(HMC_INVALID, "null context");         \
+    {                                                                               \
+        hmc_status hmc_inj_;                                                        \
+        if (::hmc::injected_data_failure(hmc_inj_)) return hmc_inj_;               \
+    }                                                                               \
+    ::hmc::DeviceGuard hmc_guard_((ctx)->device);                                   \
+    if (hmc_guard_.status() != HMC_OK) return hmc_guard_.status()
+
+// After a kernel launch: picks up a launch failure (and clears it).
+hmc_status launch_status(const char *what);
+
+inline int64_t ceil_div(int64_t n, int64_t d) { return n / d + (n % d != 0); }
+
+}  // namespace hmc

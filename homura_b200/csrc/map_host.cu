@@ -1,0 +1,103 @@
+// Host side of the elementwise engine: validation of descriptions and the launch geometry.
+#include "map.cuh"
+
+namespace hmc {
+
+hmc_status check_desc(const hmc_tensor_desc *d, const char *what) {
+    if (d == nullptr) return fail(HMC_INVALID, std::string("null description of ") + what);
+    if (!dtype_valid(d->dtype)) return fail(HMC_INVALID, std::string("unknown dtype code for ") + what);
+    if (d->ndim < 0 || d->ndim > HMC_MAX_DIMS) {
+        return fail(HMC_INVALID, std::string(what) + " has " + std::to_string(d->ndim) + " dimensions, the limit is " +
+                                     std::to_string(HMC_MAX_DIMS));
+    }
+    if (d->offset < 0) return fail(HMC_INVALID, std::string("negative offset of ") + what);
+    for (int k = 0; k < d->ndim; ++k) {
+        if (d->sizes[k] < 0) return fail(HMC_INVALID, std::string("negative size in ") + what);
+        if (d->strides[k] < 0) return fail(HMC_INVALID, std::string("negative stride in ") + what);
+    }
+    return HMC_OK;
+}
+
+hmc_status check_operands(const hmc_tensor_desc *const *descs, int n, int64_t *count) {
+    static const char *names[] = {"the output", "the first input", "the second input", "the third input"};
+    const hmc_tensor_desc *first = nullptr;
+    for (int i = 0; i < n; ++i) {
+        if (descs[i] == nullptr) continue;  // an absent (constant) operand
+        hmc_status s = check_desc(descs[i], names[i < 4 ? i : 3]);
+        if (s != HMC_OK) return s;
+        if (first == nullptr) {
+            first = descs[i];
+            continue;
+        }
+        if (descs[i]->ndim != first->ndim) return fail(HMC_INVALID, "operands differ in their number of dimensions");
+        for (int k = 0; k < first->ndim; ++k) {
+            if (descs[i]->sizes[k] != first->sizes[k]) return fail(HMC_INVALID, "operands differ in their sizes");
+        }
+    }
+    if (first == nullptr) return fail(HMC_INVALID, "no operands");
+    int64_t total = 1;
+    for (int k = 0; k < first->ndim; ++k) {
+        if (first->sizes[k] == 0) {
+            total = 0;
+            break;
+        }
+        if (__builtin_mul_overflow(total, first->sizes[k], &total)) {
+            return fail(HMC_INVALID, "the number of elements overflows 63 bits");
+        }
+    }
+    if (total > 0) {
+        for (int i = 0; i < n; ++i) {
+            if (descs[i] != nullptr && descs[i]->data == nullptr) return fail(HMC_INVALID, "null data pointer");
+        }
+    }
+    *count = total;
+    return HMC_OK;
+}
+
+void build_map_args(MapArgs &a, const hmc_tensor_desc *out, const MapOperand *inputs, int ninputs, int vec, int unr) {
+    a = MapArgs{};
+    const hmc_tensor_desc *descs[kOperands] = {out, nullptr, nullptr, nullptr};
+    for (int k = 0; k < ninputs && k < 3; ++k) {
+        if (inputs[k].constant) {
+            a.constant_mask |= 1u << (k + 1);
+            a.constant[k + 1] = inputs[k].bits;
+        } else {
+            descs[k + 1] = inputs[k].desc;
+        }
+    }
+    int nd = out->ndim;
+    if (nd == 0) {
+        a.ndim = 1;
+        a.sizes[0] = 1;
+        for (int k = 0; k < kOperands; ++k) a.strides[k][0] = 1;
+    } else {
+        a.ndim = nd;
+        for (int d = 0; d < nd; ++d) a.sizes[d] = out->sizes[d];
+        for (int k = 0; k < kOperands; ++k) {
+            if (descs[k] == nullptr) continue;
+            for (int d = 0; d < nd; ++d) a.strides[k][d] = descs[k]->strides[d];
+        }
+    }
+    for (int k = 0; k < kOperands; ++k) {
+        if (descs[k] == nullptr) continue;
+        a.base[k] = static_cast<char *>(descs[k]->data) + descs[k]->offset * element_size(descs[k]->dtype);
+    }
+    a.n0 = a.sizes[a.ndim - 1];
+    a.rows = 1;
+    for (int d = 0; d < a.ndim - 1; ++d) a.rows *= a.sizes[d];
+    if (a.n0 == 0 || a.rows == 0) {
+        a.items = 0;
+        return;
+    }
+    int64_t lanes = ceil_div(a.n0, vec);
+    int log2 = 0;
+    while ((int64_t{1} << log2) < lanes && log2 < 8) ++log2;
+    a.tpr_log2 = log2;
+    int64_t tpr = int64_t{1} << log2;
+    a.segs = ceil_div(a.n0, tpr * vec * unr);
+    int64_t rpb = kThreads / tpr;
+    a.items = ceil_div(a.rows, rpb) * a.segs;
+    a.rows_fit32 = a.rows < (int64_t{1} << 31) ? 1 : 0;
+}
+
+}  // namespace hmc

@@ -1,0 +1,150 @@
+// Device maths of the elementwise functors, in the computation type C of the dtype (float for
+// F16/BF16/F32, double for F64), formula for formula as homura's CPU backend writes them
+// (src/backend/cpu/mod.rs:362-403). The library is compiled with -fmad=false, so a*b+c is two
+// roundings unless fma() is spelled out, which is where the CPU calls mul_add.
+//
+// Transcendentals of the float computation type are evaluated in double and rounded once: the
+// result is the correctly rounded f32 value except within ~1e-9 ulp of a tie, hence within one ulp
+// of any libm whose own error is below one ulp (what homura's CPU backend calls).
+#pragma once
+
+#include "elem.cuh"
+
+namespace hmc {
+
+__device__ __forceinline__ float m_exp(float x) { return static_cast<float>(exp(static_cast<double>(x))); }
+__device__ __forceinline__ double m_exp(double x) { return exp(x); }
+__device__ __forceinline__ float m_log(float x) { return static_cast<float>(log(static_cast<double>(x))); }
+__device__ __forceinline__ double m_log(double x) { return log(x); }
+__device__ __forceinline__ float m_log1p(float x) { return static_cast<float>(log1p(static_cast<double>(x))); }
+__device__ __forceinline__ double m_log1p(double x) { return log1p(x); }
+__device__ __forceinline__ float m_sqrt(float x) { return sqrtf(x); }
+__device__ __forceinline__ double m_sqrt(double x) { return sqrt(x); }
+__device__ __forceinline__ float m_sin(float x) { return static_cast<float>(sin(static_cast<double>(x))); }
+__device__ __forceinline__ double m_sin(double x) { return sin(x); }
+__device__ __forceinline__ float m_cos(float x) { return static_cast<float>(cos(static_cast<double>(x))); }
+__device__ __forceinline__ double m_cos(double x) { return cos(x); }
+__device__ __forceinline__ float m_tanh(float x) { return static_cast<float>(tanh(static_cast<double>(x))); }
+__device__ __forceinline__ double m_tanh(double x) { return tanh(x); }
+__device__ __forceinline__ float m_pow(float x, float y) {
+    return static_cast<float>(pow(static_cast<double>(x), static_cast<double>(y)));
+}
+__device__ __forceinline__ double m_pow(double x, double y) { return pow(x, y); }
+__device__ __forceinline__ float m_abs(float x) { return fabsf(x); }
+__device__ __forceinline__ double m_abs(double x) { return fabs(x); }
+__device__ __forceinline__ float m_fma(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+__device__ __forceinline__ double m_fma(double a, double b, double c) { return __fma_rn(a, b, c); }
+
+// homura's own erf in f64 (src/backend/cpu/num.rs:189-219): a series of positive terms below 1.5,
+// the continued fraction of erfc up to 6, then 1. Used for F64 tensors, where the result is not
+// rounded to a narrower type afterwards and the formula itself decides the last bits.
+__device__ inline double erf_series(double x) {
+    if (x != x) return x;
+    const double ax = fabs(x);
+    double r;
+    if (ax < 1.5) {
+        const double x2 = ax * ax;
+        double term = ax, sum = ax, n = 0.0;
+        while (term > 1e-17 * sum) {
+            n += 1.0;
+            term *= 2.0 * x2 / (2.0 * n + 1.0);
+            sum += term;
+        }
+        r = 1.12837916709551257390 * exp(-x2) * sum;
+    } else if (ax < 6.0) {
+        double f = ax;
+        for (int k = 80; k >= 1; --k) f = ax + (static_cast<double>(k) * 0.5) / f;
+        r = 1.0 - exp(-ax * ax) / (1.7724538509055159 * f);
+    } else {
+        r = 1.0;
+    }
+    return copysign(r, x);
+}
+// For the float computation type the f64 value is rounded to f32 afterwards, so any f64 erf that is
+// good to a few ulp gives the same f32 bits; the runtime's is far cheaper than 80 divisions.
+__device__ __forceinline__ float m_erf(float x) { return static_cast<float>(erf(static_cast<double>(x))); }
+__device__ __forceinline__ double m_erf(double x) { return erf_series(x); }
+
+template <int OP, class C>
+__device__ __forceinline__ C unary_math(C x) {
+    const C one = 1, zero = 0, half = static_cast<C>(0.5);
+    if constexpr (OP == HMC_UNARY_NEG) return -x;
+    else if constexpr (OP == HMC_UNARY_ABS) return m_abs(x);
+    else if constexpr (OP == HMC_UNARY_RELU) return (x != x || x > zero) ? x : zero;
+    else if constexpr (OP == HMC_UNARY_SIGN) return x > zero ? one : (x < zero ? -one : zero);
+    else if constexpr (OP == HMC_UNARY_EXP) return m_exp(x);
+    else if constexpr (OP == HMC_UNARY_LOG) return m_log(x);
+    else if constexpr (OP == HMC_UNARY_SQRT) return m_sqrt(x);
+    else if constexpr (OP == HMC_UNARY_RSQRT) return one / m_sqrt(x);
+    else if constexpr (OP == HMC_UNARY_RECIPROCAL) return one / x;
+    else if constexpr (OP == HMC_UNARY_SIN) return m_sin(x);
+    else if constexpr (OP == HMC_UNARY_COS) return m_cos(x);
+    else if constexpr (OP == HMC_UNARY_ERF) return m_erf(x);
+    else if constexpr (OP == HMC_UNARY_TANH) return m_tanh(x);
+    else if constexpr (OP == HMC_UNARY_SIGMOID) return one / (one + m_exp(-x));
+    else if constexpr (OP == HMC_UNARY_LOG_SIGMOID) {
+        const C mn = (x != x || x < zero) ? x : zero;
+        return mn - m_log1p(m_exp(-m_abs(x)));
+    } else if constexpr (OP == HMC_UNARY_SILU) return x / (one + m_exp(-x));
+    else if constexpr (OP == HMC_UNARY_GELU) {
+        const C k = static_cast<C>(0.70710678118654752440);
+        return half * x * (one + m_erf(x * k));
+    } else {
+        static_assert(OP == HMC_UNARY_GELU_TANH, "unknown unary op");
+        // sqrt(2/pi) evaluated in f64, then converted, as the CPU does.
+        const C k = static_cast<C>(0.79788456080286535588);
+        const C c = static_cast<C>(0.044715);
+        return half * x * (one + m_tanh(k * (x + c * x * x * x)));
+    }
+}
+
+template <int OP, class C>
+__device__ __forceinline__ C binary_math(C x, C y) {
+    if constexpr (OP == HMC_BINARY_ADD) return x + y;
+    else if constexpr (OP == HMC_BINARY_SUB) return x - y;
+    else if constexpr (OP == HMC_BINARY_MUL) return x * y;
+    else if constexpr (OP == HMC_BINARY_DIV) return x / y;
+    else if constexpr (OP == HMC_BINARY_POW) return m_pow(x, y);
+    else if constexpr (OP == HMC_BINARY_MAXIMUM) return (x != x || x > y) ? x : y;
+    else {
+        static_assert(OP == HMC_BINARY_MINIMUM, "unknown binary op");
+        return (x != x || x < y) ? x : y;
+    }
+}
+
+// Wrapping integer arithmetic (src/backend/cpu/num.rs:109-187).
+template <class T> __device__ __forceinline__ T wadd(T a, T b) {
+    using U = std::make_unsigned_t<T>;
+    return static_cast<T>(static_cast<U>(static_cast<U>(a) + static_cast<U>(b)));
+}
+template <class T> __device__ __forceinline__ T wsub(T a, T b) {
+    using U = std::make_unsigned_t<T>;
+    return static_cast<T>(static_cast<U>(static_cast<U>(a) - static_cast<U>(b)));
+}
+template <class T> __device__ __forceinline__ T wmul(T a, T b) {
+    using U = std::make_unsigned_t<T>;
+    return static_cast<T>(static_cast<U>(static_cast<uint64_t>(static_cast<U>(a)) * static_cast<uint64_t>(static_cast<U>(b))));
+}
+template <class T> __device__ __forceinline__ T wneg(T a) {
+    using U = std::make_unsigned_t<T>;
+    return static_cast<T>(static_cast<U>(U{0} - static_cast<U>(a)));
+}
+template <class T> __device__ __forceinline__ T int_pow(T base, T exp) {
+    int64_t e = static_cast<int64_t>(exp);
+    if (e < 0) {
+        int64_t b = static_cast<int64_t>(base);
+        if (b == 1) return T{1};
+        if (b == -1) return (e % 2 == 0) ? T{1} : base;
+        return T{0};
+    }
+    T result = 1, b = base;
+    uint64_t ue = static_cast<uint64_t>(e);
+    while (ue > 0) {
+        if (ue & 1) result = wmul(result, b);
+        b = wmul(b, b);
+        ue >>= 1;
+    }
+    return result;
+}
+
+}  // namespace hmc

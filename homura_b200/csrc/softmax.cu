@@ -1,0 +1,302 @@
+// softmax / log_softmax along rows, in f64 like homura's CPU kernel (src/backend/cpu/misc.rs:13-51):
+// row maximum (a NaN never wins the comparison), sum of exp(x - max), then exp(x - max) / sum or
+// x - max - log(sum), rounded to the dtype once. Stands in for hmr_softmax of csrc/reduce.hip.
+//
+// A row is handled by a group of G = 32 or 256 lanes. Its elements are cut into 16-byte vectors;
+// vector v belongs to lane v mod G. When a lane owns at most 8 vectors the row lives in registers:
+// the source is read from HBM once, exp runs once per element, and the output is written once,
+// which is the algorithmic minimum of traffic. Longer rows are streamed in three passes (the
+// second and third find the row in cache when it fits). Rows whose elements are not adjacent, or
+// not 16-byte aligned, take scalar accesses with the same lane assignment and give the same bits.
+// exp is skipped for x - max = -inf (a masked logit), whose result is exactly +0.
+#include <math_constants.h>
+
+#include "map.cuh"
+#include "reduce.cuh"
+
+namespace hmc {
+namespace {
+
+struct SoftmaxArgs {
+    hmc_tensor_desc out_rows;
+    hmc_tensor_desc src_rows;
+    int64_t nrows, n, so, si;
+};
+
+struct SoftmaxPlan {
+    int kind;   // 0: row in registers, 1: streaming
+    int group;  // 32 or 256
+    int cache;  // vectors a lane keeps (kind 0)
+};
+
+SoftmaxPlan softmax_plan(int dtype, int64_t n) {
+    const int64_t vec = 16 / element_size(dtype);
+    const int64_t nvec = ceil_div(n, vec);
+    SoftmaxPlan p{};
+    p.group = nvec <= 64 ? 32 : 256;
+    const int64_t per = ceil_div(nvec, p.group);
+    p.kind = per <= 8 ? 0 : 1;
+    p.cache = 0;
+    if (p.kind == 0) {
+        p.cache = 1;
+        while (p.cache < per) p.cache *= 2;
+    }
+    return p;
+}
+
+template <int G>
+__device__ __forceinline__ double group_max(double v, double *scratch) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        double o = __shfl_xor_sync(0xFFFFFFFFu, v, d);
+        v = o > v ? o : v;
+    }
+    if constexpr (G == 256) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        __syncthreads();
+        if (lane == 0) scratch[warp] = v;
+        __syncthreads();
+        v = scratch[0];
+        for (int w = 1; w < 8; ++w) v = scratch[w] > v ? scratch[w] : v;
+    }
+    return v;
+}
+
+template <int G>
+__device__ __forceinline__ double group_sum(double v, double *scratch) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
+    if constexpr (G == 256) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        __syncthreads();
+        if (lane == 0) scratch[warp] = v;
+        __syncthreads();
+        v = scratch[0];
+        for (int w = 1; w < 8; ++w) v += scratch[w];
+    }
+    return v;
+}
+
+__device__ __forceinline__ double exp_shifted(double d) {
+    // d = x - max <= 0, or NaN. exp(-inf) is +0 without evaluating anything.
+    return d == -CUDART_INF ? 0.0 : exp(d);
+}
+
+template <class T, int G, int CV, bool LOG>
+__global__ void __launch_bounds__(kRThreads) softmax_kernel(const __grid_constant__ SoftmaxArgs a) {
+    constexpr int VEC = 16 / sizeof(T);
+    constexpr int P = kRThreads / G;
+    constexpr int NV = CV > 0 ? CV : 1;
+    __shared__ double scratch[8];
+    const int lane = threadIdx.x % G;
+    const int slot = threadIdx.x / G;
+    const int64_t tiles = (a.nrows + P - 1) / P;
+    const T *src = static_cast<const T *>(a.src_rows.data);
+    T *dst = static_cast<T *>(a.out_rows.data);
+    const int64_t nvec = (a.n + VEC - 1) / VEC;
+    const double ninf = -CUDART_INF;
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int64_t r = tile * P + slot;
+        const bool valid = r < a.nrows;
+        const int64_t rr = valid ? r : 0;
+        const T *ps = src + a.src_rows.offset + decompose(a.src_rows, rr, a.src_rows.ndim);
+        T *po = dst + a.out_rows.offset + decompose(a.out_rows, rr, a.out_rows.ndim);
+        const bool fast_in = a.si == 1 && (reinterpret_cast<uintptr_t>(ps) & 15) == 0;
+        const bool fast_out = a.so == 1 && (reinterpret_cast<uintptr_t>(po) & 15) == 0;
+        auto load_vec = [&](int64_t v, RVec<T, VEC> &x) {
+            const int64_t i0 = v * VEC;
+            if (fast_in && i0 + VEC <= a.n) {
+                x = *reinterpret_cast<const RVec<T, VEC> *>(ps + i0);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) x.v[e] = i0 + e < a.n ? ps[(i0 + e) * a.si] : T{};
+            }
+        };
+        auto store_vec = [&](int64_t v, const RVec<T, VEC> &y) {
+            const int64_t i0 = v * VEC;
+            if (fast_out && i0 + VEC <= a.n) {
+                *reinterpret_cast<RVec<T, VEC> *>(po + i0) = y;
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e)
+                    if (i0 + e < a.n) po[(i0 + e) * a.so] = y.v[e];
+            }
+        };
+        if constexpr (CV > 0) {
+            double x[NV][VEC];
+            double mx = ninf;
+            {
+                RVec<T, VEC> raw[NV];
+#pragma unroll
+                for (int c = 0; c < NV; ++c) {
+                    const int64_t v = lane + static_cast<int64_t>(c) * G;
+                    if (valid && v < nvec) load_vec(v, raw[c]);
+                }
+#pragma unroll
+                for (int c = 0; c < NV; ++c) {
+                    const int64_t v = lane + static_cast<int64_t>(c) * G;
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) {
+                        const bool in = valid && v < nvec && v * VEC + e < a.n;
+                        x[c][e] = in ? to_f64(raw[c].v[e]) : ninf;
+                        if (in && x[c][e] > mx) mx = x[c][e];
+                    }
+                }
+            }
+            mx = group_max<G>(mx, scratch);
+            double sum = 0.0;
+#pragma unroll
+            for (int c = 0; c < NV; ++c) {
+                const int64_t v = lane + static_cast<int64_t>(c) * G;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    const bool in = valid && v < nvec && v * VEC + e < a.n;
+                    if (in) {
+                        const double d = x[c][e] - mx;
+                        if constexpr (LOG) {
+                            sum += exp_shifted(d);
+                            x[c][e] = d;
+                        } else {
+                            x[c][e] = exp_shifted(d);
+                            sum += x[c][e];
+                        }
+                    }
+                }
+            }
+            sum = group_sum<G>(sum, scratch);
+            const double log_sum = LOG ? log(sum) : 0.0;
+#pragma unroll
+            for (int c = 0; c < NV; ++c) {
+                const int64_t v = lane + static_cast<int64_t>(c) * G;
+                if (valid && v < nvec) {
+                    RVec<T, VEC> y;
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) y.v[e] = from_f64<T>(LOG ? x[c][e] - log_sum : x[c][e] / sum);
+                    store_vec(v, y);
+                }
+            }
+        } else {
+            double mx = ninf;
+            for (int64_t v = lane; valid && v < nvec; v += G) {
+                RVec<T, VEC> raw;
+                load_vec(v, raw);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    if (v * VEC + e < a.n) {
+                        const double xv = to_f64(raw.v[e]);
+                        if (xv > mx) mx = xv;
+                    }
+                }
+            }
+            mx = group_max<G>(mx, scratch);
+            double sum = 0.0;
+            for (int64_t v = lane; valid && v < nvec; v += G) {
+                RVec<T, VEC> raw;
+                load_vec(v, raw);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    if (v * VEC + e < a.n) sum += exp_shifted(to_f64(raw.v[e]) - mx);
+                }
+            }
+            sum = group_sum<G>(sum, scratch);
+            const double log_sum = LOG ? log(sum) : 0.0;
+            for (int64_t v = lane; valid && v < nvec; v += G) {
+                RVec<T, VEC> raw, y;
+                load_vec(v, raw);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    const double d = to_f64(raw.v[e]) - mx;
+                    y.v[e] = from_f64<T>(LOG ? d - log_sum : exp_shifted(d) / sum);
+                }
+                store_vec(v, y);
+            }
+        }
+    }
+}
+
+template <class T, int G, int CV>
+hmc_status launch_softmax_cv(hmc_context_t ctx, const SoftmaxArgs &a, bool log) {
+    constexpr int P = kRThreads / G;
+    const int64_t tiles = (a.nrows + P - 1) / P;
+    const unsigned grid = clamp_grid(tiles, static_cast<int64_t>(ctx->sm_count) * 32);
+    if (log) softmax_kernel<T, G, CV, true><<<grid, kRThreads, 0, ctx->stream>>>(a);
+    else softmax_kernel<T, G, CV, false><<<grid, kRThreads, 0, ctx->stream>>>(a);
+    return launch_status("softmax kernel launch");
+}
+
+template <class T, int G>
+hmc_status launch_softmax_g(hmc_context_t ctx, const SoftmaxArgs &a, const SoftmaxPlan &p, bool log) {
+    switch (p.kind == 0 ? p.cache : 0) {
+        case 1: return launch_softmax_cv<T, G, 1>(ctx, a, log);
+        case 2: return launch_softmax_cv<T, G, 2>(ctx, a, log);
+        case 4: return launch_softmax_cv<T, G, 4>(ctx, a, log);
+        case 8: return launch_softmax_cv<T, G, 8>(ctx, a, log);
+        default: return launch_softmax_cv<T, G, 0>(ctx, a, log);
+    }
+}
+
+hmc_status check_lines(const hmc_tensor_desc *out_rows, const hmc_tensor_desc *src_rows, int64_t n, int64_t so,
+                       int64_t si, int64_t *nrows) {
+    const hmc_tensor_desc *d[2] = {out_rows, src_rows};
+    hmc_status s = check_operands(d, src_rows != nullptr && out_rows != nullptr ? 2 : 0, nrows);
+    if (s != HMC_OK) return s;
+    if (n < 0 || so < 0 || si < 0) return fail(HMC_INVALID, "negative row length or stride");
+    return HMC_OK;
+}
+
+}  // namespace
+}  // namespace hmc
+
+using namespace hmc;
+
+HMC_API hmc_status hmc_softmax_workspace(const hmc_tensor_desc *src_rows, int64_t n, int64_t src_stride,
+                                         int64_t *bytes) {
+    return guarded([&]() -> hmc_status {
+        if (bytes == nullptr) return fail(HMC_INVALID, "null output");
+        hmc_status s = check_desc(src_rows, "the rows");
+        if (s != HMC_OK) return s;
+        if (n < 0 || src_stride < 0) return fail(HMC_INVALID, "negative row length or stride");
+        *bytes = 0;  // both plans work in registers and caches
+        return HMC_OK;
+    });
+}
+
+HMC_API hmc_status hmc_test_softmax_plan(const hmc_tensor_desc *src_rows, int64_t n, int64_t src_stride,
+                                         int32_t *kind, int32_t *group, int32_t *cache) {
+    return guarded([&]() -> hmc_status {
+        if (kind == nullptr || group == nullptr || cache == nullptr) return fail(HMC_INVALID, "null output");
+        hmc_status s = check_desc(src_rows, "the rows");
+        if (s != HMC_OK) return s;
+        if (!dtype_is_float(src_rows->dtype)) return fail(HMC_INVALID, "softmax needs a floating point tensor");
+        SoftmaxPlan p = softmax_plan(src_rows->dtype, n);
+        *kind = p.kind;
+        *group = p.group;
+        *cache = p.cache;
+        return HMC_OK;
+    });
+}
+
+HMC_API hmc_status hmc_softmax(hmc_context_t ctx, const hmc_tensor_desc *out_rows, const hmc_tensor_desc *src_rows,
+                               int64_t n, int64_t out_stride, int64_t src_stride, int32_t log, void *workspace,
+                               int64_t workspace_bytes) {
+    return guarded([&]() -> hmc_status {
+        HMC_ENTER(ctx);
+        if (out_rows == nullptr || src_rows == nullptr) return fail(HMC_INVALID, "null description");
+        int64_t nrows = 0;
+        hmc_status s = check_lines(out_rows, src_rows, n, out_stride, src_stride, &nrows);
+        if (s != HMC_OK) return s;
+        if (!dtype_is_float(src_rows->dtype) || out_rows->dtype != src_rows->dtype) {
+            return fail(HMC_INVALID, "softmax takes a floating point tensor and writes its dtype");
+        }
+        (void)workspace;
+        (void)workspace_bytes;
+        if (nrows == 0 || n == 0) return HMC_OK;
+        SoftmaxArgs a{*out_rows, *src_rows, nrows, n, out_stride, src_stride};
+        const SoftmaxPlan p = softmax_plan(src_rows->dtype, n);
+        return dispatch_float(src_rows->dtype, [&](auto t) -> hmc_status {
+            using T = decltype(t);
+            if (p.group == 32) return launch_softmax_g<T, 32>(ctx, a, p, log != 0);
+            return launch_softmax_g<T, 256>(ctx, a, p, log != 0);
+        });
+    });
+}

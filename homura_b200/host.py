@@ -1,0 +1,548 @@
+"""Host-side glue above the C ABI: what homura's ``src/backend/rocm/{copy,elementwise,reduce}.rs`` do for
+its ROCm layer, restated for ``libhomura_cuda.so``.
+
+* :class:`TensorData`: a strided view (shape, element strides, element offset, dtype) of a storage, homura's
+  ``TensorData`` / ``Layout`` (``src/tensor/mod.rs:83-336``), with the view constructors its tests use.
+* :func:`merge_dims`, :func:`descs`: drop size-1 dimensions and merge neighbours that are contiguous in
+  every operand (``src/backend/rocm/copy.rs:34-115``), giving the ``hmc_tensor_desc`` the kernels take.
+* :func:`describe`, :func:`lines`: the kept/reduced split of a reduction and the rows of a softmax
+  (``src/backend/rocm/reduce.rs:42-75, 216-256``).
+* :class:`CudaBackend`: ``copy, fill, unary, binary, binary_constant, binary_scalar, fused, where_,
+  where_constant, reduce, var, arg_reduce, softmax`` with the argument meaning of homura's
+  ``backend::*`` functions (``src/backend/mod.rs:60-358``): outputs are allocated by the caller,
+  workspaces are taken from the allocator before the call, failures raise :class:`BackendError` carrying
+  the library's message (the Rust side panics or returns ``Error::OutOfMemory``).
+
+The Rust host of a real integration keeps all of this in Rust; there is no Rust toolchain where this was
+written, so the same logic is exercised from Python through ctypes. Only the CUDA path exists here: there is
+no CPU fallback, and a missing or unloadable library is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import ffi
+from .ffi import hmc_tensor_desc
+
+BOOL, U8, I8, I16, I32, I64, F16, BF16, F32, F64 = range(10)
+DTYPE_NAMES = ["bool", "u8", "i8", "i16", "i32", "i64", "f16", "bf16", "f32", "f64"]
+ALL_DTYPES = list(range(10))
+FLOATS = [F16, BF16, F32, F64]
+INTS = [U8, I8, I16, I32, I64]
+# numpy type that holds the raw element (bool as a byte, f16/bf16 as their bit patterns)
+STORAGE = [np.uint8, np.uint8, np.int8, np.int16, np.int32, np.int64, np.uint16, np.uint16, np.float32, np.float64]
+SIZE = [1, 1, 1, 2, 4, 8, 2, 2, 4, 8]
+MAX_DIMS = ffi.HMC_MAX_DIMS
+
+
+def is_float(dt: int) -> bool:
+    return dt >= F16
+
+
+def is_int(dt: int) -> bool:
+    return U8 <= dt <= I64
+
+
+class BackendError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+def contiguous_strides(shape: Sequence[int]) -> list[int]:
+    st, acc = [], 1
+    for n in reversed(shape):
+        st.append(acc)
+        acc *= max(n, 1)
+    return st[::-1]
+
+
+@dataclass
+class Storage:
+    """Device memory (``ptr`` on ``device``) or host memory (``array``)."""
+    nbytes: int
+    ptr: int = 0
+    device: Optional[int] = None
+    array: Optional[np.ndarray] = None
+    owner: object = None  # the allocator block that frees the memory
+
+    @property
+    def address(self) -> int:
+        return self.ptr if self.array is None else self.array.ctypes.data
+
+
+@dataclass
+class TensorData:
+    storage: Storage
+    dtype: int
+    shape: tuple
+    strides: tuple
+    offset: int = 0
+
+    @property
+    def numel(self) -> int:
+        return math.prod(self.shape)
+
+    def is_contiguous(self) -> bool:
+        expect = 1
+        for n, s in zip(reversed(self.shape), reversed(self.strides)):
+            if n != 1 and s != expect:
+                return False
+            expect *= n
+        return True
+
+    def _view(self, shape, strides, offset=None) -> "TensorData":
+        return TensorData(self.storage, self.dtype, tuple(shape), tuple(strides), self.offset if offset is None else offset)
+
+    # view constructors (no data movement)
+    def reshape(self, *shape) -> "TensorData":
+        shape = tuple(shape[0]) if len(shape) == 1 and isinstance(shape[0], (tuple, list)) else tuple(shape)
+        assert self.is_contiguous() and math.prod(shape) == self.numel, "reshape of a non-contiguous view"
+        return self._view(shape, contiguous_strides(shape))
+
+    def transpose(self, a: int, b: int) -> "TensorData":
+        sh, st = list(self.shape), list(self.strides)
+        sh[a], sh[b] = sh[b], sh[a]
+        st[a], st[b] = st[b], st[a]
+        return self._view(sh, st)
+
+    def t(self) -> "TensorData":
+        return self.transpose(0, 1)
+
+    def permute(self, *dims) -> "TensorData":
+        dims = tuple(dims[0]) if len(dims) == 1 and isinstance(dims[0], (tuple, list)) else dims
+        return self._view([self.shape[d] for d in dims], [self.strides[d] for d in dims])
+
+    def narrow(self, dim: int, start: int, length: int) -> "TensorData":
+        sh = list(self.shape)
+        sh[dim] = length
+        return self._view(sh, self.strides, self.offset + start * self.strides[dim])
+
+    def select(self, dim: int, index: int) -> "TensorData":
+        sh, st = list(self.shape), list(self.strides)
+        off = self.offset + index * st[dim]
+        del sh[dim], st[dim]
+        return self._view(sh, st, off)
+
+    def expand(self, *shape) -> "TensorData":
+        shape = tuple(shape[0]) if len(shape) == 1 and isinstance(shape[0], (tuple, list)) else tuple(shape)
+        pad = len(shape) - len(self.shape)
+        sh = (1,) * pad + tuple(self.shape)
+        st = (0,) * pad + tuple(self.strides)
+        out = []
+        for n, have, s in zip(shape, sh, st):
+            if have == n:
+                out.append(s)
+            else:
+                assert have == 1, f"cannot expand {self.shape} to {shape}"
+                out.append(0)
+        return self._view(shape, out)
+
+    def unsqueeze(self, dim: int) -> "TensorData":
+        sh, st = list(self.shape), list(self.strides)
+        sh.insert(dim, 1)
+        st.insert(dim, 0)
+        return self._view(sh, st)
+
+
+def merge_dims(shape: Sequence[int], strides: Sequence[Sequence[int]]):
+    """``[(size, [stride per operand])]`` outermost first, or None for an empty shape.
+    src/backend/rocm/copy.rs:34-57 (the CPU twin is Plan::new, src/backend/cpu/iter.rs:27-55)."""
+    if 0 in shape:
+        return None
+    dims: list[tuple[int, list[int]]] = []
+    for i, size in enumerate(shape):
+        if size == 1:
+            continue
+        st = [s[i] for s in strides]
+        if dims:
+            outer_size, outer_st = dims[-1]
+            if all(st[k] * size == outer_st[k] and st[k] * size < 2**63 for k in range(len(st))):
+                dims[-1] = (outer_size * size, st)
+                continue
+        dims.append((size, st))
+    return dims
+
+
+def descs_with_dims(kernel: str, operands: Sequence[TensorData], offsets: Sequence[int], dims) -> list[hmc_tensor_desc]:
+    """src/backend/rocm/copy.rs:86-115."""
+    if len(dims) > MAX_DIMS:
+        raise BackendError(ffi.HMC_INVALID, f"{kernel} on CUDA supports at most {MAX_DIMS} dimensions that can't be "
+                                            f"merged, got {len(dims)}")
+    out = []
+    for k, t in enumerate(operands):
+        d = hmc_tensor_desc()
+        d.data = t.storage.address
+        d.offset = offsets[k]
+        d.dtype = t.dtype
+        d.ndim = len(dims)
+        for j, (size, st) in enumerate(dims):
+            d.sizes[j] = size
+            d.strides[j] = st[k]
+        out.append(d)
+    return out
+
+
+def descs(kernel: str, operands: Sequence[TensorData]) -> Optional[list[hmc_tensor_desc]]:
+    """Descriptions of same-shaped operands, None when they have no elements. copy.rs:59-84."""
+    shape = operands[0].shape
+    for t in operands[1:]:
+        assert tuple(t.shape) == tuple(shape), "kernel operands must have the same shape"
+    dims = merge_dims(shape, [t.strides for t in operands])
+    if dims is None:
+        return None
+    return descs_with_dims(kernel, operands, [t.offset for t in operands], dims)
+
+
+@dataclass
+class Reduction:
+    dims: list
+    kept: hmc_tensor_desc
+    red: hmc_tensor_desc
+
+
+def describe(kernel: str, src: TensorData, mask: Sequence[bool]) -> Optional[Reduction]:
+    """src/backend/rocm/reduce.rs:42-75."""
+    strides = src.strides if src.numel > 0 else (0,) * len(src.strides)
+    kept_shape, kept_strides, red_shape, red_strides = [], [], [], []
+    for size, stride, reduced in zip(src.shape, strides, mask):
+        if reduced:
+            red_shape.append(size)
+            red_strides.append(stride)
+        else:
+            kept_shape.append(size)
+            kept_strides.append(stride)
+    out_strides = contiguous_strides(kept_shape)
+    dims = merge_dims(kept_shape, [out_strides, kept_strides])
+    if dims is None:
+        return None
+    red_dims = merge_dims(red_shape, [red_strides])
+    if red_dims is None:
+        red_dims = [(0, [0])]  # nothing to fold
+    src_dims = [(n, [st[1]]) for n, st in dims]
+    (kept,) = descs_with_dims(kernel, [src], [src.offset], src_dims)
+    (red,) = descs_with_dims(kernel, [src], [0], red_dims)
+    return Reduction(dims, kept, red)
+
+
+def output_desc(kernel: str, r: Reduction, out: TensorData) -> hmc_tensor_desc:
+    assert out.is_contiguous(), f"internal error: {kernel} into a strided tensor"
+    dims = [(n, [st[0]]) for n, st in r.dims]
+    (d,) = descs_with_dims(kernel, [out], [out.offset], dims)
+    return d
+
+
+def lines(kernel: str, out: TensorData, src: TensorData, dim: int, out_strides: Sequence[int]):
+    """Rows along `dim`: (descs of the other dims for out and src, n, out stride, src stride).
+    src/backend/rocm/reduce.rs:216-256."""
+    assert tuple(out.shape) == tuple(src.shape), "kernel operands must have the same shape"
+    if src.numel == 0:
+        return None
+    shape = src.shape
+    others = lambda v: [s for d, s in enumerate(v) if d != dim]
+    if len(shape) == 0:
+        n, so, si = 1, 0, 0
+    else:
+        n, so, si = shape[dim], out_strides[dim], src.strides[dim]
+    dims = merge_dims(others(shape), [others(out_strides), others(src.strides)])
+    if dims is None:
+        return None
+    d = descs_with_dims(kernel, [out, src], [out.offset, src.offset], dims)
+    return d, n, so, si
+
+
+def scalar_bits(value, dtype: int) -> int:
+    """The element of `dtype` holding `value` as the low bytes of a u64 (src/backend/rocm/copy.rs:256-270):
+    floats are rounded as Sealed::from_f64 rounds them (half types through f32), integers wrap."""
+    if dtype == BOOL:
+        return int(bool(value))
+    if is_int(dtype):
+        v = int(value)  # trunc toward zero for floats
+        return v & ((1 << (8 * SIZE[dtype])) - 1)
+    if dtype == F64:
+        return int(np.array([value], dtype=np.float64).view(np.uint64)[0])
+    f = np.array([value], dtype=np.float64).astype(np.float32)
+    if dtype == F32:
+        return int(f.view(np.uint32)[0])
+    return int(f32_to_half_bits(f, dtype)[0])
+
+
+def f32_to_half_bits(f: np.ndarray, dtype: int) -> np.ndarray:
+    """`half`'s f32 -> f16 / bf16 (round to nearest even; a NaN keeps its top payload bits, made quiet)."""
+    x = f.astype(np.float32).view(np.uint32)
+    if dtype == BF16:
+        nan = (x & 0x7FFFFFFF) > 0x7F800000
+        r = ((x.astype(np.uint64) + 0x7FFF + ((x >> 16) & 1)) >> 16).astype(np.uint16)
+        return np.where(nan, ((x >> 16) | 0x40).astype(np.uint16), r)
+    with np.errstate(over="ignore", invalid="ignore"):
+        h = f.astype(np.float16).view(np.uint16)
+    nan = (x & 0x7FFFFFFF) > 0x7F800000
+    q = (((x >> 16) & 0x8000) | 0x7E00 | ((x >> 13) & 0x3FF)).astype(np.uint16)
+    return np.where(nan, q, h)
+
+
+def half_bits_to_f32(b: np.ndarray, dtype: int) -> np.ndarray:
+    b = b.astype(np.uint16)
+    if dtype == BF16:
+        return (b.astype(np.uint32) << 16).view(np.float32)
+    return b.view(np.float16).astype(np.float32)
+
+
+class CudaBackend:
+    """One device: its context (stream), a caching allocator over hmc_malloc/hmc_free, and homura's backend
+    functions on :class:`TensorData` whose storage lives on that device."""
+
+    name = "cuda"
+
+    def __init__(self, device: int = 0, lib=None, allocator=None):
+        from . import load
+        self.lib = lib or load()
+        self.device = device
+        ctx = ctypes.c_void_p()
+        self._check(self.lib.hmc_context_create(device, ctypes.byref(ctx)))
+        self.ctx = ctx
+        if allocator is None:
+            from .caching import CachingAllocator, CudaMemory
+            allocator = CachingAllocator(CudaMemory(self.lib, device, self))
+        self.allocator = allocator
+
+    # ---- plumbing ----
+    def _check(self, status: int) -> None:
+        if status != ffi.HMC_OK:
+            raise BackendError(status, self.lib.hmc_last_error().decode())
+
+    def close(self) -> None:
+        if self.ctx is not None:
+            self.synchronize()
+            self.allocator.destroy()
+            self._check(self.lib.hmc_context_destroy(self.ctx))
+            self.ctx = None
+
+    def synchronize(self) -> None:
+        self._check(self.lib.hmc_context_synchronize(self.ctx))
+
+    def storage(self, nbytes: int) -> Storage:
+        block = self.allocator.allocate(nbytes)
+        return Storage(nbytes, ptr=block.ptr, device=self.device, owner=block)
+
+    def empty(self, shape, dtype: int) -> TensorData:
+        shape = tuple(shape)
+        return TensorData(self.storage(math.prod(shape) * SIZE[dtype]), dtype, shape, tuple(contiguous_strides(shape)))
+
+    def workspace(self, nbytes: int) -> Optional[Storage]:
+        return self.storage(nbytes) if nbytes > 0 else None
+
+    def upload(self, array: np.ndarray, dtype: int, shape=None) -> TensorData:
+        """A contiguous device tensor with the raw elements of `array` (storage dtype of `dtype`)."""
+        array = np.ascontiguousarray(array, dtype=STORAGE[dtype])
+        shape = tuple(array.shape if shape is None else shape)
+        t = self.empty(shape, dtype)
+        if array.nbytes:
+            self._check(self.lib.hmc_copy_from_host(self.ctx, t.storage.ptr, array.ctypes.data, array.nbytes))
+        return t
+
+    def download_storage(self, t: TensorData) -> np.ndarray:
+        """The whole storage behind `t` as a flat array of its storage dtype."""
+        n = t.storage.nbytes // SIZE[t.dtype]
+        out = np.empty(n, dtype=STORAGE[t.dtype])
+        if out.nbytes:
+            self._check(self.lib.hmc_copy_to_host(self.ctx, out.ctypes.data, t.storage.ptr, out.nbytes))
+        return out
+
+    def download(self, t: TensorData) -> np.ndarray:
+        """The elements of `t` in row-major order (raw storage dtype), whatever its layout."""
+        flat = self.download_storage(t)
+        if t.numel == 0:
+            return np.empty(t.shape, dtype=STORAGE[t.dtype])
+        es = SIZE[t.dtype]
+        view = np.lib.stride_tricks.as_strided(flat[t.offset:], shape=t.shape, strides=[s * es for s in t.strides],
+                                               writeable=False)
+        return np.ascontiguousarray(view).reshape(t.shape)
+
+    # ---- homura's backend functions ----
+    def copy(self, dst: TensorData, src: TensorData) -> None:
+        src = src.expand(dst.shape)
+        d = descs("copy", [dst, src])
+        if d is None:
+            return
+        self._check(self.lib.hmc_copy(self.ctx, d[0], d[1]))
+
+    def fill(self, dst: TensorData, value) -> None:
+        d = descs("fill", [dst])
+        if d is None:
+            return
+        self._check(self.lib.hmc_fill(self.ctx, d[0], scalar_bits(value, dst.dtype)))
+
+    def unary(self, op: int, out: TensorData, src: TensorData) -> None:
+        d = descs("unary", [out, src])
+        if d is None:
+            return
+        self._check(self.lib.hmc_unary(self.ctx, op, d[0], d[1]))
+
+    def binary(self, op: int, out: TensorData, a: TensorData, b: TensorData) -> None:
+        d = descs("binary", [out, a, b])
+        if d is None:
+            return
+        self._check(self.lib.hmc_binary(self.ctx, op, d[0], d[1], d[2]))
+
+    def binary_promoted(self, op: int, out: TensorData, a: TensorData, b: TensorData) -> None:
+        d = descs("binary_promoted", [out, a, b])
+        if d is None:
+            return
+        self._check(self.lib.hmc_binary_promoted(self.ctx, op, d[0], d[1], d[2]))
+
+    def binary_constant(self, op: int, out: TensorData, a: TensorData, value, constant_first: bool) -> None:
+        bits = scalar_bits(value, a.dtype)
+        d = descs("binary_constant", [out, a])
+        if d is None:
+            return
+        self._check(self.lib.hmc_binary_constant(self.ctx, op, d[0], d[1], bits, int(constant_first)))
+
+    def binary_scalar(self, op: int, out: TensorData, a: TensorData, s: float, scalar_first: bool) -> None:
+        assert op in (ffi.HMC_BINARY_MUL, ffi.HMC_BINARY_DIV), "this op rounds its scalar to the dtype"
+        d = descs("binary_scalar", [out, a])
+        if d is None:
+            return
+        self._check(self.lib.hmc_binary_scalar(self.ctx, op, d[0], d[1], float(s), int(scalar_first)))
+
+    def fused(self, op: int, value: float, out: TensorData, a: TensorData, b: TensorData,
+              c: Optional[TensorData] = None) -> None:
+        """`op` is an HMC_FUSED_* code, `value` homura's Fused payload (alpha, weight or value); the
+        coefficient is computed here as the CPU computes it (src/backend/rocm/elementwise.rs:163-187)."""
+        coefficient, small = fused_coefficient(op, value, out.dtype)
+        ops = [out, a, b] + ([c] if c is not None else [])
+        d = descs("fused", ops)
+        if d is None:
+            return
+        self._check(self.lib.hmc_fused(self.ctx, op, d[0], d[1], d[2], d[3] if c is not None else None,
+                                       coefficient, int(small)))
+
+    def where_(self, out: TensorData, cond: TensorData, x: TensorData, y: TensorData) -> None:
+        d = descs("where_", [out, cond, x, y])
+        if d is None:
+            return
+        self._check(self.lib.hmc_where(self.ctx, d[0], d[1], d[2], d[3]))
+
+    def where_constant(self, out: TensorData, cond: TensorData, x, y) -> None:
+        """x / y: a TensorData, or a Python scalar for a constant branch."""
+        xt, yt = isinstance(x, TensorData), isinstance(y, TensorData)
+        if xt and yt:
+            return self.where_(out, cond, x, y)
+        ops = [out, cond] + ([x] if xt else []) + ([y] if yt else [])
+        d = descs("where_constant", ops)
+        if d is None:
+            return
+        xb = 0 if xt else scalar_bits(x, out.dtype)
+        yb = 0 if yt else scalar_bits(y, out.dtype)
+        xd = d[2] if xt else None
+        yd = d[2] if (yt and not xt) else (d[3] if yt else None)
+        self._check(self.lib.hmc_where_constant(self.ctx, d[0], d[1], xd, xb, yd, yb))
+
+    def _plan_workspace(self, r: Reduction, var: bool) -> Optional[Storage]:
+        nbytes = ctypes.c_int64()
+        self._check(self.lib.hmc_reduce_workspace(r.kept, r.red, int(var), ctypes.byref(nbytes)))
+        return self.workspace(nbytes.value)
+
+    def reduce(self, op: int, out: TensorData, src: TensorData, mask: Sequence[bool]) -> None:
+        r = describe("reduce", src, mask)
+        if r is None:
+            return
+        o = output_desc("reduce", r, out)
+        ws = self._plan_workspace(r, False)
+        self._check(self.lib.hmc_reduce(self.ctx, op, o, r.kept, r.red, ws.ptr if ws else None, ws.nbytes if ws else 0))
+
+    def var(self, out: TensorData, src: TensorData, mask: Sequence[bool], correction: float, take_sqrt: bool) -> None:
+        r = describe("var", src, mask)
+        if r is None:
+            return
+        o = output_desc("var", r, out)
+        ws = self._plan_workspace(r, True)
+        self._check(self.lib.hmc_var(self.ctx, o, r.kept, r.red, float(correction), int(take_sqrt),
+                                     ws.ptr if ws else None, ws.nbytes if ws else 0))
+
+    def arg_reduce(self, values: Optional[TensorData], indices: TensorData, src: TensorData, dim: int,
+                   is_max: bool) -> None:
+        nd = len(src.shape)
+        mask = [d == dim for d in range(nd)]
+        if nd > 0:
+            assert src.shape[dim] > 0, "cannot compute the arg reduction of an empty dimension"
+        r = describe("arg_reduce", src, mask)
+        if r is None:
+            return
+        i = output_desc("arg_reduce", r, indices)
+        v = output_desc("arg_reduce", r, values) if values is not None else None
+        ws = self._plan_workspace(r, False)
+        self._check(self.lib.hmc_arg_reduce(self.ctx, v, i, r.kept, r.red, int(is_max), ws.ptr if ws else None,
+                                            ws.nbytes if ws else 0))
+
+    def softmax(self, out: TensorData, src: TensorData, dim: int, log: bool) -> None:
+        ln = lines("softmax", out, src, dim, out.strides)
+        if ln is None:
+            return
+        (o, s), n, so, si = ln
+        nbytes = ctypes.c_int64()
+        self._check(self.lib.hmc_softmax_workspace(s, n, si, ctypes.byref(nbytes)))
+        ws = self.workspace(nbytes.value)
+        self._check(self.lib.hmc_softmax(self.ctx, o, s, n, so, si, int(log), ws.ptr if ws else None,
+                                         ws.nbytes if ws else 0))
+
+    def adamw_step(self, param: TensorData, grad: TensorData, exp_avg: TensorData, exp_avg_sq: TensorData, *,
+                   lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: float) -> None:
+        """The fused AdamW update (hmc_adamw_step) with the scalars homura's optimizer derives
+        (src/optim/adam.rs:139-170)."""
+        d = descs("adamw_step", [param, grad, exp_avg, exp_avg_sq])
+        if d is None:
+            return
+        sc = adamw_scalars(param.dtype, lr, beta1, beta2, eps, weight_decay, step)
+        self._check(self.lib.hmc_adamw_step(self.ctx, d[0], d[1], d[2], d[3], ctypes.byref(sc)))
+
+
+def _round_to_compute(v: float, dtype: int) -> float:
+    return float(v) if dtype == F64 else float(np.float32(v))
+
+
+def _round_to_dtype(v: float, dtype: int) -> float:
+    """`v` rounded to `dtype` (Sealed::from_f64) and widened back."""
+    if dtype == F64:
+        return float(v)
+    f = np.array([v], dtype=np.float64).astype(np.float32)
+    if dtype == F32:
+        return float(f[0])
+    return float(half_bits_to_f32(f32_to_half_bits(f, dtype), dtype)[0])
+
+
+def fused_coefficient(op: int, value: float, dtype: int):
+    """(coefficient exact in the computation type, small) as cpu::fused derives them
+    (src/backend/cpu/mod.rs:541-566)."""
+    if op == ffi.HMC_FUSED_SCALED_ADD:
+        return _round_to_dtype(value, dtype), False
+    if op == ffi.HMC_FUSED_LERP:
+        w = _round_to_compute(value, dtype)
+        small = abs(w) < 0.5
+        if small:
+            return w, True
+        one = np.float64(1.0) if dtype == F64 else np.float32(1.0)
+        wc = np.float64(w) if dtype == F64 else np.float32(w)
+        return float(wc - one), False
+    return _round_to_compute(value, dtype), False
+
+
+def adamw_scalars(dtype: int, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
+                  step: float) -> ffi.hmc_adamw_scalars:
+    sc = ffi.hmc_adamw_scalars()
+    sc.has_decay = int(weight_decay != 0.0)
+    sc.decay = _round_to_compute(1.0 - lr * weight_decay, dtype)
+    coeff, small = fused_coefficient(ffi.HMC_FUSED_LERP, 1.0 - beta1, dtype)
+    sc.lerp_coeff, sc.lerp_small = coeff, int(small)
+    sc.beta2 = _round_to_compute(beta2, dtype)
+    sc.one_minus_beta2 = _round_to_compute(1.0 - beta2, dtype)
+    bias_correction2 = 1.0 - beta2 ** step
+    sc.bias2_sqrt = _round_to_compute(bias_correction2 ** 0.5, dtype)
+    sc.eps = _round_to_dtype(eps, dtype)
+    sc.neg_step_size = _round_to_compute(-(lr / (1.0 - beta1 ** step)), dtype)
+    return sc

@@ -1,0 +1,329 @@
+/*
+ * homura_cuda.h: the C ABI of homura's CUDA backend for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a `cuda` feature of homura binds, next to its `rocm` one: the Rust side
+ * (the files of src/backend/cuda and the generated ffi.rs) sees exactly these symbols. Each entry point names the
+ * declaration of homura's ROCm boundary (csrc/homura_rocm.h) it stands in for.
+ *
+ * Rules every entry point keeps:
+ *  - plain C: only <stddef.h> and <stdint.h>; pointers, sizes and int32 codes;
+ *  - the return value is an hmc_status; after a failure hmc_last_error() gives the calling
+ *    thread's message until that thread calls the library again;
+ *  - no C++ exception leaves the library;
+ *  - an entry that works on a device makes it the thread's current CUDA device for the call only;
+ *  - a failed entry has queued nothing, and the CUDA runtime's own "last error" is cleared;
+ *  - kernels are queued on the context's stream and the entry returns without waiting.
+ */
+#ifndef HOMURA_CUDA_H
+#define HOMURA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status (csrc/homura_rocm.h:26-40) ---- */
+#define HMC_OK 0
+#define HMC_OUT_OF_MEMORY 1  /* device or pinned host memory exhausted */
+#define HMC_INVALID 2        /* bad argument, unsupported op/dtype pair, unsupported GPU */
+#define HMC_CUDA_ERROR 3     /* the CUDA runtime (or NCCL) reported an error */
+#define HMC_INTERNAL_ERROR 4 /* a fault inside this library, e.g. a caught C++ exception */
+
+typedef int32_t hmc_status;
+
+/* csrc/homura_rocm.h:40 */
+const char *hmc_last_error(void);
+
+/* ---- devices (csrc/homura_rocm.h:42-64) ---- */
+#define HMC_NAME_LEN 256
+#define HMC_ARCH_LEN 64
+
+typedef struct hmc_device_properties {
+    char name[HMC_NAME_LEN]; /* e.g. "NVIDIA B200" */
+    char arch[HMC_ARCH_LEN]; /* e.g. "sm_100" */
+    int32_t multiprocessor_count;
+    int32_t warp_size;
+    uint64_t total_memory;
+} hmc_device_properties;
+
+/* Visible CUDA devices; 0 with HMC_OK when there is no driver or no device.
+ * csrc/homura_rocm.h:59 */
+hmc_status hmc_device_count(int32_t *count);
+/* csrc/homura_rocm.h:61 */
+hmc_status hmc_device_properties_get(int32_t device, hmc_device_properties *out);
+/* cudaMemGetInfo. csrc/homura_rocm.h:64 */
+hmc_status hmc_mem_get_info(int32_t device, uint64_t *free_bytes, uint64_t *total_bytes);
+
+/* ---- context: one device, one non-blocking stream (csrc/homura_rocm.h:66-79) ---- */
+typedef struct hmc_context *hmc_context_t;
+
+/* Refuses a GPU whose architecture the library holds no code for (HMC_INVALID), creates the
+ * stream, and runs a probe kernel whose answer is checked. Nothing stays allocated on failure. */
+hmc_status hmc_context_create(int32_t device, hmc_context_t *out);
+hmc_status hmc_context_destroy(hmc_context_t ctx);
+hmc_status hmc_context_synchronize(hmc_context_t ctx);
+
+/* ---- memory for the caller's caching allocator (csrc/homura_rocm.h:81-100, 144-146) ---- */
+hmc_status hmc_malloc(int32_t device, uint64_t nbytes, void **out);
+hmc_status hmc_free(int32_t device, void *ptr);
+/* cudaMemsetAsync on the context's stream. */
+hmc_status hmc_memset(hmc_context_t ctx, void *ptr, uint8_t value, uint64_t nbytes);
+/* Stream-ordered copies between host memory and the device that have completed on return. */
+hmc_status hmc_copy_to_host(hmc_context_t ctx, void *dst, const void *src, uint64_t nbytes);
+hmc_status hmc_copy_from_host(hmc_context_t ctx, void *dst, const void *src, uint64_t nbytes);
+/* Async device-to-device copy of non-overlapping ranges. */
+hmc_status hmc_copy_device(hmc_context_t ctx, void *dst, const void *src, uint64_t nbytes);
+
+/* ---- dtypes, numbered as homura's DType (csrc/homura_rocm.h:102-113) ----
+ * Bool is a byte 0/1; F16 and BF16 are their 16-bit patterns. */
+#define HMC_BOOL 0
+#define HMC_U8 1
+#define HMC_I8 2
+#define HMC_I16 3
+#define HMC_I32 4
+#define HMC_I64 5
+#define HMC_F16 6
+#define HMC_BF16 7
+#define HMC_F32 8
+#define HMC_F64 9
+
+#define HMC_MAX_DIMS 25
+
+/* A strided view of device memory (csrc/homura_rocm.h:118-130). Element (i_0..i_{ndim-1}) lives at
+ * element index offset + sum_k i_k * strides[k] of the `dtype` array at `data`. Offsets and
+ * strides count elements, not bytes. ndim 0 is one element. The caller has already dropped
+ * size-1 dimensions and merged neighbours (src/backend/rocm/copy.rs:34-57). */
+typedef struct hmc_tensor_desc {
+    void *data;
+    int64_t offset;
+    int32_t dtype;
+    int32_t ndim;
+    int64_t sizes[HMC_MAX_DIMS];
+    int64_t strides[HMC_MAX_DIMS];
+} hmc_tensor_desc;
+
+/* dst[i] = cast(src[i]) with homura's Element::to_element rules (src/dtype.rs:144-273); equal
+ * dtypes copy bytes. Same ndim and sizes; src strides may be 0. csrc/homura_rocm.h:138 */
+hmc_status hmc_copy(hmc_context_t ctx, const hmc_tensor_desc *dst, const hmc_tensor_desc *src);
+/* Every element of dst becomes the low bytes of `bits` (little endian). csrc/homura_rocm.h:142 */
+hmc_status hmc_fill(hmc_context_t ctx, const hmc_tensor_desc *dst, uint64_t bits);
+
+/* ---- elementwise (csrc/homura_rocm.h:148-255) ----
+ * Results are those of homura's CPU backend (src/backend/cpu/mod.rs): float maths in f32 for
+ * F16/BF16/F32 and in f64 for F64 with a single rounding to the dtype; integer arithmetic wraps.
+ * Operands share ndim and sizes; inputs may have zero strides; the output's elements are distinct
+ * and an input either is the output view itself or does not touch it. */
+#define HMC_UNARY_NEG 0
+#define HMC_UNARY_ABS 1
+#define HMC_UNARY_SIGN 2
+#define HMC_UNARY_RELU 3
+#define HMC_UNARY_EXP 4
+#define HMC_UNARY_LOG 5
+#define HMC_UNARY_SQRT 6
+#define HMC_UNARY_RSQRT 7
+#define HMC_UNARY_RECIPROCAL 8
+#define HMC_UNARY_SIN 9
+#define HMC_UNARY_COS 10
+#define HMC_UNARY_ERF 11
+#define HMC_UNARY_TANH 12
+#define HMC_UNARY_SIGMOID 13
+#define HMC_UNARY_LOG_SIGMOID 14
+#define HMC_UNARY_SILU 15
+#define HMC_UNARY_GELU 16
+#define HMC_UNARY_GELU_TANH 17
+#define HMC_UNARY_LOGICAL_NOT 18
+#define HMC_UNARY_COUNT 19
+
+#define HMC_BINARY_ADD 0
+#define HMC_BINARY_SUB 1
+#define HMC_BINARY_MUL 2
+#define HMC_BINARY_DIV 3
+#define HMC_BINARY_POW 4
+#define HMC_BINARY_MAXIMUM 5
+#define HMC_BINARY_MINIMUM 6
+#define HMC_BINARY_GREATER 7
+#define HMC_BINARY_GREATER_EQUAL 8
+#define HMC_BINARY_LESS 9
+#define HMC_BINARY_LESS_EQUAL 10
+#define HMC_BINARY_EQUAL 11
+#define HMC_BINARY_NOT_EQUAL 12
+#define HMC_BINARY_LOGICAL_AND 13
+#define HMC_BINARY_LOGICAL_OR 14
+#define HMC_BINARY_COUNT 15
+
+#define HMC_FUSED_SCALED_ADD 0
+#define HMC_FUSED_LERP 1
+#define HMC_FUSED_ADDCMUL 2
+#define HMC_FUSED_ADDCDIV 3
+
+/* out = op(src); LogicalNot writes Bool, everything else src's dtype. csrc/homura_rocm.h:202 */
+hmc_status hmc_unary(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
+                     const hmc_tensor_desc *src);
+/* out = op(a, b), a and b of one dtype; comparisons and logical ops write Bool.
+ * csrc/homura_rocm.h:206 */
+hmc_status hmc_binary(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
+                      const hmc_tensor_desc *a, const hmc_tensor_desc *b);
+/* hmc_binary with one operand replaced by the element of a's dtype held in the low bytes of
+ * `bits`; constant_first puts it on the left. csrc/homura_rocm.h:212 */
+hmc_status hmc_binary_constant(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
+                               const hmc_tensor_desc *a, uint64_t bits, int32_t constant_first);
+/* MUL or DIV of a float tensor with a scalar kept in the computation type (f32 for F16, BF16,
+ * F32): a*s, a/s, or s/a with scalar_first. csrc/homura_rocm.h:217 */
+hmc_status hmc_binary_scalar(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
+                             const hmc_tensor_desc *a, double s, int32_t scalar_first);
+/* The optimizers' single-rounding steps on float operands of one dtype; c is NULL for SCALED_ADD
+ * and LERP. `coefficient` is exact in the computation type.
+ *   SCALED_ADD fma(b, k, a) | LERP fma(k, b - a, small ? a : b)
+ *   ADDCMUL fma(k * b, c, a) | ADDCDIV a + k * b / c (no fma)
+ * csrc/homura_rocm.h:227 */
+hmc_status hmc_fused(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
+                     const hmc_tensor_desc *a, const hmc_tensor_desc *b,
+                     const hmc_tensor_desc *c, double coefficient, int32_t small);
+/* out = cond ? x : y with a Bool cond. csrc/homura_rocm.h:247 */
+hmc_status hmc_where(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *cond,
+                     const hmc_tensor_desc *x, const hmc_tensor_desc *y);
+/* hmc_where where a NULL branch is the constant in x_bits / y_bits. csrc/homura_rocm.h:253 */
+hmc_status hmc_where_constant(hmc_context_t ctx, const hmc_tensor_desc *out,
+                              const hmc_tensor_desc *cond, const hmc_tensor_desc *x,
+                              uint64_t x_bits, const hmc_tensor_desc *y, uint64_t y_bits);
+
+/* ---- reductions (csrc/homura_rocm.h:297-346) ----
+ * `kept`: kept dimensions with the source's strides, data, offset, dtype. `red`: reduced
+ * dimensions with the source's strides. Outputs are contiguous over the kept sizes. The order in
+ * which an output's elements are folded is a function of the sizes and strides only, so results
+ * repeat from run to run. A plan may need scratch memory: ask hmc_reduce_workspace (var = 1 for
+ * hmc_var) and pass at least that many bytes (NULL is fine for 0). */
+#define HMC_REDUCE_SUM 0
+#define HMC_REDUCE_PROD 1
+#define HMC_REDUCE_MEAN 2
+#define HMC_REDUCE_MAX 3
+#define HMC_REDUCE_MIN 4
+#define HMC_REDUCE_ALL 5
+#define HMC_REDUCE_ANY 6
+
+/* csrc/homura_rocm.h:315 */
+hmc_status hmc_reduce_workspace(const hmc_tensor_desc *kept, const hmc_tensor_desc *red,
+                                int32_t var, int64_t *bytes);
+/* cpu::reduce (src/backend/cpu/reduce.rs:92-131): float sum/prod/mean in f64, integer and bool
+ * sum/prod wrapping into I64, max/min in the dtype (first NaN, then first of equals), all/any to
+ * Bool (U8 stays U8). csrc/homura_rocm.h:321 */
+hmc_status hmc_reduce(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
+                      const hmc_tensor_desc *kept, const hmc_tensor_desc *red, void *workspace,
+                      int64_t workspace_bytes);
+/* cpu::var (src/backend/cpu/reduce.rs:135-170): two passes in f64, divisor max(0, n - correction),
+ * NaN for n = 0, sqrt on request. csrc/homura_rocm.h:327 */
+hmc_status hmc_var(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *kept,
+                   const hmc_tensor_desc *red, double correction, int32_t take_sqrt,
+                   void *workspace, int64_t workspace_bytes);
+/* cpu::arg_reduce (src/backend/cpu/reduce.rs:175-225): I64 index along the reduced dimension and,
+ * unless `values` is NULL, the value. csrc/homura_rocm.h:333 */
+hmc_status hmc_arg_reduce(hmc_context_t ctx, const hmc_tensor_desc *values,
+                          const hmc_tensor_desc *indices, const hmc_tensor_desc *kept,
+                          const hmc_tensor_desc *red, int32_t is_max, void *workspace,
+                          int64_t workspace_bytes);
+/* cpu::softmax (src/backend/cpu/misc.rs:15-51) on rows of n elements that are out_stride /
+ * src_stride apart; out_rows / src_rows describe all other dimensions.
+ * csrc/homura_rocm.h:341-346 */
+hmc_status hmc_softmax_workspace(const hmc_tensor_desc *src_rows, int64_t n, int64_t src_stride,
+                                 int64_t *bytes);
+hmc_status hmc_softmax(hmc_context_t ctx, const hmc_tensor_desc *out_rows,
+                       const hmc_tensor_desc *src_rows, int64_t n, int64_t out_stride,
+                       int64_t src_stride, int32_t log, void *workspace,
+                       int64_t workspace_bytes);
+
+/* ---- additions of this backend (no counterpart in csrc/homura_rocm.h) ---- */
+
+/* out = a + b where a and b may differ in float dtype and out has the promoted dtype
+ * (src/dtype.rs:429-470): the same bits as homura's "cast both with hmc_copy, then hmc_binary ADD"
+ * (src/ops/binary.rs:55-60, 132-136) without the temporaries. Also MUL/SUB. */
+hmc_status hmc_binary_promoted(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
+                               const hmc_tensor_desc *a, const hmc_tensor_desc *b);
+
+/* Scalars of one AdamW step (src/optim/adam.rs:125-171), each already rounded to the parameter
+ * dtype's computation type by the caller, as the op-by-op path rounds them. */
+typedef struct hmc_adamw_scalars {
+    double decay;       /* 1 - lr * weight_decay, multiplies the parameter (skipped when 1) */
+    double lerp_coeff;  /* Lerp coefficient for exp_avg: w or w - 1, w = 1 - beta1 */
+    int32_t lerp_small; /* |w| < 0.5 */
+    int32_t has_decay;  /* weight_decay != 0 */
+    double beta2;       /* multiplies exp_avg_sq */
+    double one_minus_beta2;
+    double bias2_sqrt;  /* divides sqrt(exp_avg_sq) */
+    double eps;
+    double neg_step_size; /* -lr / (1 - beta1^t) */
+} hmc_adamw_scalars;
+
+/* One kernel for the whole decoupled-weight-decay Adam update of one parameter: the same
+ * roundings, in the same order, as the sequence of hmc_binary_constant / hmc_fused / hmc_unary /
+ * hmc_copy calls that src/optim/adam.rs:139-170 issues. param, exp_avg and exp_avg_sq are
+ * updated in place; all four operands have one float dtype, equal sizes, any strides. */
+hmc_status hmc_adamw_step(hmc_context_t ctx, const hmc_tensor_desc *param,
+                          const hmc_tensor_desc *grad, const hmc_tensor_desc *exp_avg,
+                          const hmc_tensor_desc *exp_avg_sq, const hmc_adamw_scalars *scalars);
+
+/* Pinned host memory for transfers that should run at link speed. */
+hmc_status hmc_host_alloc(uint64_t nbytes, void **out);
+hmc_status hmc_host_free(void *ptr);
+
+/* The raw cudaStream_t of a context, for callers that order their own work behind it. */
+hmc_status hmc_context_stream(hmc_context_t ctx, void **stream);
+
+/* Elapsed-time markers on the context's stream (cudaEvent_t underneath), so that callers time
+ * kernels on the stream they run on. */
+typedef struct hmc_event *hmc_event_t;
+hmc_status hmc_event_create(hmc_context_t ctx, hmc_event_t *out);
+hmc_status hmc_event_record(hmc_context_t ctx, hmc_event_t ev);
+hmc_status hmc_event_elapsed_ms(hmc_event_t start, hmc_event_t stop, float *ms);
+hmc_status hmc_event_destroy(hmc_event_t ev);
+
+/* ---- introspection (csrc/homura_rocm.h:589-610) ---- */
+const char *hmc_built_archs(void);
+
+typedef struct hmc_abi_info {
+    uint32_t abi_info_size;
+    uint32_t properties_size;
+    uint32_t properties_align;
+    uint32_t properties_offsets[5];
+    int32_t status_values[5];
+    int32_t name_len;
+    int32_t arch_len;
+    uint32_t desc_size;
+    uint32_t desc_align;
+    uint32_t desc_offsets[6];
+    int32_t dtype_values[10];
+    int32_t max_dims;
+    uint32_t adamw_scalars_size;
+    uint32_t adamw_scalars_align;
+} hmc_abi_info;
+
+void hmc_abi_check(hmc_abi_info *out);
+
+/* ---- testing hooks, not part of the supported interface (csrc/homura_rocm.h:612-666) ----
+ * fail_stream_create(n): the thread's next n stream creations fail with HMC_OUT_OF_MEMORY.
+ * fail_after_probe(n): the next n context creations fail late, after stream and probe succeeded.
+ * fail_properties(n): the next n hmc_device_properties_get fail with HMC_CUDA_ERROR.
+ * fail_data(n, oom): the next n data operations fail before queueing anything.
+ * reduce_plan / softmax_plan: which plan the library picks, so tests can reach every path.
+ *   reduce: kind (0 rows, 1 columns, 2 generic), splits of the reduced range, elements per split.
+ *   softmax: kind (0 row in registers, 1 streaming), lanes per row, elements a lane keeps.
+ * live_streams: streams the thread created and has not destroyed. */
+void hmc_test_fail_stream_create(int32_t n);
+void hmc_test_fail_after_probe(int32_t n);
+void hmc_test_fail_properties(int32_t n);
+void hmc_test_fail_data(int32_t n, int32_t out_of_memory);
+hmc_status hmc_test_reduce_plan(const hmc_tensor_desc *kept, const hmc_tensor_desc *red,
+                                int64_t *kind, int64_t *splits, int64_t *chunk);
+hmc_status hmc_test_softmax_plan(const hmc_tensor_desc *src_rows, int64_t n, int64_t src_stride,
+                                 int32_t *kind, int32_t *group, int32_t *cache);
+int32_t hmc_test_live_streams(void);
+hmc_status hmc_test_current_device(int32_t *device);
+hmc_status hmc_test_set_current_device(int32_t device);
+hmc_status hmc_test_fail(const char *message);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HOMURA_CUDA_H */

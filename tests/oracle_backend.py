@@ -1,0 +1,190 @@
+"""The CPU checker behind the interface of homura_b200.host.CudaBackend, over host (numpy) storage.
+TEST INFRASTRUCTURE: it loads oracle/_build/liboracle.so, which no product code may touch."""
+from __future__ import annotations
+
+import ctypes
+import importlib.util
+import math
+from pathlib import Path
+from typing import Optional, Sequence
+
+import numpy as np
+
+from homura_b200 import ffi
+from homura_b200.ffi import hmc_tensor_desc
+from homura_b200.host import (SIZE, STORAGE, Storage, TensorData, contiguous_strides, describe, descs, lines,
+                              output_desc, scalar_bits)
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _load_oracle():
+    spec = importlib.util.spec_from_file_location("oracle_build", ROOT / "oracle" / "build.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    lib = ctypes.CDLL(str(mod.build()))
+    D = ctypes.POINTER(hmc_tensor_desc)
+    i32, i64, u64, f64, vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_uint64, ctypes.c_double, ctypes.c_void_p
+    protos = {
+        "orc_copy": [D, D], "orc_fill": [D, u64], "orc_unary": [i32, D, D], "orc_binary": [i32, D, D, D],
+        "orc_binary_constant": [i32, D, D, u64, i32], "orc_binary_scalar": [i32, D, D, f64, i32],
+        "orc_fused": [i32, D, D, D, D, f64], "orc_where": [D, D, D, D], "orc_where_constant": [D, D, D, u64, D, u64],
+        "orc_reduce": [i32, D, D, D], "orc_var": [D, D, D, f64, i32], "orc_arg_reduce": [D, D, D, D, i32],
+        "orc_softmax": [D, D, i64, i64, i64, i32],
+        "orc_adamw_step": [i32, i64, vp, vp, vp, vp, f64, f64, f64, f64, f64, f64],
+    }
+    for name, args in protos.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = i32, args
+    lib.orc_f32_to_f16.restype, lib.orc_f32_to_f16.argtypes = ctypes.c_uint16, [ctypes.c_float]
+    lib.orc_f32_to_bf16.restype, lib.orc_f32_to_bf16.argtypes = ctypes.c_uint16, [ctypes.c_float]
+    lib.orc_f16_to_f32.restype, lib.orc_f16_to_f32.argtypes = ctypes.c_float, [ctypes.c_uint16]
+    lib.orc_bf16_to_f32.restype, lib.orc_bf16_to_f32.argtypes = ctypes.c_float, [ctypes.c_uint16]
+    lib.orc_erf.restype, lib.orc_erf.argtypes = f64, [f64]
+    return lib
+
+
+class OraclePanic(RuntimeError):
+    """The CPU kernel would panic (unsupported dtype / op, empty max, ...)."""
+
+
+class OracleBackend:
+    name = "oracle"
+
+    def __init__(self):
+        self.lib = _load_oracle()
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise OraclePanic(f"oracle status {rc}")
+
+    def synchronize(self) -> None:
+        pass
+
+    def empty(self, shape, dtype: int) -> TensorData:
+        shape = tuple(shape)
+        n = math.prod(shape)
+        arr = np.zeros(max(n, 1), dtype=STORAGE[dtype])
+        return TensorData(Storage(n * SIZE[dtype], array=arr), dtype, shape, tuple(contiguous_strides(shape)))
+
+    def upload(self, array: np.ndarray, dtype: int, shape=None) -> TensorData:
+        array = np.ascontiguousarray(array, dtype=STORAGE[dtype])
+        shape = tuple(array.shape if shape is None else shape)
+        flat = array.reshape(-1).copy()
+        if flat.size == 0:
+            flat = np.zeros(1, dtype=STORAGE[dtype])
+        return TensorData(Storage(array.nbytes, array=flat), dtype, shape, tuple(contiguous_strides(shape)))
+
+    def download_storage(self, t: TensorData) -> np.ndarray:
+        return t.storage.array
+
+    def download(self, t: TensorData) -> np.ndarray:
+        if t.numel == 0:
+            return np.empty(t.shape, dtype=STORAGE[t.dtype])
+        es = SIZE[t.dtype]
+        view = np.lib.stride_tricks.as_strided(t.storage.array[t.offset:], shape=t.shape,
+                                               strides=[s * es for s in t.strides], writeable=False)
+        return np.ascontiguousarray(view).reshape(t.shape)
+
+    # ---- backend functions (names and argument meaning of src/backend/cpu) ----
+    def copy(self, dst, src):
+        d = descs("copy", [dst, src.expand(dst.shape)])
+        if d is not None:
+            self._check(self.lib.orc_copy(d[0], d[1]))
+
+    def fill(self, dst, value):
+        d = descs("fill", [dst])
+        if d is not None:
+            self._check(self.lib.orc_fill(d[0], scalar_bits(value, dst.dtype)))
+
+    def unary(self, op, out, src):
+        d = descs("unary", [out, src])
+        if d is not None:
+            self._check(self.lib.orc_unary(op, d[0], d[1]))
+
+    def binary(self, op, out, a, b):
+        d = descs("binary", [out, a, b])
+        if d is not None:
+            self._check(self.lib.orc_binary(op, d[0], d[1], d[2]))
+
+    def binary_promoted(self, op, out, a, b):
+        """homura's route for operands of different dtypes: cast both, then the binary kernel
+        (src/ops/binary.rs:55-60)."""
+        ac, bc = self.empty(a.shape, out.dtype), self.empty(b.shape, out.dtype)
+        self.copy(ac, a)
+        self.copy(bc, b)
+        self.binary(op, out, ac, bc)
+
+    def binary_constant(self, op, out, a, value, constant_first):
+        d = descs("binary_constant", [out, a])
+        if d is not None:
+            self._check(self.lib.orc_binary_constant(op, d[0], d[1], scalar_bits(value, a.dtype), int(constant_first)))
+
+    def binary_scalar(self, op, out, a, s, scalar_first):
+        d = descs("binary_scalar", [out, a])
+        if d is not None:
+            self._check(self.lib.orc_binary_scalar(op, d[0], d[1], float(s), int(scalar_first)))
+
+    def fused(self, op, value, out, a, b, c=None):
+        ops = [out, a, b] + ([c] if c is not None else [])
+        d = descs("fused", ops)
+        if d is not None:
+            self._check(self.lib.orc_fused(op, d[0], d[1], d[2], d[3] if c is not None else None, float(value)))
+
+    def where_(self, out, cond, x, y):
+        d = descs("where_", [out, cond, x, y])
+        if d is not None:
+            self._check(self.lib.orc_where(d[0], d[1], d[2], d[3]))
+
+    def where_constant(self, out, cond, x, y):
+        xt, yt = isinstance(x, TensorData), isinstance(y, TensorData)
+        if xt and yt:
+            return self.where_(out, cond, x, y)
+        ops = [out, cond] + ([x] if xt else []) + ([y] if yt else [])
+        d = descs("where_constant", ops)
+        if d is None:
+            return
+        xb = 0 if xt else scalar_bits(x, out.dtype)
+        yb = 0 if yt else scalar_bits(y, out.dtype)
+        xd = d[2] if xt else None
+        yd = d[2] if (yt and not xt) else (d[3] if yt else None)
+        self._check(self.lib.orc_where_constant(d[0], d[1], xd, xb, yd, yb))
+
+    def reduce(self, op, out, src, mask):
+        r = describe("reduce", src, mask)
+        if r is not None:
+            self._check(self.lib.orc_reduce(op, output_desc("reduce", r, out), r.kept, r.red))
+
+    def var(self, out, src, mask, correction, take_sqrt):
+        r = describe("var", src, mask)
+        if r is not None:
+            self._check(self.lib.orc_var(output_desc("var", r, out), r.kept, r.red, float(correction), int(take_sqrt)))
+
+    def arg_reduce(self, values, indices, src, dim, is_max):
+        nd = len(src.shape)
+        r = describe("arg_reduce", src, [d == dim for d in range(nd)])
+        if r is None:
+            return
+        v = output_desc("arg_reduce", r, values) if values is not None else None
+        self._check(self.lib.orc_arg_reduce(v, output_desc("arg_reduce", r, indices), r.kept, r.red, int(is_max)))
+
+    def softmax(self, out, src, dim, log):
+        ln = lines("softmax", out, src, dim, out.strides)
+        if ln is None:
+            return
+        (o, s), n, so, si = ln
+        self._check(self.lib.orc_softmax(o, s, n, so, si, int(log)))
+
+    def adamw_step(self, param, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, weight_decay, step):
+        """The op-by-op sequence of homura's optimizer on contiguous copies, written back in place."""
+        def flat(t):
+            c = self.empty(t.shape, t.dtype)
+            self.copy(c, t)
+            return c
+        p, g, m, v = flat(param), flat(grad), flat(exp_avg), flat(exp_avg_sq)
+        self._check(self.lib.orc_adamw_step(param.dtype, param.numel, p.storage.address, g.storage.address,
+                                            m.storage.address, v.storage.address, lr, beta1, beta2, eps,
+                                            weight_decay, float(step)))
+        self.copy(param, p)
+        self.copy(exp_avg, m)
+        self.copy(exp_avg_sq, v)
