@@ -1,0 +1,378 @@
+"""Benchmark of the elementwise / broadcast hot path on B200: achieved HBM GB/s by algorithmic bytes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE.json configs[1], "Elementwise/broadcast at HBM scale"), one step =
+    x bf16 [8192, 8192] ~ N(0, 1), bias f32 [8192, 1], scale bf16 [1, 8192]
+    y  = silu(x)     * scale + bias   (bf16 + f32 -> f32)          3 kernels
+    yt = silu(x.t()) * scale + bias   (transposed, non-contiguous)  3 kernels
+    c  = x.to(f32)                    (contiguous cast copy)        1 kernel
+through the C ABI of include/homura_cuda.h, outputs preallocated from the caching allocator.
+Algorithmic bytes per step (distinct input elements + output elements, temporaries count zero):
+silu 4N, mul 4N, promoting add 6N (twice), cast 6N, with N = 8192^2: 34 N = 2281.7 MB.
+
+`value` is the whole job's GB/s with inputs resident in HBM; `e2e` is the same metric with the inputs
+coming from pinned host memory and the results going back to it inside the timed region. With N > 1 ranks
+(torchrun) every rank runs the workload on its own GPU (weak scaling, no data-path collective); the time is
+the maximum over ranks. `--impl reference` times the CPU restatement of homura's single-threaded CPU backend
+on a bounded sample of the same workload on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+ROWS = COLS = 8192
+N2 = ROWS * COLS
+STEP_BYTES = 34 * N2
+METRIC = "hbm_gbs_algorithmic"
+UNIT = "GB/s"
+WORKLOAD = "c2_elementwise_broadcast_bf16_8192x8192"
+L2_BYTES = 126 << 20
+
+
+def philox_normal(n: int, seed: int) -> np.ndarray:
+    """Seeded N(0, 1) values (numpy's Philox bit generator), float32."""
+    return np.random.Generator(np.random.Philox(seed)).standard_normal(n, dtype=np.float32)
+
+
+def f32_to_bf16_bits(f: np.ndarray) -> np.ndarray:
+    x = f.astype(np.float32).view(np.uint32).astype(np.uint64)
+    return ((x + 0x7FFF + ((x >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while running."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.proc.wait()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+class Workload:
+    """The C2 step on one backend (device tensors and preallocated outputs)."""
+
+    def __init__(self, be, rows: int = ROWS, cols: int = COLS, seed: int = 0):
+        from homura_b200.host import BF16, F32
+        self.be, self.rows, self.cols = be, rows, cols
+        self.host_x = f32_to_bf16_bits(philox_normal(rows * cols, 11 + seed)).reshape(rows, cols)
+        self.host_bias = philox_normal(rows, 12 + seed).reshape(rows, 1)
+        self.host_scale = f32_to_bf16_bits(philox_normal(cols, 13 + seed)).reshape(1, cols)
+        self.x = be.upload(self.host_x, BF16)
+        self.bias = be.upload(self.host_bias, F32)
+        self.scale = be.upload(self.host_scale, BF16)
+        self.s = be.empty((rows, cols), BF16)      # silu(x), then silu(x) * scale
+        self.st = be.empty((cols, rows), BF16)     # the same for x.t()
+        self.y = be.empty((rows, cols), F32)
+        self.yt = be.empty((cols, rows), F32)
+        self.c = be.empty((rows, cols), F32)
+        self.launches_per_step = 7
+        n = rows * cols
+        self.op_bytes = {"silu": 4 * n, "mul_scale": 4 * n + 2 * cols, "add_bias": 6 * n + 4 * rows,
+                         "silu_t": 4 * n, "mul_scale_t": 4 * n + 2 * rows, "add_bias_t": 6 * n + 4 * cols, "cast": 6 * n}
+
+    def ops(self):
+        from homura_b200 import ffi
+        be, r, c = self.be, self.rows, self.cols
+        xt = self.x.t()
+        # for the transposed product the roles of the broadcast operands swap: scale spans the rows of x.t()
+        scale_t = self.scale.reshape(c, 1).expand(c, r)
+        bias_t = self.bias.reshape(1, r).expand(c, r)
+        return [
+            ("silu", lambda: be.unary(ffi.HMC_UNARY_SILU, self.s, self.x)),
+            ("mul_scale", lambda: be.binary(ffi.HMC_BINARY_MUL, self.s, self.s, self.scale.expand(r, c))),
+            ("add_bias", lambda: be.binary_promoted(ffi.HMC_BINARY_ADD, self.y, self.s, self.bias.expand(r, c))),
+            ("silu_t", lambda: be.unary(ffi.HMC_UNARY_SILU, self.st, xt)),
+            ("mul_scale_t", lambda: be.binary(ffi.HMC_BINARY_MUL, self.st, self.st, scale_t)),
+            ("add_bias_t", lambda: be.binary_promoted(ffi.HMC_BINARY_ADD, self.yt, self.st, bias_t)),
+            ("cast", lambda: be.copy(self.c, self.x)),
+        ]
+
+    def step(self):
+        for _, f in self.ops():
+            f()
+
+
+class Events:
+    def __init__(self, be):
+        self.be = be
+
+    def new(self):
+        ev = ctypes.c_void_p()
+        self.be._check(self.be.lib.hmc_event_create(self.be.ctx, ctypes.byref(ev)))
+        return ev
+
+    def record(self, ev):
+        self.be._check(self.be.lib.hmc_event_record(self.be.ctx, ev))
+
+    def elapsed(self, a, b) -> float:
+        ms = ctypes.c_float()
+        self.be._check(self.be.lib.hmc_event_elapsed_ms(a, b, ctypes.byref(ms)))
+        return ms.value
+
+
+def cpu_sample(seconds_budget: float = 20.0) -> dict:
+    """The CPU restatement of homura's CPU backend (single-threaded, as the original is by construction:
+    every kernel runs inside one global lock, src/backend/cpu/mod.rs:40-64) on rows of the same workload."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    from homura_b200 import ffi
+    from oracle_backend import OracleBackend
+    be = OracleBackend()
+    rows = 256
+    w = Workload(be, rows=rows, cols=COLS)
+    w.step()  # warm the pages
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        w.step()
+        reps += 1
+        if time.perf_counter() - t0 > seconds_budget or reps >= 64:
+            break
+    dt = time.perf_counter() - t0
+    nbytes = 34 * rows * COLS * reps
+    return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"{reps} passes of the 7-kernel step on x bf16 [{rows}, {COLS}] ({rows * COLS} of {N2} elements per pass)",
+            "seconds": dt}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = []
+    sys.path.insert(0, str(ROOT / "tests"))
+    from oracle_backend import OracleBackend
+    be = OracleBackend()
+    rows = 1024
+    w = Workload(be, rows=rows, cols=COLS)
+    for _ in range(args.warmup):
+        w.step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        t1 = time.perf_counter()
+        w.step()
+        per_step.append(time.perf_counter() - t1)
+    dt = time.perf_counter() - t0
+    value = 34 * rows * COLS * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": f"each step covers x bf16 [{rows}, {COLS}] of [{ROWS}, {COLS}]"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port",
+                         "sample": f"{args.steps} steps of the 7-kernel pass on {rows} of {ROWS} rows; homura's CPU "
+                                   "backend is single-threaded by construction"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from homura_b200.host import CudaBackend
+    be = CudaBackend(local)
+    ev = Events(be)
+    w = Workload(be, seed=rank)
+    ops = w.ops()
+
+    def barrier():
+        be.synchronize()
+        if dist is not None:
+            import torch
+            dist.barrier(device_ids=[local])
+            torch.cuda.synchronize()
+
+    # ---- device-resident throughput: W warm-up steps, then exactly K timed steps ----
+    for _ in range(args.warmup):
+        w.step()
+    barrier()
+    start, stop = ev.new(), ev.new()
+    with ClockSampler(local) as clocks:
+        ev.record(start)
+        for _ in range(args.steps):
+            w.step()
+        ev.record(stop)
+        be.synchronize()
+    ms = ev.elapsed(start, stop)
+    barrier()
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = STEP_BYTES * args.steps * world / (ms * 1e-3) / 1e9
+
+    # ---- per-kernel durations, each launch alone with L2 flushed before it ----
+    scratch = be.storage(512 << 20)
+    per_op = {}
+    for name, f in ops:
+        times = []
+        for i in range(3 + 10):
+            be._check(be.lib.hmc_memset(be.ctx, scratch.ptr, i & 0xFF, scratch.nbytes))
+            a, b = ev.new(), ev.new()
+            ev.record(a)
+            f()
+            ev.record(b)
+            t_ms = ev.elapsed(a, b)
+            if i >= 3:
+                times.append(t_ms)
+            be.lib.hmc_event_destroy(a)
+            be.lib.hmc_event_destroy(b)
+        per_op[name] = float(np.mean(times))
+    total_op_ms = sum(per_op.values())
+    dominant = max(per_op, key=per_op.get)
+    peak, peak_kind = peaks()
+    achieved = w.op_bytes[dominant] / (per_op[dominant] * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": UNIT,
+                "frac": achieved / peak, "traffic": None, "share_of_step": per_op[dominant] / total_op_ms,
+                "per_kernel_gbs": {k: w.op_bytes[k] / (v * 1e-3) / 1e9 for k, v in per_op.items()},
+                "per_kernel_ms": per_op}
+
+    # ---- end to end: inputs from pinned host memory, results back to it, inside the timed region ----
+    def pinned(nbytes):
+        p = ctypes.c_void_p()
+        be._check(be.lib.hmc_host_alloc(nbytes, ctypes.byref(p)))
+        return p
+    hx, hb, hs = pinned(w.host_x.nbytes), pinned(w.host_bias.nbytes), pinned(w.host_scale.nbytes)
+    ctypes.memmove(hx, w.host_x.ctypes.data, w.host_x.nbytes)
+    ctypes.memmove(hb, w.host_bias.ctypes.data, w.host_bias.nbytes)
+    ctypes.memmove(hs, w.host_scale.ctypes.data, w.host_scale.nbytes)
+    out_bytes = 4 * N2
+    hy, hyt, hc = pinned(out_bytes), pinned(out_bytes), pinned(out_bytes)
+    h2d = w.host_x.nbytes + w.host_bias.nbytes + w.host_scale.nbytes
+    d2h = 3 * out_bytes
+
+    def e2e_step():
+        lib, ctx = be.lib, be.ctx
+        be._check(lib.hmc_copy_from_host(ctx, w.x.storage.ptr, hx, w.host_x.nbytes))
+        be._check(lib.hmc_copy_from_host(ctx, w.bias.storage.ptr, hb, w.host_bias.nbytes))
+        be._check(lib.hmc_copy_from_host(ctx, w.scale.storage.ptr, hs, w.host_scale.nbytes))
+        w.step()
+        be._check(lib.hmc_copy_to_host(ctx, hy, w.y.storage.ptr, out_bytes))
+        be._check(lib.hmc_copy_to_host(ctx, hyt, w.yt.storage.ptr, out_bytes))
+        be._check(lib.hmc_copy_to_host(ctx, hc, w.c.storage.ptr, out_bytes))
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    ev.record(start)
+    for _ in range(e2e_steps):
+        e2e_step()
+    ev.record(stop)
+    be.synchronize()
+    e2e_ms = ev.elapsed(start, stop)
+    if dist is not None:
+        import torch
+        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = STEP_BYTES * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
+    for p in (hx, hb, hs, hy, hyt, hc):
+        be.lib.hmc_host_free(p)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_sample()
+    barrier()
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "rows": ROWS, "cols": COLS, "kernels_per_step": w.launches_per_step,
+                       "algorithmic_bytes_per_step": STEP_BYTES, "l2": "inputs_larger_than_l2 (x is 134 MB, outputs 268 MB)",
+                       "elements_per_s": 7 * N2 * args.steps * world / (ms * 1e-3),
+                       "frac_of_nominal_8tbs": value / world / 8000.0, "frac_of_measured_copy": value / world / peak},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": w.launches_per_step * args.steps,
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    be.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -49,7 +49,12 @@ inline bool dtype_is_int(int dtype) { return dtype >= HMC_U8 && dtype <= HMC_I64
 
 // ---- f32 <-> half types ----
 __device__ __forceinline__ float f16_to_f32(uint16_t h) {
-    // Exact; the hardware conversion makes a signalling NaN quiet and keeps its payload.
+    // Exact. The hardware conversion turns every NaN into the canonical one, `half` keeps the sign and
+    // payload and sets the quiet bit, so NaNs are widened by hand.
+    if ((h & 0x7FFFu) > 0x7C00u) {
+        return __uint_as_float((static_cast<uint32_t>(h & 0x8000u) << 16) | 0x7FC00000u |
+                               (static_cast<uint32_t>(h & 0x03FFu) << 13));
+    }
     return __half2float(__ushort_as_half(h));
 }
 __device__ __forceinline__ uint16_t f32_to_f16(float f) {
@@ -80,9 +85,10 @@ template <> __device__ __forceinline__ double to_f64(F16 v) { return static_cast
 template <> __device__ __forceinline__ double to_f64(BF16 v) { return static_cast<double>(bf16_to_f32_quiet(v.b)); }
 template <> __device__ __forceinline__ double to_f64(Bool v) { return v.b ? 1.0 : 0.0; }
 
-// Rust's `as i64`: toward zero, saturating, NaN -> 0; the hardware conversion does exactly that.
-__device__ __forceinline__ int64_t f64_as_i64(double v) { return __double2ll_rz(v); }
-__device__ __forceinline__ int64_t f32_as_i64(float v) { return __float2ll_rz(v); }
+// Rust's `as i64`: toward zero, saturating, NaN -> 0. The hardware conversion saturates the same way but
+// turns a NaN into i64::MIN.
+__device__ __forceinline__ int64_t f64_as_i64(double v) { return v != v ? 0 : __double2ll_rz(v); }
+__device__ __forceinline__ int64_t f32_as_i64(float v) { return v != v ? 0 : __float2ll_rz(v); }
 
 template <class T> __device__ __forceinline__ int64_t to_i64(T v) { return static_cast<int64_t>(v); }
 template <> __device__ __forceinline__ int64_t to_i64(float v) { return f32_as_i64(v); }

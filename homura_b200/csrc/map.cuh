@@ -34,6 +34,9 @@ struct MapArgs {
     int32_t rows_fit32;    // rows < 2^31: 32-bit index arithmetic for the row decomposition
     uint32_t constant_mask;  // bit k: operand k is a constant held in constant[k]
     uint64_t constant[kOperands];
+    // The tiled kernel (operands read against the grain through shared memory):
+    uint32_t tile_mask;     // bit k: input k has unit stride along the second-to-last dimension
+    int64_t tiles_a, tiles_b, ntiles;
     char *base[kOperands];  // data + offset, as bytes
     int64_t sizes[HMC_MAX_DIMS];
     int64_t strides[kOperands][HMC_MAX_DIMS];
@@ -212,6 +215,116 @@ __global__ void __launch_bounds__(kThreads) map_kernel(const __grid_constant__ M
     }
 }
 
+// ---- the tiled kernel ----
+// For operands whose unit stride runs along the second-to-last dimension A while the output's runs
+// along the last dimension B (a transposed view): a 64 x 64 tile of each such operand is read with
+// the threads consecutive along A (full 32-byte sectors), parked in shared memory, and read back with
+// the threads consecutive along B, so that both the loads and the stores are coalesced. The tile's
+// row pitch is padded so that both passes are free of bank conflicts for every element size.
+constexpr int kTile = 64;
+
+template <class T> constexpr int tile_pitch() {
+    if constexpr (std::is_same_v<T, Unused>) return 0;
+    else return kTile + (sizeof(T) <= 4 ? 4 / static_cast<int>(sizeof(T)) : 1);
+}
+template <class T> constexpr size_t tile_bytes() {
+    if constexpr (std::is_same_v<T, Unused>) return 0;
+    else return (static_cast<size_t>(kTile) * tile_pitch<T>() * sizeof(T) + 15) / 16 * 16;
+}
+
+template <class T>
+__device__ __forceinline__ void tile_fill(T *tile, const MapArgs &a, int k, int64_t off, int64_t a0, int64_t b0,
+                                          int64_t size_a, int64_t size_b, int64_t sb) {
+    if constexpr (!std::is_same_v<T, Unused>) {
+        constexpr int P = tile_pitch<T>();
+        const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
+        const T *p = reinterpret_cast<const T *>(a.base[k]) + off + (a0 + tx);
+        T v[kTile / 4];
+#pragma unroll
+        for (int i = 0; i < kTile / 4; ++i) {
+            const int b = ty + 4 * i;
+            if (a0 + tx < size_a && b0 + b < size_b) v[i] = p[(b0 + b) * sb];
+        }
+#pragma unroll
+        for (int i = 0; i < kTile / 4; ++i) tile[(ty + 4 * i) * P + tx] = v[i];
+    }
+}
+
+template <class T>
+__device__ __forceinline__ T tile_or_direct(const T *tile, bool tiled, const MapArgs &a, int k, int64_t off, int aa,
+                                            int bb, int64_t a0, int64_t b0, int64_t sa, int64_t sb) {
+    if (tiled) return tile[bb * tile_pitch<T>() + aa];
+    if (a.constant_mask & (1u << k)) {
+        T c;
+        uint64_t bits = a.constant[k];
+        memcpy(&c, &bits, sizeof(T));
+        return c;
+    }
+    return reinterpret_cast<const T *>(a.base[k])[off + (a0 + aa) * sa + (b0 + bb) * sb];
+}
+
+template <class F>
+__global__ void __launch_bounds__(kThreads) map_tile_kernel(const __grid_constant__ MapArgs a, const F f) {
+    using TO = typename F::Out;
+    using TA = typename F::A;
+    using TB = typename F::B;
+    using TC = typename F::C;
+    extern __shared__ __align__(16) unsigned char tile_memory[];
+    TA *tile_a = reinterpret_cast<TA *>(tile_memory);
+    TB *tile_b = reinterpret_cast<TB *>(tile_memory + tile_bytes<TA>());
+    TC *tile_c = reinterpret_cast<TC *>(tile_memory + tile_bytes<TA>() + tile_bytes<TB>());
+    const bool ta = a.tile_mask & 2u, tb = a.tile_mask & 4u, tc = a.tile_mask & 8u;
+    const int da = a.ndim - 2, db = a.ndim - 1;
+    const int64_t size_a = a.sizes[da], size_b = a.sizes[db];
+    const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
+    constexpr int R = kTile / 4;
+    for (int64_t t = blockIdx.x; t < a.ntiles; t += gridDim.x) {
+        const int64_t jb = t % a.tiles_b;
+        const int64_t t2 = t / a.tiles_b;
+        const int64_t ja = t2 % a.tiles_a;
+        int64_t outer = t2 / a.tiles_a;
+        int64_t off[kOperands] = {0, 0, 0, 0};
+        for (int d = da - 1; d >= 0; --d) {
+            const int64_t size = a.sizes[d];
+            const int64_t q = outer / size;
+            const int64_t i = outer - q * size;
+#pragma unroll
+            for (int k = 0; k < kOperands; ++k) off[k] += i * a.strides[k][d];
+            outer = q;
+        }
+        const int64_t a0 = ja * kTile, b0 = jb * kTile;
+        if (ta) tile_fill<TA>(tile_a, a, 1, off[1], a0, b0, size_a, size_b, a.strides[1][db]);
+        if (tb) tile_fill<TB>(tile_b, a, 2, off[2], a0, b0, size_a, size_b, a.strides[2][db]);
+        if (tc) tile_fill<TC>(tile_c, a, 3, off[3], a0, b0, size_a, size_b, a.strides[3][db]);
+        __syncthreads();
+        Pack<TA, R> va;
+        Pack<TB, R> vb;
+        Pack<TC, R> vc;
+        const bool col_ok = b0 + tx < size_b;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int aa = ty + 4 * i;
+            if (col_ok && a0 + aa < size_a) {
+                if constexpr (!std::is_same_v<TA, Unused>)
+                    va.v[i] = tile_or_direct<TA>(tile_a, ta, a, 1, off[1], aa, tx, a0, b0, a.strides[1][da], a.strides[1][db]);
+                if constexpr (!std::is_same_v<TB, Unused>)
+                    vb.v[i] = tile_or_direct<TB>(tile_b, tb, a, 2, off[2], aa, tx, a0, b0, a.strides[2][da], a.strides[2][db]);
+                if constexpr (!std::is_same_v<TC, Unused>)
+                    vc.v[i] = tile_or_direct<TC>(tile_c, tc, a, 3, off[3], aa, tx, a0, b0, a.strides[3][da], a.strides[3][db]);
+            }
+        }
+        TO *po = reinterpret_cast<TO *>(a.base[0]) + off[0];
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int aa = ty + 4 * i;
+            if (col_ok && a0 + aa < size_a) {
+                po[(a0 + aa) * a.strides[0][da] + (b0 + tx) * a.strides[0][db]] = apply<F>(f, va, vb, vc, i);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // One operand of a launch: a description, or (for inputs) a constant given by its bits.
 struct MapOperand {
     const hmc_tensor_desc *desc = nullptr;
@@ -236,6 +349,22 @@ hmc_status launch_map(hmc_context_t ctx, const F &f, const hmc_tensor_desc *out,
     MapArgs a;
     build_map_args(a, out, inputs, ninputs, vec_of<F>(), unroll_of<F>());
     if (a.items == 0) return HMC_OK;
+    if (a.tile_mask != 0) {
+        const size_t smem = tile_bytes<typename F::A>() + tile_bytes<typename F::B>() + tile_bytes<typename F::C>();
+        if (smem > 48 * 1024) {
+            static bool raised = false;  // per instantiation; the attribute is sticky for the function
+            if (!raised) {
+                cudaError_t err = cudaFuncSetAttribute(map_tile_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                       static_cast<int>(smem));
+                if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute");
+                raised = true;
+            }
+        }
+        const int64_t tcap = static_cast<int64_t>(ctx->sm_count) * 32;
+        const unsigned tgrid = static_cast<unsigned>(a.ntiles < tcap ? a.ntiles : tcap);
+        map_tile_kernel<F><<<tgrid, kThreads, smem, ctx->stream>>>(a, f);
+        return launch_status("tiled elementwise kernel launch");
+    }
     int64_t cap = static_cast<int64_t>(ctx->sm_count) * 16;
     unsigned grid = static_cast<unsigned>(a.items < cap ? a.items : cap);
     map_kernel<F><<<grid, kThreads, 0, ctx->stream>>>(a, f);

@@ -1,6 +1,8 @@
 // Host side of the elementwise engine: validation of descriptions and the launch geometry.
 #include "map.cuh"
 
+#include <utility>
+
 namespace hmc {
 
 hmc_status check_desc(const hmc_tensor_desc *d, const char *what) {
@@ -81,6 +83,33 @@ void build_map_args(MapArgs &a, const hmc_tensor_desc *out, const MapOperand *in
     for (int k = 0; k < kOperands; ++k) {
         if (descs[k] == nullptr) continue;
         a.base[k] = static_cast<char *>(descs[k]->data) + descs[k]->offset * element_size(descs[k]->dtype);
+    }
+    // Elementwise work may visit the dimensions in any order: put the output's unit-stride dimension last,
+    // so that stores are always coalesced and an operand that runs against the grain becomes "transposed".
+    if (a.ndim >= 2 && a.strides[0][a.ndim - 1] != 1) {
+        for (int d = a.ndim - 2; d >= 0; --d) {
+            if (a.strides[0][d] == 1) {
+                const int last = a.ndim - 1;
+                std::swap(a.sizes[d], a.sizes[last]);
+                for (int k = 0; k < kOperands; ++k) std::swap(a.strides[k][d], a.strides[k][last]);
+                break;
+            }
+        }
+    }
+    // The tiled kernel: some input has unit stride along the second-to-last dimension and not along the last.
+    if (a.ndim >= 2 && a.strides[0][a.ndim - 1] == 1 && a.sizes[a.ndim - 1] >= 16 && a.sizes[a.ndim - 2] >= 16) {
+        const int da = a.ndim - 2, db = a.ndim - 1;
+        for (int k = 1; k < kOperands; ++k) {
+            if (descs[k] == nullptr) continue;
+            if (a.strides[k][da] == 1 && a.strides[k][db] > 1) a.tile_mask |= 1u << k;
+        }
+        if (a.tile_mask != 0) {
+            a.tiles_a = ceil_div(a.sizes[da], 64);
+            a.tiles_b = ceil_div(a.sizes[db], 64);
+            int64_t outer = 1;
+            for (int d = 0; d < da; ++d) outer *= a.sizes[d];
+            a.ntiles = outer * a.tiles_a * a.tiles_b;
+        }
     }
     a.n0 = a.sizes[a.ndim - 1];
     a.rows = 1;

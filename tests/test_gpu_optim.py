@@ -8,7 +8,7 @@ import optim_cases
 from homura_b200.host import BF16, DTYPE_NAMES, F16, F32, F64, FLOATS
 from optim_protocol import Adam
 from test_gpu_reduce import normal
-from values import assert_same, f64_to_storage
+from values import assert_bitwise, f64_to_storage
 
 pytestmark = pytest.mark.gpu
 
@@ -56,4 +56,5 @@ def test_fused_kernel_equals_op_by_op_in_any_layout(oracle, cuda, dtype):
         results.append([be.download(x) for x in (p, st.exp_avg, st.exp_avg_sq)])
     for other in results[1:]:
         for got, want, what in zip(other, results[0], ("param", "exp_avg", "exp_avg_sq")):
-            assert_same(got, want, dtype, what)
+            # f16 moments underflow to 0 here, so 0/0 appears: a NaN only has to meet a NaN
+            assert_bitwise(got, want, dtype, what)
