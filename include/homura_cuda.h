@@ -235,6 +235,19 @@ hmc_status hmc_softmax(hmc_context_t ctx, const hmc_tensor_desc *out_rows,
 
 /* ---- additions of this backend (no counterpart in csrc/homura_rocm.h) ---- */
 
+/* hmc_reduce without a workspace argument, for callers that cannot allocate one when they need the
+ * reduction (an out-of-memory handler, a loop that must stay clear of the allocator and of driver
+ * allocations, a host whose device memory is all in its own arena). No counterpart in homura's ROCm
+ * boundary, where the Rust side always brings the workspace. The partials live in an array of
+ * HMC_NOALLOC_SCRATCH_BYTES built into the library's device image (held on every GPU that loads the
+ * library until the process exits); a reduction whose plan needs more is refused with HMC_INVALID.
+ * Same results, bit for bit, as hmc_reduce. The entry point allocates nothing. All calls share the one
+ * array: calls that overlap on a GPU race, calls on one context are ordered by its stream. The first
+ * call on a device also looks up the array's device address; make it before any stream capture. */
+#define HMC_NOALLOC_SCRATCH_BYTES 4194304
+hmc_status hmc_reduce_noalloc(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
+                              const hmc_tensor_desc *kept, const hmc_tensor_desc *red);
+
 /* out = a + b where a and b may differ in float dtype and out has the promoted dtype
  * (src/dtype.rs:429-470): the same bits as homura's "cast both with hmc_copy, then hmc_binary ADD"
  * (src/ops/binary.rs:55-60, 132-136) without the temporaries. Also MUL/SUB. */
