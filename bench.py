@@ -231,6 +231,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="only the warm-up and the timed steps (no per-kernel loop, end-to-end pass or CPU sample): "
+                         "the short command to run under ncu")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     if args.impl == "reference":
@@ -278,6 +281,15 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     value = STEP_BYTES * args.steps * world / (ms * 1e-3) / 1e9
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "ms_per_step": ms / args.steps, "profile_run": True,
+                              "gpu_launches": w.launches_per_step * args.steps}))
+        be.close()
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     # ---- per-kernel durations, each launch alone with L2 flushed before it ----
     scratch = be.storage(512 << 20)

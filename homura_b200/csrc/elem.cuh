@@ -5,6 +5,7 @@
 // is narrowed keeps the top of its payload and is made quiet.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <cstdint>
@@ -162,16 +163,33 @@ template <class D, class S> __device__ __forceinline__ D convert(S x) {
 template <class T> struct Comp { using C = float; };
 template <> struct Comp<double> { using C = double; };
 
+// Widening and rounding around arithmetic use the hardware conversions: exact widening, round to nearest
+// even. They differ from the cast routines above only in the sign and payload of a NaN (the hardware
+// produces its canonical NaN), which no arithmetic result is compared on.
 __device__ __forceinline__ float up(float v) { return v; }
 __device__ __forceinline__ double up(double v) { return v; }
-__device__ __forceinline__ float up(F16 v) { return f16_to_f32(v.b); }
+__device__ __forceinline__ float up(F16 v) { return __half2float(__ushort_as_half(v.b)); }
 __device__ __forceinline__ float up(BF16 v) { return bf16_to_f32(v.b); }
 
 template <class T> __device__ __forceinline__ T down(typename Comp<T>::C c);
 template <> __device__ __forceinline__ float down<float>(float c) { return c; }
 template <> __device__ __forceinline__ double down<double>(double c) { return c; }
-template <> __device__ __forceinline__ F16 down<F16>(float c) { return F16{f32_to_f16(c)}; }
-template <> __device__ __forceinline__ BF16 down<BF16>(float c) { return BF16{f32_to_bf16(c)}; }
+template <> __device__ __forceinline__ F16 down<F16>(float c) { return F16{__half_as_ushort(__float2half_rn(c))}; }
+template <> __device__ __forceinline__ BF16 down<BF16>(float c) {
+    return BF16{__bfloat16_as_ushort(__float2bfloat16_rn(c))};
+}
+
+// Two results rounded with one packed conversion.
+__device__ __forceinline__ void down2(F16 &lo, F16 &hi, float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    lo.b = __half_as_ushort(__low2half(h));
+    hi.b = __half_as_ushort(__high2half(h));
+}
+__device__ __forceinline__ void down2(BF16 &lo, BF16 &hi, float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    lo.b = __bfloat16_as_ushort(__low2bfloat16(h));
+    hi.b = __bfloat16_as_ushort(__high2bfloat16(h));
+}
 
 // Host-side dispatch of a dtype code to a type tag.
 template <class F> inline hmc_status dispatch_all(int dtype, F &&f) {

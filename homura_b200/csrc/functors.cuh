@@ -9,12 +9,14 @@
 namespace hmc {
 
 // ---- unary (cpu::unary, src/backend/cpu/mod.rs:334-407) ----
+// Float functors give their result in the computation type through compute(); the engine rounds the
+// results of a whole vector to the dtype (two per conversion for the half types).
 template <class T, int OP>
 struct UnaryFloat {
     using Out = T; using A = T; using B = Unused; using C = Unused;
-    __device__ __forceinline__ T operator()(T v) const {
-        return down<T>(unary_math<OP, typename Comp<T>::C>(up(v)));
-    }
+    using Compute = typename Comp<T>::C;
+    static constexpr bool kFast = std::is_same_v<T, F16> || std::is_same_v<T, BF16>;
+    __device__ __forceinline__ Compute compute(T v) const { return unary_math<OP, Compute, kFast>(up(v)); }
 };
 
 template <class T, int OP>
@@ -63,9 +65,8 @@ struct Fill {
 template <class T, int OP>
 struct BinaryFloat {
     using Out = T; using A = T; using B = T; using C = Unused;
-    __device__ __forceinline__ T operator()(T x, T y) const {
-        return down<T>(binary_math<OP, typename Comp<T>::C>(up(x), up(y)));
-    }
+    using Compute = typename Comp<T>::C;
+    __device__ __forceinline__ Compute compute(T x, T y) const { return binary_math<OP, Compute>(up(x), up(y)); }
 };
 
 // out = op(cast(a), cast(b)) in the promoted float dtype P: the bits of homura's separate cast
@@ -73,8 +74,9 @@ struct BinaryFloat {
 template <class P, class TA, class TB, int OP>
 struct BinaryPromoted {
     using Out = P; using A = TA; using B = TB; using C = Unused;
-    __device__ __forceinline__ P operator()(TA x, TB y) const {
-        return down<P>(binary_math<OP, typename Comp<P>::C>(up(convert<P, TA>(x)), up(convert<P, TB>(y))));
+    using Compute = typename Comp<P>::C;
+    __device__ __forceinline__ Compute compute(TA x, TB y) const {
+        return binary_math<OP, Compute>(up(convert<P, TA>(x)), up(convert<P, TB>(y)));
     }
 };
 
@@ -129,11 +131,12 @@ struct Compare {
 template <class T, int MODE>
 struct ScalarOp {
     using Out = T; using A = T; using B = Unused; using C = Unused;
-    typename Comp<T>::C s;
-    __device__ __forceinline__ T operator()(T x) const {
-        if constexpr (MODE == 0) return down<T>(up(x) * s);
-        else if constexpr (MODE == 1) return down<T>(up(x) / s);
-        else return down<T>(s / up(x));
+    using Compute = typename Comp<T>::C;
+    Compute s;
+    __device__ __forceinline__ Compute compute(T x) const {
+        if constexpr (MODE == 0) return up(x) * s;
+        else if constexpr (MODE == 1) return up(x) / s;
+        else return s / up(x);
     }
 };
 
@@ -141,22 +144,24 @@ struct ScalarOp {
 template <class T, int OP>
 struct Fused2 {
     using Out = T; using A = T; using B = T; using C = Unused;
-    typename Comp<T>::C k;
+    using Compute = typename Comp<T>::C;
+    Compute k;
     bool small;
-    __device__ __forceinline__ T operator()(T a, T b) const {
+    __device__ __forceinline__ Compute compute(T a, T b) const {
         auto x = up(a), y = up(b);
-        if constexpr (OP == HMC_FUSED_SCALED_ADD) return down<T>(m_fma(y, k, x));
-        else return down<T>(m_fma(k, y - x, small ? x : y));
+        if constexpr (OP == HMC_FUSED_SCALED_ADD) return m_fma(y, k, x);
+        else return m_fma(k, y - x, small ? x : y);
     }
 };
 template <class T, int OP>
 struct Fused3 {
     using Out = T; using A = T; using B = T; using C = T;
-    typename Comp<T>::C k;
-    __device__ __forceinline__ T operator()(T a, T b, T c) const {
+    using Compute = typename Comp<T>::C;
+    Compute k;
+    __device__ __forceinline__ Compute compute(T a, T b, T c) const {
         auto x = up(a), y = up(b), z = up(c);
-        if constexpr (OP == HMC_FUSED_ADDCMUL) return down<T>(m_fma(k * y, z, x));
-        else return down<T>(x + k * y / z);
+        if constexpr (OP == HMC_FUSED_ADDCMUL) return m_fma(k * y, z, x);
+        else return x + k * y / z;
     }
 };
 

@@ -20,6 +20,9 @@
 namespace hmc {
 
 constexpr int kThreads = 256;
+#ifndef HMC_MAP_MIN_BLOCKS
+#define HMC_MAP_MIN_BLOCKS 4
+#endif
 constexpr int kOperands = 4;
 
 struct Unused {};
@@ -60,30 +63,36 @@ template <class F> constexpr int vec_of() {
     constexpr int a = 16 / mn, b = 64 / mx;
     return a < b ? a : b;
 }
+template <class T> constexpr int size_or_zero() { return sizeof(T); }
+template <> constexpr int size_or_zero<Unused>() { return 0; }
+
 template <class F> constexpr int unroll_of() {
-    // 64 bytes of the widest operand per thread and iteration.
-    constexpr int so = sizeof(typename F::Out);
-    constexpr int sa = size_or<typename F::A>(so), sb = size_or<typename F::B>(so), sc = size_or<typename F::C>(so);
-    constexpr int mx = so > sa ? (so > sb ? (so > sc ? so : sc) : (sb > sc ? sb : sc)) : (sa > sb ? (sa > sc ? sa : sc) : (sb > sc ? sb : sc));
-    constexpr int bytes = mx * vec_of<F>();
-    return bytes >= 64 ? 1 : (bytes >= 32 ? 2 : 4);
+    // About 64 bytes of inputs in flight per thread and iteration (the loads of all inputs are issued before
+    // the first store), and never more than 64 bytes of output held at once.
+    constexpr int in_bytes = (size_or_zero<typename F::A>() + size_or_zero<typename F::B>() + size_or_zero<typename F::C>()) *
+                             vec_of<F>();
+    constexpr int out_bytes = static_cast<int>(sizeof(typename F::Out)) * vec_of<F>();
+    constexpr int by_in = in_bytes == 0 ? 4 : (in_bytes >= 64 ? 1 : (in_bytes >= 32 ? 2 : 4));
+    constexpr int by_out = out_bytes >= 64 ? 1 : (out_bytes >= 32 ? 2 : 4);
+    return by_in < by_out ? by_in : by_out;
 }
 
+// How an operand is walked along the inner dimension.
+enum : int { kModeUnit = 0, kModeBroadcast = 1, kModeStrided = 2, kModeConstant = 3 };
+
+__device__ __forceinline__ int operand_mode(const MapArgs &a, int k) {
+    if (a.constant_mask & (1u << k)) return kModeConstant;
+    const int64_t s0 = a.strides[k][a.ndim - 1];
+    return s0 == 1 ? kModeUnit : (s0 == 0 ? kModeBroadcast : kModeStrided);
+}
+
+// VEC elements of operand k starting at inner index idx; `row` points to the row's first element.
 template <class T, int VEC>
-__device__ __forceinline__ void load_operand(Pack<T, VEC> &dst, const MapArgs &a, int k, int64_t row_off, int64_t idx,
-                                             int64_t s0) {
+__device__ __forceinline__ void load_operand(Pack<T, VEC> &dst, const MapArgs &a, int k, int mode, const T *row,
+                                             int64_t idx) {
     if constexpr (!std::is_same_v<T, Unused>) {
-        if (a.constant_mask & (1u << k)) {
-            T c;
-            uint64_t bits = a.constant[k];
-            memcpy(&c, &bits, sizeof(T));
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) dst.v[j] = c;
-            return;
-        }
-        const T *p = reinterpret_cast<const T *>(a.base[k]) + row_off;
-        if (s0 == 1) {
-            p += idx;
+        if (mode == kModeUnit) {
+            const T *p = row + idx;
             if (idx + VEC <= a.n0 && (reinterpret_cast<uintptr_t>(p) & (alignof(Pack<T, VEC>) - 1)) == 0) {
                 dst = *reinterpret_cast<const Pack<T, VEC> *>(p);
             } else {
@@ -91,24 +100,30 @@ __device__ __forceinline__ void load_operand(Pack<T, VEC> &dst, const MapArgs &a
                 for (int j = 0; j < VEC; ++j)
                     if (idx + j < a.n0) dst.v[j] = p[j];
             }
-        } else if (s0 == 0) {
-            T c = *p;
+        } else if (mode == kModeBroadcast) {
+            const T c = *row;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) dst.v[j] = c;
+        } else if (mode == kModeConstant) {
+            T c;
+            uint64_t bits = a.constant[k];
+            memcpy(&c, &bits, sizeof(T));
 #pragma unroll
             for (int j = 0; j < VEC; ++j) dst.v[j] = c;
         } else {
+            const int64_t s0 = a.strides[k][a.ndim - 1];
 #pragma unroll
             for (int j = 0; j < VEC; ++j)
-                if (idx + j < a.n0) dst.v[j] = p[(idx + j) * s0];
+                if (idx + j < a.n0) dst.v[j] = row[(idx + j) * s0];
         }
     }
 }
 
 template <class T, int VEC>
-__device__ __forceinline__ void store_operand(const Pack<T, VEC> &src, const MapArgs &a, int64_t row_off, int64_t idx,
-                                              int64_t s0, int k = 0) {
-    T *p = reinterpret_cast<T *>(a.base[k]) + row_off;
-    if (s0 == 1) {
-        p += idx;
+__device__ __forceinline__ void store_operand(const Pack<T, VEC> &src, const MapArgs &a, int k, int mode, T *row,
+                                              int64_t idx) {
+    if (mode == kModeUnit) {
+        T *p = row + idx;
         if (idx + VEC <= a.n0 && (reinterpret_cast<uintptr_t>(p) & (alignof(Pack<T, VEC>) - 1)) == 0) {
             *reinterpret_cast<Pack<T, VEC> *>(p) = src;
         } else {
@@ -117,22 +132,124 @@ __device__ __forceinline__ void store_operand(const Pack<T, VEC> &src, const Map
                 if (idx + j < a.n0) p[j] = src.v[j];
         }
     } else {
+        const int64_t s0 = a.strides[k][a.ndim - 1];
 #pragma unroll
         for (int j = 0; j < VEC; ++j)
-            if (idx + j < a.n0) p[(idx + j) * s0] = src.v[j];
+            if (idx + j < a.n0) row[(idx + j) * s0] = src.v[j];
     }
 }
 
+// The offsets of the operands at outer index `row` (all dimensions but the last), in elements.
+__device__ __forceinline__ void row_offsets(const MapArgs &a, int64_t row, int64_t off[kOperands]) {
+    const int last = a.ndim - 1;
+#pragma unroll
+    for (int k = 0; k < kOperands; ++k) off[k] = 0;
+    if (last <= 0) return;
+    if (a.rows_fit32) {
+        uint32_t r = static_cast<uint32_t>(row);
+        for (int d = last - 1; d > 0; --d) {
+            const uint32_t size = static_cast<uint32_t>(a.sizes[d]);
+            const uint32_t q = r / size;
+            const uint32_t i = r - q * size;
+#pragma unroll
+            for (int k = 0; k < kOperands; ++k) off[k] += static_cast<int64_t>(i) * a.strides[k][d];
+            r = q;
+        }
+#pragma unroll
+        for (int k = 0; k < kOperands; ++k) off[k] += static_cast<int64_t>(r) * a.strides[k][0];
+    } else {
+        int64_t r = row;
+        for (int d = last - 1; d > 0; --d) {
+            const int64_t size = a.sizes[d];
+            const int64_t q = r / size;
+            const int64_t i = r - q * size;
+#pragma unroll
+            for (int k = 0; k < kOperands; ++k) off[k] += i * a.strides[k][d];
+            r = q;
+        }
+#pragma unroll
+        for (int k = 0; k < kOperands; ++k) off[k] += r * a.strides[k][0];
+    }
+}
+
+template <class T, int VEC> __device__ __forceinline__ bool vector_aligned(const T *p) {
+    if constexpr (std::is_same_v<T, Unused>) return true;
+    else return (reinterpret_cast<uintptr_t>(p) & (alignof(Pack<T, VEC>) - 1)) == 0;
+}
+
+// The one value of a broadcast or constant operand for a row (unused for unit-stride operands).
+template <class T>
+__device__ __forceinline__ Pack<T, 1> splat_value(const MapArgs &a, int k, int mode, const T *row) {
+    Pack<T, 1> out;
+    if constexpr (!std::is_same_v<T, Unused>) {
+        if (mode == kModeBroadcast) {
+            out.v[0] = *row;
+        } else if (mode == kModeConstant) {
+            uint64_t bits = a.constant[k];
+            memcpy(&out.v[0], &bits, sizeof(T));
+        } else {
+            out.v[0] = T{};
+        }
+    }
+    return out;
+}
+
+template <class T, int VEC>
+__device__ __forceinline__ void fast_load(Pack<T, VEC> &dst, int mode, const T *row, int64_t idx, const Pack<T, 1> &c) {
+    if constexpr (!std::is_same_v<T, Unused>) {
+        if (mode == kModeUnit) {
+            dst = *reinterpret_cast<const Pack<T, VEC> *>(row + idx);
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) dst.v[j] = c.v[0];
+        }
+    }
+}
+
+template <class T> __device__ __forceinline__ T *operand_row(const MapArgs &a, int k, int64_t off) {
+    if constexpr (std::is_same_v<T, Unused>) return nullptr;
+    else return reinterpret_cast<T *>(a.base[k]) + off;
+}
+
+template <class F, class = void> struct has_compute : std::false_type {};
+template <class F> struct has_compute<F, std::void_t<typename F::Compute>> : std::true_type {};
+
 template <class F, class A, class B, class C>
-__device__ __forceinline__ typename F::Out apply(const F &f, const A &a, const B &b, const C &c, int j) {
-    if constexpr (std::is_same_v<typename F::A, Unused>) return f();
-    else if constexpr (std::is_same_v<typename F::B, Unused>) return f(a.v[j]);
-    else if constexpr (std::is_same_v<typename F::C, Unused>) return f(a.v[j], b.v[j]);
-    else return f(a.v[j], b.v[j], c.v[j]);
+__device__ __forceinline__ auto apply(const F &f, const A &a, const B &b, const C &c, int j) {
+    if constexpr (has_compute<F>::value) {
+        if constexpr (std::is_same_v<typename F::B, Unused>) return f.compute(a.v[j]);
+        else if constexpr (std::is_same_v<typename F::C, Unused>) return f.compute(a.v[j], b.v[j]);
+        else return f.compute(a.v[j], b.v[j], c.v[j]);
+    } else {
+        if constexpr (std::is_same_v<typename F::A, Unused>) return f();
+        else if constexpr (std::is_same_v<typename F::B, Unused>) return f(a.v[j]);
+        else if constexpr (std::is_same_v<typename F::C, Unused>) return f(a.v[j], b.v[j]);
+        else return f(a.v[j], b.v[j], c.v[j]);
+    }
+}
+
+// The outputs of N elements: functors with compute() give results in the computation type, which are
+// rounded to the output dtype here, two per conversion for the half types.
+template <class F, int N, class A, class B, class C>
+__device__ __forceinline__ void apply_all(Pack<typename F::Out, N> &out, const F &f, const A &a, const B &b, const C &c) {
+    using TO = typename F::Out;
+    if constexpr (has_compute<F>::value && (std::is_same_v<TO, F16> || std::is_same_v<TO, BF16>) && N % 2 == 0) {
+#pragma unroll
+        for (int j = 0; j < N; j += 2) {
+            const float r0 = apply<F>(f, a, b, c, j), r1 = apply<F>(f, a, b, c, j + 1);
+            down2(out.v[j], out.v[j + 1], r0, r1);
+        }
+    } else if constexpr (has_compute<F>::value) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) out.v[j] = down<TO>(apply<F>(f, a, b, c, j));
+    } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) out.v[j] = apply<F>(f, a, b, c, j);
+    }
 }
 
 template <class F>
-__global__ void __launch_bounds__(kThreads) map_kernel(const __grid_constant__ MapArgs a, const F f) {
+__global__ void __launch_bounds__(kThreads, HMC_MAP_MIN_BLOCKS) map_kernel(const __grid_constant__ MapArgs a, const F f) {
     using TO = typename F::Out;
     using TA = typename F::A;
     using TB = typename F::B;
@@ -143,9 +260,9 @@ __global__ void __launch_bounds__(kThreads) map_kernel(const __grid_constant__ M
     const int lane = threadIdx.x & (tpr - 1);
     const int rib = threadIdx.x >> a.tpr_log2;
     const int rpb = kThreads >> a.tpr_log2;
-    const int last = a.ndim - 1;
-    const int64_t s0o = a.strides[0][last], s0a = a.strides[1][last], s0b = a.strides[2][last], s0c = a.strides[3][last];
+    const int mo = operand_mode(a, 0), ma = operand_mode(a, 1), mb = operand_mode(a, 2), mc = operand_mode(a, 3);
     const int64_t step = static_cast<int64_t>(tpr) * VEC;
+    const bool modes_fast = mo == kModeUnit && ma != kModeStrided && mb != kModeStrided && mc != kModeStrided;
 
     for (int64_t item = blockIdx.x; item < a.items; item += gridDim.x) {
         int64_t rg, seg;
@@ -161,45 +278,54 @@ __global__ void __launch_bounds__(kThreads) map_kernel(const __grid_constant__ M
         }
         const int64_t row = rg * rpb + rib;
         if (row >= a.rows) continue;
-        int64_t off[kOperands] = {0, 0, 0, 0};
-        if (last > 0) {
-            if (a.rows_fit32) {
-                uint32_t r = static_cast<uint32_t>(row);
-                for (int d = last - 1; d > 0; --d) {
-                    uint32_t size = static_cast<uint32_t>(a.sizes[d]);
-                    uint32_t q = r / size;
-                    uint32_t i = r - q * size;
-#pragma unroll
-                    for (int k = 0; k < kOperands; ++k) off[k] += static_cast<int64_t>(i) * a.strides[k][d];
-                    r = q;
-                }
-#pragma unroll
-                for (int k = 0; k < kOperands; ++k) off[k] += static_cast<int64_t>(r) * a.strides[k][0];
-            } else {
-                int64_t r = row;
-                for (int d = last - 1; d > 0; --d) {
-                    int64_t size = a.sizes[d];
-                    int64_t q = r / size;
-                    int64_t i = r - q * size;
-#pragma unroll
-                    for (int k = 0; k < kOperands; ++k) off[k] += i * a.strides[k][d];
-                    r = q;
-                }
-#pragma unroll
-                for (int k = 0; k < kOperands; ++k) off[k] += r * a.strides[k][0];
-            }
+        TO *po;
+        const TA *pa;
+        const TB *pb;
+        const TC *pc;
+        {
+            int64_t off[kOperands];
+            row_offsets(a, row, off);
+            po = operand_row<TO>(a, 0, off[0]);
+            pa = operand_row<TA>(a, 1, off[1]);
+            pb = operand_row<TB>(a, 2, off[2]);
+            pc = operand_row<TC>(a, 3, off[3]);
         }
         const int64_t i0 = seg * (step * UNR) + static_cast<int64_t>(lane) * VEC;
         Pack<TA, VEC> va[UNR];
         Pack<TB, VEC> vb[UNR];
         Pack<TC, VEC> vc[UNR];
+        // The common case, decided once per row segment: every vector of this thread is whole, the output and
+        // the unit-stride inputs are aligned for vector accesses, the other inputs are one value per row.
+        const bool fast = modes_fast && i0 + (UNR - 1) * step + VEC <= a.n0 && vector_aligned<TO, VEC>(po) &&
+                          (ma != kModeUnit || vector_aligned<TA, VEC>(pa)) && (mb != kModeUnit || vector_aligned<TB, VEC>(pb)) &&
+                          (mc != kModeUnit || vector_aligned<TC, VEC>(pc));
+        if (fast) {
+            const Pack<TA, 1> ca = splat_value<TA>(a, 1, ma, pa);
+            const Pack<TB, 1> cb = splat_value<TB>(a, 2, mb, pb);
+            const Pack<TC, 1> cc = splat_value<TC>(a, 3, mc, pc);
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const int64_t idx = i0 + u * step;
+                fast_load<TA, VEC>(va[u], ma, pa, idx, ca);
+                fast_load<TB, VEC>(vb[u], mb, pb, idx, cb);
+                fast_load<TC, VEC>(vc[u], mc, pc, idx, cc);
+            }
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const int64_t idx = i0 + u * step;
+                Pack<TO, VEC> vo;
+                apply_all<F, VEC>(vo, f, va[u], vb[u], vc[u]);
+                *reinterpret_cast<Pack<TO, VEC> *>(po + idx) = vo;
+            }
+            continue;
+        }
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
             const int64_t idx = i0 + u * step;
             if (idx < a.n0) {
-                load_operand<TA, VEC>(va[u], a, 1, off[1], idx, s0a);
-                load_operand<TB, VEC>(vb[u], a, 2, off[2], idx, s0b);
-                load_operand<TC, VEC>(vc[u], a, 3, off[3], idx, s0c);
+                load_operand<TA, VEC>(va[u], a, 1, ma, pa, idx);
+                load_operand<TB, VEC>(vb[u], a, 2, mb, pb, idx);
+                load_operand<TC, VEC>(vc[u], a, 3, mc, pc, idx);
             }
         }
 #pragma unroll
@@ -207,9 +333,8 @@ __global__ void __launch_bounds__(kThreads) map_kernel(const __grid_constant__ M
             const int64_t idx = i0 + u * step;
             if (idx < a.n0) {
                 Pack<TO, VEC> vo;
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) vo.v[j] = apply<F>(f, va[u], vb[u], vc[u], j);
-                store_operand<TO, VEC>(vo, a, off[0], idx, s0o);
+                apply_all<F, VEC>(vo, f, va[u], vb[u], vc[u]);
+                store_operand<TO, VEC>(vo, a, 0, mo, po, idx);
             }
         }
     }
@@ -217,50 +342,94 @@ __global__ void __launch_bounds__(kThreads) map_kernel(const __grid_constant__ M
 
 // ---- the tiled kernel ----
 // For operands whose unit stride runs along the second-to-last dimension A while the output's runs
-// along the last dimension B (a transposed view): a 64 x 64 tile of each such operand is read with
-// the threads consecutive along A (full 32-byte sectors), parked in shared memory, and read back with
-// the threads consecutive along B, so that both the loads and the stores are coalesced. The tile's
-// row pitch is padded so that both passes are free of bank conflicts for every element size.
+// along the last dimension B (a transposed view). Work is cut into 64 x 64 tiles. A tile of each such
+// operand is read with 16-byte loads along A (its grain), parked in shared memory as rows of A with
+// a 16-byte padded pitch, and read back along B: a thread produces one 32-byte sector of the output
+// (EB consecutive elements along B at one A), the lanes of a warp sit on consecutive A, so every
+// shared-memory gather is conflict free and every global access moves whole sectors. Tiles on the
+// boundary, and operands that are not 16-byte aligned, take an element-wise path through the same
+// shared-memory tile.
 constexpr int kTile = 64;
 
-template <class T> constexpr int tile_pitch() {
+template <class T> constexpr int tile_pitch() {  // elements per shared-memory row (one B index, 64 A's)
     if constexpr (std::is_same_v<T, Unused>) return 0;
-    else return kTile + (sizeof(T) <= 4 ? 4 / static_cast<int>(sizeof(T)) : 1);
+    else return kTile + 16 / static_cast<int>(sizeof(T));
 }
 template <class T> constexpr size_t tile_bytes() {
     if constexpr (std::is_same_v<T, Unused>) return 0;
-    else return (static_cast<size_t>(kTile) * tile_pitch<T>() * sizeof(T) + 15) / 16 * 16;
+    else return static_cast<size_t>(kTile) * tile_pitch<T>() * sizeof(T);
+}
+template <class TO> constexpr int tile_eb() {  // output elements per thread along B: a 32-byte sector
+    return sizeof(TO) >= 8 ? 4 : (sizeof(TO) == 4 ? 8 : 16);
 }
 
+// Fills tile[b][a] (b, a in 0..63) with operand k's elements (a0 + a, b0 + b); `p` points at (a0, b0).
 template <class T>
-__device__ __forceinline__ void tile_fill(T *tile, const MapArgs &a, int k, int64_t off, int64_t a0, int64_t b0,
-                                          int64_t size_a, int64_t size_b, int64_t sb) {
+__device__ __forceinline__ void tile_fill(T *tile, const T *p, int64_t sb, bool vector_ok, int na, int nb) {
     if constexpr (!std::is_same_v<T, Unused>) {
         constexpr int P = tile_pitch<T>();
-        const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
-        const T *p = reinterpret_cast<const T *>(a.base[k]) + off + (a0 + tx);
-        T v[kTile / 4];
+        constexpr int VA = 16 / sizeof(T);
+        constexpr int CH = kTile / VA;  // 16-byte chunks per row
+        if (vector_ok) {
+            constexpr int N = kTile * CH / kThreads;
+            Pack<T, VA> v[N];
 #pragma unroll
-        for (int i = 0; i < kTile / 4; ++i) {
-            const int b = ty + 4 * i;
-            if (a0 + tx < size_a && b0 + b < size_b) v[i] = p[(b0 + b) * sb];
+            for (int i = 0; i < N; ++i) {
+                const int idx = threadIdx.x + kThreads * i;
+                const int b = idx / CH, ac = idx % CH;
+                v[i] = *reinterpret_cast<const Pack<T, VA> *>(p + b * sb + ac * VA);
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                const int idx = threadIdx.x + kThreads * i;
+                const int b = idx / CH, ac = idx % CH;
+                *reinterpret_cast<Pack<T, VA> *>(tile + b * P + ac * VA) = v[i];
+            }
+        } else {
+            const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
+            for (int b = ty; b < nb; b += kThreads / kTile) {
+                if (tx < na) tile[b * P + tx] = p[b * sb + tx];
+            }
         }
-#pragma unroll
-        for (int i = 0; i < kTile / 4; ++i) tile[(ty + 4 * i) * P + tx] = v[i];
     }
 }
 
-template <class T>
-__device__ __forceinline__ T tile_or_direct(const T *tile, bool tiled, const MapArgs &a, int k, int64_t off, int aa,
-                                            int bb, int64_t a0, int64_t b0, int64_t sa, int64_t sb) {
-    if (tiled) return tile[bb * tile_pitch<T>() + aa];
-    if (a.constant_mask & (1u << k)) {
-        T c;
-        uint64_t bits = a.constant[k];
-        memcpy(&c, &bits, sizeof(T));
-        return c;
+// EB elements of input k for output position (a, b .. b + EB): from the tile, a constant, or memory.
+template <class T, int EB>
+__device__ __forceinline__ void tile_gather(Pack<T, EB> &dst, const T *tile, bool tiled, const MapArgs &arg, int k,
+                                            const T *p, int64_t sa, int64_t sb, int a, int b, int nvalid) {
+    if constexpr (!std::is_same_v<T, Unused>) {
+        constexpr int P = tile_pitch<T>();
+        if (tiled) {
+#pragma unroll
+            for (int j = 0; j < EB; ++j) dst.v[j] = tile[(b + j) * P + a];
+        } else if (arg.constant_mask & (1u << k)) {
+            T c;
+            uint64_t bits = arg.constant[k];
+            memcpy(&c, &bits, sizeof(T));
+#pragma unroll
+            for (int j = 0; j < EB; ++j) dst.v[j] = c;
+        } else {
+            const T *q = p + a * sa + b * sb;
+            if (sb == 0) {
+                const T c = *q;
+#pragma unroll
+                for (int j = 0; j < EB; ++j) dst.v[j] = c;
+            } else if (sb == 1 && nvalid == EB && (reinterpret_cast<uintptr_t>(q) & 15) == 0) {
+                constexpr int V = 16 / sizeof(T);
+#pragma unroll
+                for (int j = 0; j < EB; j += V) {
+                    const Pack<T, V> x = *reinterpret_cast<const Pack<T, V> *>(q + j);
+#pragma unroll
+                    for (int e = 0; e < V; ++e) dst.v[j + e] = x.v[e];
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < EB; ++j)
+                    if (j < nvalid) dst.v[j] = q[j * sb];
+            }
+        }
     }
-    return reinterpret_cast<const T *>(a.base[k])[off + (a0 + aa) * sa + (b0 + bb) * sb];
 }
 
 template <class F>
@@ -269,6 +438,9 @@ __global__ void __launch_bounds__(kThreads) map_tile_kernel(const __grid_constan
     using TA = typename F::A;
     using TB = typename F::B;
     using TC = typename F::C;
+    constexpr int EB = tile_eb<TO>();
+    constexpr int BC = kTile / EB;                 // sectors per tile row
+    constexpr int ITEMS = kTile * BC / kThreads;   // sectors per thread
     extern __shared__ __align__(16) unsigned char tile_memory[];
     TA *tile_a = reinterpret_cast<TA *>(tile_memory);
     TB *tile_b = reinterpret_cast<TB *>(tile_memory + tile_bytes<TA>());
@@ -276,8 +448,10 @@ __global__ void __launch_bounds__(kThreads) map_tile_kernel(const __grid_constan
     const bool ta = a.tile_mask & 2u, tb = a.tile_mask & 4u, tc = a.tile_mask & 8u;
     const int da = a.ndim - 2, db = a.ndim - 1;
     const int64_t size_a = a.sizes[da], size_b = a.sizes[db];
-    const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
-    constexpr int R = kTile / 4;
+    const int64_t sao = a.strides[0][da];
+    const int64_t saa = a.strides[1][da], sab = a.strides[1][db];
+    const int64_t sba = a.strides[2][da], sbb = a.strides[2][db];
+    const int64_t sca = a.strides[3][da], scb = a.strides[3][db];
     for (int64_t t = blockIdx.x; t < a.ntiles; t += gridDim.x) {
         const int64_t jb = t % a.tiles_b;
         const int64_t t2 = t / a.tiles_b;
@@ -293,32 +467,48 @@ __global__ void __launch_bounds__(kThreads) map_tile_kernel(const __grid_constan
             outer = q;
         }
         const int64_t a0 = ja * kTile, b0 = jb * kTile;
-        if (ta) tile_fill<TA>(tile_a, a, 1, off[1], a0, b0, size_a, size_b, a.strides[1][db]);
-        if (tb) tile_fill<TB>(tile_b, a, 2, off[2], a0, b0, size_a, size_b, a.strides[2][db]);
-        if (tc) tile_fill<TC>(tile_c, a, 3, off[3], a0, b0, size_a, size_b, a.strides[3][db]);
+        const int na = static_cast<int>(size_a - a0 < kTile ? size_a - a0 : kTile);
+        const int nb = static_cast<int>(size_b - b0 < kTile ? size_b - b0 : kTile);
+        const bool whole = na == kTile && nb == kTile;
+        // pointers at the tile's corner (a0, b0)
+        TO *po = operand_row<TO>(a, 0, off[0] + a0 * sao + b0);
+        const TA *pa = operand_row<TA>(a, 1, off[1] + a0 * saa + b0 * sab);
+        const TB *pb = operand_row<TB>(a, 2, off[2] + a0 * sba + b0 * sbb);
+        const TC *pc = operand_row<TC>(a, 3, off[3] + a0 * sca + b0 * scb);
+        if (ta) tile_fill<TA>(tile_a, pa, sab, whole && vector_aligned<TA, 16 / size_or<TA>(1)>(pa) && (sab * size_or<TA>(1)) % 16 == 0, na, nb);
+        if (tb) tile_fill<TB>(tile_b, pb, sbb, whole && vector_aligned<TB, 16 / size_or<TB>(1)>(pb) && (sbb * size_or<TB>(1)) % 16 == 0, na, nb);
+        if (tc) tile_fill<TC>(tile_c, pc, scb, whole && vector_aligned<TC, 16 / size_or<TC>(1)>(pc) && (scb * size_or<TC>(1)) % 16 == 0, na, nb);
         __syncthreads();
-        Pack<TA, R> va;
-        Pack<TB, R> vb;
-        Pack<TC, R> vc;
-        const bool col_ok = b0 + tx < size_b;
+        const bool out_vector = whole && (reinterpret_cast<uintptr_t>(po) & 15) == 0 && (sao * sizeof(TO)) % 16 == 0;
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int aa = ty + 4 * i;
-            if (col_ok && a0 + aa < size_a) {
-                if constexpr (!std::is_same_v<TA, Unused>)
-                    va.v[i] = tile_or_direct<TA>(tile_a, ta, a, 1, off[1], aa, tx, a0, b0, a.strides[1][da], a.strides[1][db]);
-                if constexpr (!std::is_same_v<TB, Unused>)
-                    vb.v[i] = tile_or_direct<TB>(tile_b, tb, a, 2, off[2], aa, tx, a0, b0, a.strides[2][da], a.strides[2][db]);
-                if constexpr (!std::is_same_v<TC, Unused>)
-                    vc.v[i] = tile_or_direct<TC>(tile_c, tc, a, 3, off[3], aa, tx, a0, b0, a.strides[3][da], a.strides[3][db]);
-            }
-        }
-        TO *po = reinterpret_cast<TO *>(a.base[0]) + off[0];
+        for (int it = 0; it < ITEMS; ++it) {
+            const int idx = threadIdx.x + kThreads * it;
+            const int aa = idx % kTile, bb = (idx / kTile) * EB;
+            if (aa < na && bb < nb) {
+                const int nvalid = nb - bb < EB ? nb - bb : EB;
+                Pack<TA, EB> va;
+                Pack<TB, EB> vb;
+                Pack<TC, EB> vc;
+                tile_gather<TA, EB>(va, tile_a, ta, a, 1, pa, saa, sab, aa, bb, nvalid);
+                tile_gather<TB, EB>(vb, tile_b, tb, a, 2, pb, sba, sbb, aa, bb, nvalid);
+                tile_gather<TC, EB>(vc, tile_c, tc, a, 3, pc, sca, scb, aa, bb, nvalid);
+                Pack<TO, EB> vo;
+                apply_all<F, EB>(vo, f, va, vb, vc);
+                TO *q = po + aa * sao + bb;
+                if (out_vector) {
+                    constexpr int V = 16 / sizeof(TO);
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int aa = ty + 4 * i;
-            if (col_ok && a0 + aa < size_a) {
-                po[(a0 + aa) * a.strides[0][da] + (b0 + tx) * a.strides[0][db]] = apply<F>(f, va, vb, vc, i);
+                    for (int j = 0; j < EB; j += V) {
+                        Pack<TO, V> x;
+#pragma unroll
+                        for (int e = 0; e < V; ++e) x.v[e] = vo.v[j + e];
+                        *reinterpret_cast<Pack<TO, V> *>(q + j) = x;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < EB; ++j)
+                        if (j < nvalid) q[j] = vo.v[j];
+                }
             }
         }
         __syncthreads();
@@ -365,7 +555,9 @@ hmc_status launch_map(hmc_context_t ctx, const F &f, const hmc_tensor_desc *out,
         map_tile_kernel<F><<<tgrid, kThreads, smem, ctx->stream>>>(a, f);
         return launch_status("tiled elementwise kernel launch");
     }
-    int64_t cap = static_cast<int64_t>(ctx->sm_count) * 16;
+    // One item per block while the grid allows it: the hardware scheduler then balances the blocks, and a
+    // block's loads are all in flight at once. The kernel's loop covers larger item counts.
+    const int64_t cap = int64_t{1} << 30;
     unsigned grid = static_cast<unsigned>(a.items < cap ? a.items : cap);
     map_kernel<F><<<grid, kThreads, 0, ctx->stream>>>(a, f);
     return launch_status("elementwise kernel launch");

@@ -50,11 +50,10 @@ __global__ void __launch_bounds__(kThreads) adamw_kernel(const __grid_constant__
     const int lane = threadIdx.x & (tpr - 1);
     const int rib = threadIdx.x >> a.tpr_log2;
     const int rpb = kThreads >> a.tpr_log2;
-    const int last = a.ndim - 1;
     const int64_t step = static_cast<int64_t>(tpr) * VEC;
-    int64_t s0[kOperands];
+    int mode[kOperands];
 #pragma unroll
-    for (int k = 0; k < kOperands; ++k) s0[k] = a.strides[k][last];
+    for (int k = 0; k < kOperands; ++k) mode[k] = operand_mode(a, k);
     for (int64_t item = blockIdx.x; item < a.items; item += gridDim.x) {
         int64_t rg, seg;
         if (a.rows == 1) { rg = 0; seg = item; }
@@ -62,30 +61,22 @@ __global__ void __launch_bounds__(kThreads) adamw_kernel(const __grid_constant__
         else { rg = item / a.segs; seg = item - rg * a.segs; }
         const int64_t row = rg * rpb + rib;
         if (row >= a.rows) continue;
-        int64_t off[kOperands] = {0, 0, 0, 0};
-        if (last > 0) {
-            int64_t r = row;
-            for (int d = last - 1; d > 0; --d) {
-                const int64_t size = a.sizes[d];
-                const int64_t q = r / size;
-                const int64_t i = r - q * size;
-#pragma unroll
-                for (int k = 0; k < kOperands; ++k) off[k] += i * a.strides[k][d];
-                r = q;
-            }
-#pragma unroll
-            for (int k = 0; k < kOperands; ++k) off[k] += r * a.strides[k][0];
-        }
+        int64_t off[kOperands];
+        row_offsets(a, row, off);
+        T *pp = operand_row<T>(a, 0, off[0]);
+        const T *pg = operand_row<T>(a, 1, off[1]);
+        T *pm = operand_row<T>(a, 2, off[2]);
+        T *pv = operand_row<T>(a, 3, off[3]);
         const int64_t i0 = seg * (step * UNR) + static_cast<int64_t>(lane) * VEC;
         Pack<T, VEC> vp[UNR], vg[UNR], vm[UNR], vv[UNR];
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
             const int64_t idx = i0 + u * step;
             if (idx < a.n0) {
-                load_operand<T, VEC>(vp[u], a, 0, off[0], idx, s0[0]);
-                load_operand<T, VEC>(vg[u], a, 1, off[1], idx, s0[1]);
-                load_operand<T, VEC>(vm[u], a, 2, off[2], idx, s0[2]);
-                load_operand<T, VEC>(vv[u], a, 3, off[3], idx, s0[3]);
+                load_operand<T, VEC>(vp[u], a, 0, mode[0], pp, idx);
+                load_operand<T, VEC>(vg[u], a, 1, mode[1], pg, idx);
+                load_operand<T, VEC>(vm[u], a, 2, mode[2], pm, idx);
+                load_operand<T, VEC>(vv[u], a, 3, mode[3], pv, idx);
             }
         }
 #pragma unroll
@@ -94,9 +85,9 @@ __global__ void __launch_bounds__(kThreads) adamw_kernel(const __grid_constant__
             if (idx < a.n0) {
 #pragma unroll
                 for (int j = 0; j < VEC; ++j) f(vp[u].v[j], vg[u].v[j], vm[u].v[j], vv[u].v[j]);
-                store_operand<T, VEC>(vp[u], a, off[0], idx, s0[0], 0);
-                store_operand<T, VEC>(vm[u], a, off[2], idx, s0[2], 2);
-                store_operand<T, VEC>(vv[u], a, off[3], idx, s0[3], 3);
+                store_operand<T, VEC>(vp[u], a, 0, mode[0], pp, idx);
+                store_operand<T, VEC>(vm[u], a, 2, mode[2], pm, idx);
+                store_operand<T, VEC>(vv[u], a, 3, mode[3], pv, idx);
             }
         }
     }
