@@ -11,6 +11,9 @@ through the C ABI of include/homura_cuda.h, outputs preallocated from the cachin
 Algorithmic bytes per step (distinct input elements + output elements, temporaries count zero):
 silu 4N, mul 4N, promoting add 6N (twice), cast 6N, with N = 8192^2: 34 N = 2281.7 MB.
 
+Other configurations of BASELINE.json can be timed the same way with `--workload c3|c4|c5` (reductions, softmax,
+sharded-size elementwise + AdamW); the default, and what the headline number is quoted on, is c2.
+
 `value` is the whole job's GB/s with inputs resident in HBM; `e2e` is the same metric with the inputs
 coming from pinned host memory and the results going back to it inside the timed region. With N > 1 ranks
 (torchrun) every rank runs the workload on its own GPU (weak scaling, no data-path collective); the time is
@@ -149,6 +152,155 @@ class Workload:
             f()
 
 
+def _tile_fill(be, big, small):
+    """Fills the contiguous `big` with repetitions of the contiguous `small` (a device-side broadcast copy)."""
+    n = small.numel
+    reps = big.numel // n
+    be.copy(big.reshape(reps, n), small.reshape(1, n).expand(reps, n))
+
+
+class C3Workload:
+    """BASELINE configs[2]: reductions of f32 / i32 [16384, 4096]."""
+
+    name = "c3_reductions_16384x4096"
+
+    def __init__(self, be, seed: int = 0):
+        from homura_b200.host import F32, I32, I64
+        self.be = be
+        r, c = 16384, 4096
+        n = r * c
+        self.x = be.upload(philox_normal(n, 21 + seed).reshape(r, c), F32)
+        rng = np.random.Generator(np.random.Philox(22 + seed))
+        self.i = be.upload(rng.integers(-1000, 1001, size=(r, c), dtype=np.int32), I32)
+        e = be.empty
+        self.out = {"rows_f": e((r,), F32), "cols_f": e((c,), F32), "full_f": e((), F32), "rows_idx": e((r,), I64),
+                    "rows_i": e((r,), I64), "cols_i": e((c,), I64), "full_i": e((), I64), "rows_iv": e((r,), I32)}
+        b4 = 4 * n
+        self.op_bytes = {k: b4 for k in ["sum_rows", "mean_rows", "var_rows", "sum_cols", "mean_cols", "var_cols", "max_rows",
+                                         "sum_full", "isum_rows", "isum_cols", "imax_rows", "isum_full"]}
+        self.launches_per_step = 12
+
+    def ops(self):
+        from homura_b200 import ffi
+        be, x, i, o = self.be, self.x, self.i, self.out
+        R, C, A = [False, True], [True, False], [True, True]
+        return [
+            ("sum_rows", lambda: be.reduce(ffi.HMC_REDUCE_SUM, o["rows_f"], x, R)),
+            ("mean_rows", lambda: be.reduce(ffi.HMC_REDUCE_MEAN, o["rows_f"], x, R)),
+            ("var_rows", lambda: be.var(o["rows_f"], x, R, 1.0, False)),
+            ("sum_cols", lambda: be.reduce(ffi.HMC_REDUCE_SUM, o["cols_f"], x, C)),
+            ("mean_cols", lambda: be.reduce(ffi.HMC_REDUCE_MEAN, o["cols_f"], x, C)),
+            ("var_cols", lambda: be.var(o["cols_f"], x, C, 1.0, False)),
+            ("max_rows", lambda: be.arg_reduce(o["rows_f"], o["rows_idx"], x, 1, True)),
+            ("sum_full", lambda: be.reduce(ffi.HMC_REDUCE_SUM, o["full_f"], x, A)),
+            ("isum_rows", lambda: be.reduce(ffi.HMC_REDUCE_SUM, o["rows_i"], i, R)),
+            ("isum_cols", lambda: be.reduce(ffi.HMC_REDUCE_SUM, o["cols_i"], i, C)),
+            ("imax_rows", lambda: be.arg_reduce(o["rows_iv"], o["rows_idx"], i, 1, True)),
+            ("isum_full", lambda: be.reduce(ffi.HMC_REDUCE_SUM, o["full_i"], i, A)),
+        ]
+
+    def step(self):
+        for _, f in self.ops():
+            f()
+
+
+class C4Workload:
+    """BASELINE configs[3]: softmax / log_softmax of causally masked f32 logits [8, 32, 2048, 2048] and the
+    row mean of squares of bf16 [32768, 4096] as homura's rms_norm composes it (to f32, pow 2, mean)."""
+
+    name = "c4_softmax_8x32x2048x2048"
+
+    def __init__(self, be, seed: int = 0, batch: int = 256):
+        from homura_b200.host import BF16, BOOL, F32
+        self.be = be
+        n = 2048
+        logits = (3.0 * philox_normal(n * n, 31 + seed)).reshape(n, n)
+        one = be.upload(logits, F32)
+        self.logits = be.empty((batch, n, n), F32)
+        _tile_fill(be, self.logits, one)
+        self.mask = be.upload(np.triu(np.ones((n, n), dtype=np.uint8), 1), BOOL)
+        self.masked = be.empty((batch, n, n), F32)
+        self.soft = be.empty((batch, n, n), F32)
+        k_rows, k_cols = 32768, 4096
+        self.h = be.upload(f32_to_bf16_bits(philox_normal(k_rows * k_cols, 32 + seed)).reshape(k_rows, k_cols), BF16)
+        self.h32 = be.empty((k_rows, k_cols), F32)
+        self.ms = be.empty((k_rows, 1), F32)
+        m = batch * n * n
+        k = k_rows * k_cols
+        self.op_bytes = {"masked_fill": 8 * m + n * n, "softmax": 8 * m, "log_softmax": 8 * m, "to_f32": 6 * k, "pow2": 8 * k,
+                         "mean_rows": 4 * k + 4 * k_rows}
+        self.launches_per_step = 6
+
+    def ops(self):
+        from homura_b200 import ffi
+        be = self.be
+        b, n = self.logits.shape[0], 2048
+        mask = self.mask.reshape(1, n, n).expand(b, n, n)
+        return [
+            ("masked_fill", lambda: be.where_constant(self.masked, mask, float("-inf"), self.logits)),
+            ("softmax", lambda: be.softmax(self.soft, self.masked, 2, False)),
+            ("log_softmax", lambda: be.softmax(self.soft, self.masked, 2, True)),
+            ("to_f32", lambda: be.copy(self.h32, self.h)),
+            ("pow2", lambda: be.binary_constant(ffi.HMC_BINARY_POW, self.h32, self.h32, 2.0, False)),
+            ("mean_rows", lambda: be.reduce(ffi.HMC_REDUCE_MEAN, self.ms, self.h32, [False, True])),
+        ]
+
+    def step(self):
+        for _, f in self.ops():
+            f()
+
+
+class C5Workload:
+    """BASELINE configs[4], one GPU's share: a * b + c on flat f32 tensors, their sum and maximum, and an AdamW
+    step (lr 1e-4, wd 0.01) with the gradient norm. `log2n` sets the elements per tensor (2^32 split over 8 GPUs
+    is 2^29 per GPU)."""
+
+    name = "c5_flat_elementwise_adamw"
+
+    def __init__(self, be, seed: int = 0, log2n: int = 29):
+        from homura_b200.host import F32, F64
+        self.be = be
+        n = 1 << log2n
+        base = [be.upload(philox_normal(1 << 22, 41 + seed + j), F32) for j in range(3)]
+        self.a, self.b, self.c = (be.empty((n,), F32) for _ in range(3))
+        for t, s0 in zip((self.a, self.b, self.c), base):
+            _tile_fill(be, t, s0)
+        self.t = be.empty((n,), F32)
+        self.s = be.empty((), F32)
+        # AdamW: params N(0, 0.02), grads N(0, 1e-3), moments start at 0
+        self.p, self.g, self.m, self.v = (be.empty((n,), F32) for _ in range(4))
+        _tile_fill(be, self.p, be.upload(0.02 * philox_normal(1 << 22, 51 + seed), F32))
+        _tile_fill(be, self.g, be.upload(1e-3 * philox_normal(1 << 22, 52 + seed), F32))
+        be.fill(self.m, 0.0)
+        be.fill(self.v, 0.0)
+        self.step_no = 0
+        self.op_bytes = {"mul": 12 * n, "add": 12 * n, "sum": 4 * n, "max": 4 * n, "adamw": 28 * n, "grad_sq": 8 * n,
+                         "grad_sum": 4 * n}
+        self.launches_per_step = 7
+
+    def ops(self):
+        from homura_b200 import ffi
+        be = self.be
+
+        def adamw():
+            self.step_no += 1
+            be.adamw_step(self.p, self.g, self.m, self.v, lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01,
+                          step=float(self.step_no))
+        return [
+            ("mul", lambda: be.binary(ffi.HMC_BINARY_MUL, self.t, self.a, self.b)),
+            ("add", lambda: be.binary(ffi.HMC_BINARY_ADD, self.t, self.t, self.c)),
+            ("sum", lambda: be.reduce(ffi.HMC_REDUCE_SUM, self.s, self.t, [True])),
+            ("max", lambda: be.reduce(ffi.HMC_REDUCE_MAX, self.s, self.t, [True])),
+            ("adamw", adamw),
+            ("grad_sq", lambda: be.binary(ffi.HMC_BINARY_MUL, self.t, self.g, self.g)),
+            ("grad_sum", lambda: be.reduce(ffi.HMC_REDUCE_SUM, self.s, self.t, [True])),
+        ]
+
+    def step(self):
+        for _, f in self.ops():
+            f()
+
+
 class Events:
     def __init__(self, be):
         self.be = be
@@ -231,6 +383,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
     ap.add_argument("--profile", action="store_true",
                     help="only the warm-up and the timed steps (no per-kernel loop, end-to-end pass or CPU sample): "
                          "the short command to run under ncu")
@@ -252,7 +405,12 @@ def main() -> None:
     from homura_b200.host import CudaBackend
     be = CudaBackend(local)
     ev = Events(be)
-    w = Workload(be, seed=rank)
+    if args.workload == "c2":
+        w = Workload(be, seed=rank)
+        workload_name, step_bytes = WORKLOAD, STEP_BYTES
+    else:
+        w = {"c3": C3Workload, "c4": C4Workload, "c5": C5Workload}[args.workload](be, seed=rank)
+        workload_name, step_bytes = w.name, sum(w.op_bytes.values())
     ops = w.ops()
 
     def barrier():
@@ -280,7 +438,7 @@ def main() -> None:
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    value = STEP_BYTES * args.steps * world / (ms * 1e-3) / 1e9
+    value = step_bytes * args.steps * world / (ms * 1e-3) / 1e9
     if args.profile:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -316,6 +474,21 @@ def main() -> None:
                 "frac": achieved / peak, "traffic": None, "share_of_step": per_op[dominant] / total_op_ms,
                 "per_kernel_gbs": {k: w.op_bytes[k] / (v * 1e-3) / 1e9 for k, v in per_op.items()},
                 "per_kernel_ms": per_op}
+
+    if args.workload != "c2":
+        # the other configurations report device-resident throughput and per-kernel rooflines only
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+                              "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+                              "config": {"workload": workload_name, "kernels_per_step": w.launches_per_step,
+                                         "algorithmic_bytes_per_step": step_bytes},
+                              "clocks": clocks.summary(), "gpu_launches": w.launches_per_step * args.steps,
+                              "roofline": roofline}))
+        be.close()
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end: inputs from pinned host memory, results back to it, inside the timed region ----
     def pinned(nbytes):

@@ -12,6 +12,33 @@
 
 namespace hmc {
 
+// e^d for an f64 argument to a relative error below 2^-40 (not the last bits of an f64): 2^k * 2^r with
+// t = d * log2(e), k = round(t), r = t - k in [-1/2, 1/2], 2^r by its Taylor polynomial of degree 10, the
+// scaling through the exponent field. Results below 2^-1022 come out as 2^-1022-ish tiny values instead of
+// subnormals, which is all a sum of exponentials or an f32 result needs.
+__device__ __forceinline__ double exp_lite(double d) {
+    double t = d * 1.4426950408889634074;
+    t = fmin(fmax(t, -1100.0), 1100.0);
+    const double magic = 6755399441055744.0;  // 1.5 * 2^52: adding it leaves round(t) in the low word
+    const double z = t + magic;
+    const double r = t - (z - magic);
+    int k = __double2loint(z);
+    double p = 0x1.e4cf5158b8ecap-28;
+    p = __fma_rn(p, r, 0x1.b5253d395e7c4p-24);
+    p = __fma_rn(p, r, 0x1.62c0223a5c824p-20);
+    p = __fma_rn(p, r, 0x1.ffcbfc588b0c7p-17);
+    p = __fma_rn(p, r, 0x1.430912f86c787p-13);
+    p = __fma_rn(p, r, 0x1.5d87fe78a6731p-10);
+    p = __fma_rn(p, r, 0x1.3b2ab6fba4e77p-7);
+    p = __fma_rn(p, r, 0x1.c6b08d704a0c0p-5);
+    p = __fma_rn(p, r, 0x1.ebfbdff82c58fp-3);
+    p = __fma_rn(p, r, 0x1.62e42fefa39efp-1);
+    p = __fma_rn(p, r, 1.0);
+    k = max(-1022, min(1023, k));
+    const double y = p * __hiloint2double((k + 1023) << 20, 0);
+    return d != d ? d : y;
+}
+
 // exp of an f32 through f64, without the general-purpose f64 exp: e^x = 2^k * 2^r with t = x * log2(e),
 // k = round(t), r = t - k in [-1/2, 1/2] (exact), 2^r by its Taylor polynomial of degree 10 (relative error
 // below 2^-41), the scaling by 2^k through the exponent field, and one rounding to f32, which also produces
@@ -53,6 +80,9 @@ __device__ __forceinline__ double m_cos(double x) { return cos(x); }
 __device__ __forceinline__ float m_tanh(float x) { return static_cast<float>(tanh(static_cast<double>(x))); }
 __device__ __forceinline__ double m_tanh(double x) { return tanh(x); }
 __device__ __forceinline__ float m_pow(float x, float y) {
+    // x^2 (homura's `x.pow(2)`, e.g. in its rms_norm) is x * x rounded once, which is what a correctly
+    // rounded powf gives; everything else goes through the f64 pow and one rounding.
+    if (y == 2.0f) return x * x;
     return static_cast<float>(pow(static_cast<double>(x), static_cast<double>(y)));
 }
 __device__ __forceinline__ double m_pow(double x, double y) { return pow(x, y); }

@@ -448,7 +448,8 @@ struct SquaredDeviation {
 
 // ---- sinks ----
 // Float sum / prod / mean: mode 0 rounds the f64 to T, mode 1 divides by the count first, mode 2
-// stores the f64 mean into `means` (first pass of var).
+// stores the f64 mean into `means` (first pass of var), mode 3 stores the f64 accumulator itself (the
+// partial of one shard).
 template <class T>
 struct FloatSink {
     T *out;
@@ -457,7 +458,8 @@ struct FloatSink {
     __device__ __forceinline__ void put(int64_t o, double a, int64_t count) const {
         if (mode == 0) out[o] = from_f64<T>(a);
         else if (mode == 1) out[o] = from_f64<T>(a / static_cast<double>(count));
-        else means[o] = a / static_cast<double>(count);
+        else if (mode == 2) means[o] = a / static_cast<double>(count);
+        else means[o] = a;
     }
 };
 struct Int64Sink {
@@ -491,6 +493,7 @@ struct VarSink {
 
 // Internal launchers, one translation unit each.
 hmc_status reduce_float(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out, ReduceArgs &a);
+hmc_status reduce_float_partial(hmc_context_t ctx, int32_t op, double *partial, ReduceArgs &a);
 hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs &a, double correction, int take_sqrt,
                       double *means);
 hmc_status reduce_int(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out, ReduceArgs &a);

@@ -12,6 +12,14 @@ hmc_status reduce_float(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *ou
     });
 }
 
+hmc_status reduce_float_partial(hmc_context_t ctx, int32_t op, double *partial, ReduceArgs &a) {
+    return dispatch_float(a.kept.dtype, [&](auto t) {
+        using T = decltype(t);
+        if (op == HMC_REDUCE_PROD) return launch_reduce(a, FloatFold<T, true>{}, FloatSink<T>{nullptr, partial, 3}, ctx->stream);
+        return launch_reduce(a, FloatFold<T, false>{}, FloatSink<T>{nullptr, partial, 3}, ctx->stream);
+    });
+}
+
 namespace {
 
 // Sum, mean and squared deviations of each output in one kernel, for plans without chunks: the

@@ -12,6 +12,7 @@
 #include <math_constants.h>
 
 #include "map.cuh"
+#include "math.cuh"
 #include "reduce.cuh"
 
 namespace hmc {
@@ -77,13 +78,23 @@ __device__ __forceinline__ double group_sum(double v, double *scratch) {
     return v;
 }
 
+// exp(d) for d = x - max <= 0, or NaN. exp(-inf) is +0 without evaluating anything. Rows of F16, BF16 and
+// F32 tensors are rounded to at most 24 bits at the end, so their exponentials need 40 good bits, not 53:
+// they take the short polynomial; F64 rows take the full f64 exp.
+template <class T>
 __device__ __forceinline__ double exp_shifted(double d) {
-    // d = x - max <= 0, or NaN. exp(-inf) is +0 without evaluating anything.
-    return d == -CUDART_INF ? 0.0 : exp(d);
+    if (d == -CUDART_INF) return 0.0;
+    if constexpr (std::is_same_v<T, double>) return exp(d);
+    else return exp_lite(d);
 }
 
+// Rows are handled one after the other inside a block (load, max, exp, sum, store are dependent phases), so
+// throughput is rows in flight per SM: the register budget is set to keep four blocks resident while a lane
+// caches up to two vectors, three for four.
+constexpr int softmax_min_blocks(int cv) { return cv <= 2 ? 4 : (cv <= 4 ? 3 : 2); }
+
 template <class T, int G, int CV, bool LOG>
-__global__ void __launch_bounds__(kRThreads) softmax_kernel(const __grid_constant__ SoftmaxArgs a) {
+__global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_kernel(const __grid_constant__ SoftmaxArgs a) {
     constexpr int VEC = 16 / sizeof(T);
     constexpr int P = kRThreads / G;
     constexpr int NV = CV > 0 ? CV : 1;
@@ -154,10 +165,10 @@ __global__ void __launch_bounds__(kRThreads) softmax_kernel(const __grid_constan
                     if (in) {
                         const double d = x[c][e] - mx;
                         if constexpr (LOG) {
-                            sum += exp_shifted(d);
+                            sum += exp_shifted<T>(d);
                             x[c][e] = d;
                         } else {
-                            x[c][e] = exp_shifted(d);
+                            x[c][e] = exp_shifted<T>(d);
                             sum += x[c][e];
                         }
                     }
@@ -165,13 +176,19 @@ __global__ void __launch_bounds__(kRThreads) softmax_kernel(const __grid_constan
             }
             sum = group_sum<G>(sum, scratch);
             const double log_sum = LOG ? log(sum) : 0.0;
+            // One division per row for the narrower dtypes: e * (1 / sum) differs from e / sum by an f64 ulp,
+            // far below their rounding. F64 rows divide element by element like the CPU.
+            constexpr bool kReciprocal = !std::is_same_v<T, double>;
+            const double inv = kReciprocal ? 1.0 / sum : 0.0;
 #pragma unroll
             for (int c = 0; c < NV; ++c) {
                 const int64_t v = lane + static_cast<int64_t>(c) * G;
                 if (valid && v < nvec) {
                     RVec<T, VEC> y;
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) y.v[e] = from_f64<T>(LOG ? x[c][e] - log_sum : x[c][e] / sum);
+                    for (int e = 0; e < VEC; ++e) {
+                        y.v[e] = from_f64<T>(LOG ? x[c][e] - log_sum : (kReciprocal ? x[c][e] * inv : x[c][e] / sum));
+                    }
                     store_vec(v, y);
                 }
             }
@@ -195,7 +212,7 @@ __global__ void __launch_bounds__(kRThreads) softmax_kernel(const __grid_constan
                 load_vec(v, raw);
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) {
-                    if (v * VEC + e < a.n) sum += exp_shifted(to_f64(raw.v[e]) - mx);
+                    if (v * VEC + e < a.n) sum += exp_shifted<T>(to_f64(raw.v[e]) - mx);
                 }
             }
             sum = group_sum<G>(sum, scratch);
@@ -206,7 +223,7 @@ __global__ void __launch_bounds__(kRThreads) softmax_kernel(const __grid_constan
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) {
                     const double d = to_f64(raw.v[e]) - mx;
-                    y.v[e] = from_f64<T>(LOG ? d - log_sum : exp_shifted(d) / sum);
+                    y.v[e] = from_f64<T>(LOG ? d - log_sum : exp_shifted<T>(d) / sum);
                 }
                 store_vec(v, y);
             }

@@ -480,6 +480,35 @@ class CudaBackend:
         self._check(self.lib.hmc_arg_reduce(self.ctx, v, i, r.kept, r.red, int(is_max), ws.ptr if ws else None,
                                             ws.nbytes if ws else 0))
 
+    # ---- sharded reductions (include/homura_cuda_shard.h) ----
+    def reduce_partial(self, op: int, partial: Storage, src: TensorData, mask: Sequence[bool]) -> None:
+        """f64 partial sums (products) of this shard, one per output, into `partial`."""
+        r = describe("reduce_partial", src, mask)
+        if r is None:
+            return
+        ws = self._plan_workspace(r, False)
+        self._check(self.lib.hmc_reduce_partial(self.ctx, op, ctypes.cast(partial.ptr, ctypes.POINTER(ctypes.c_double)),
+                                                r.kept, r.red, ws.ptr if ws else None, ws.nbytes if ws else 0))
+
+    def shard_combine_float(self, op: int, out: TensorData, gathered: Storage, ranks: int, nout: int, count: int) -> None:
+        d = _flat_desc(out)
+        self._check(self.lib.hmc_shard_combine_float(self.ctx, op, d, ctypes.cast(gathered.ptr, ctypes.POINTER(ctypes.c_double)),
+                                                     ranks, nout, count))
+
+    def shard_combine_int(self, op: int, out: TensorData, gathered: Storage, ranks: int, nout: int) -> None:
+        d = _flat_desc(out)
+        self._check(self.lib.hmc_shard_combine_int(self.ctx, op, d, ctypes.cast(gathered.ptr, ctypes.POINTER(ctypes.c_int64)),
+                                                   ranks, nout))
+
+    def shard_combine_extreme(self, is_max: bool, values: Optional[TensorData], indices: Optional[TensorData],
+                              gathered_values: Storage, dtype: int, gathered_indices: Optional[Storage],
+                              offsets: Optional[Sequence[int]], ranks: int, nout: int) -> None:
+        off = (ctypes.c_int64 * ranks)(*offsets) if offsets is not None else None
+        gi = ctypes.cast(gathered_indices.ptr, ctypes.POINTER(ctypes.c_int64)) if gathered_indices is not None else None
+        self._check(self.lib.hmc_shard_combine_extreme(
+            self.ctx, int(is_max), _flat_desc(values) if values is not None else None,
+            _flat_desc(indices) if indices is not None else None, gathered_values.ptr, dtype, gi, off, ranks, nout))
+
     def softmax(self, out: TensorData, src: TensorData, dim: int, log: bool) -> None:
         ln = lines("softmax", out, src, dim, out.strides)
         if ln is None:
@@ -500,6 +529,19 @@ class CudaBackend:
             return
         sc = adamw_scalars(param.dtype, lr, beta1, beta2, eps, weight_decay, step)
         self._check(self.lib.hmc_adamw_step(self.ctx, d[0], d[1], d[2], d[3], ctypes.byref(sc)))
+
+
+def _flat_desc(t: TensorData) -> hmc_tensor_desc:
+    """A contiguous tensor as one dimension."""
+    assert t.is_contiguous()
+    d = hmc_tensor_desc()
+    d.data, d.offset, d.dtype = t.storage.address, t.offset, t.dtype
+    if t.numel == 1:
+        d.ndim = 0
+    else:
+        d.ndim = 1
+        d.sizes[0], d.strides[0] = t.numel, 1
+    return d
 
 
 def _round_to_compute(v: float, dtype: int) -> float:

@@ -1,0 +1,76 @@
+/*
+ * homura_cuda_shard.h: reductions of a tensor that is split along its outermost dimension over the
+ * GPUs of one machine.
+ *
+ * homura has no multi-GPU collective of any kind (its devices exchange data through host memory, one
+ * device lock at a time, src/backend/mod.rs:240-255), so nothing here replaces a declaration of
+ * csrc/homura_rocm.h; this is the exchange step its reductions need once a tensor is sharded. Elementwise
+ * work, reductions over inner dimensions and softmax over the last dimension need no exchange at all:
+ * each GPU runs the ordinary entry points on its shard.
+ *
+ * A reduction that folds the sharded dimension runs in three steps, all on the contexts' streams:
+ *   1. every rank folds its shard into per-output partials that keep the accumulator's precision
+ *      (f64 for float sums, products and means: hmc_reduce_partial; integer sums, max/min values and
+ *      their indices are exact already and come from hmc_reduce / hmc_arg_reduce);
+ *   2. the partials of all ranks are gathered into every rank's own memory (hmc_comm_allgather: one NCCL
+ *      all-gather of a few bytes per output, latency bound);
+ *   3. every rank folds the gathered partials in rank order (hmc_shard_combine_*): the same bits on every
+ *      rank and on every run, "first NaN, then first of equals" across shards as within one, and global
+ *      indices for the arg reductions. (An NCCL all-reduce with ncclSum / ncclMax promises neither an
+ *      order nor a NaN rule, which is why the combine is a kernel of this library.)
+ *
+ * The hmc_comm_* entry points live in libhomura_cuda_shard.so, which links NCCL; the rest is in
+ * libhomura_cuda.so.
+ */
+#ifndef HOMURA_CUDA_SHARD_H
+#define HOMURA_CUDA_SHARD_H
+
+#include "homura_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* hmc_reduce for float SUM, PROD or MEAN that stops before the rounding: partial[o] is the f64 sum (or
+ * product) of output o's elements on this shard (MEAN gives the sum). `partial` holds one f64 per output
+ * in device memory. Workspace as for hmc_reduce. */
+hmc_status hmc_reduce_partial(hmc_context_t ctx, int32_t op, double *partial, const hmc_tensor_desc *kept,
+                              const hmc_tensor_desc *red, void *workspace, int64_t workspace_bytes);
+
+/* out[o] = round(fold over r = 0..ranks-1 of gathered[r * nout + o]) for SUM and PROD, the sum divided by
+ * total_count for MEAN. `out` is a contiguous float tensor of nout elements. */
+hmc_status hmc_shard_combine_float(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out, const double *gathered,
+                                   int32_t ranks, int64_t nout, int64_t total_count);
+
+/* Wrapping i64 SUM or PROD of the ranks' I64 results. */
+hmc_status hmc_shard_combine_int(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out, const int64_t *gathered,
+                                 int32_t ranks, int64_t nout);
+
+/* Maximum or minimum over the ranks' results: gathered_values[r * nout + o] has the dtype of out_values;
+ * gathered_indices (may be NULL) holds each rank's local index along the sharded dimension, to which
+ * index_offsets[r] (host memory, `ranks` entries: the first global index of rank r's shard) is added.
+ * A NaN of the lowest rank wins, then the first of equal values. Either output may be NULL. */
+hmc_status hmc_shard_combine_extreme(hmc_context_t ctx, int32_t is_max, const hmc_tensor_desc *out_values,
+                                     const hmc_tensor_desc *out_indices, const void *gathered_values, int32_t dtype,
+                                     const int64_t *gathered_indices, const int64_t *index_offsets, int32_t ranks,
+                                     int64_t nout);
+
+/* ---- NCCL (libhomura_cuda_shard.so) ---- */
+#define HMC_COMM_ID_BYTES 128
+typedef struct hmc_comm *hmc_comm_t;
+
+/* A fresh identifier for a communicator; rank 0 makes it and hands it to the others by any channel. */
+hmc_status hmc_comm_unique_id(uint8_t *id);
+/* Joins the communicator `id` as `rank` of `ranks` with the context's device and stream (collective:
+ * every rank calls it). */
+hmc_status hmc_comm_create(hmc_context_t ctx, int32_t ranks, int32_t rank, const uint8_t *id, hmc_comm_t *out);
+hmc_status hmc_comm_destroy(hmc_comm_t comm);
+/* Queues an all-gather on the context's stream: rank r's `bytes` bytes at `send` land at
+ * recv + r * bytes on every rank. send and recv are device memory of the context's device. */
+hmc_status hmc_comm_allgather(hmc_comm_t comm, const void *send, void *recv, uint64_t bytes);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HOMURA_CUDA_SHARD_H */

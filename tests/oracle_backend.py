@@ -175,6 +175,61 @@ class OracleBackend:
         (o, s), n, so, si = ln
         self._check(self.lib.orc_softmax(o, s, n, so, si, int(log)))
 
+    # ---- the sharded reductions' local and combine steps, restated on the host for the CPU tests ----
+    def storage(self, nbytes: int) -> Storage:
+        return Storage(nbytes, array=np.zeros(max(nbytes, 1), dtype=np.uint8))
+
+    def reduce_partial(self, op, partial: Storage, src, mask):
+        """f64 partial sums / products in the CPU's fold order: the fold of the exactly widened elements."""
+        from homura_b200.host import F64
+        wide = self.empty(src.shape, F64)
+        self.copy(wide, src)
+        kept = [n for n, m in zip(src.shape, mask) if not m]
+        out = self.empty(kept, F64)
+        self.reduce(ffi.HMC_REDUCE_SUM if op == ffi.HMC_REDUCE_MEAN else op, out, wide, mask)
+        partial.array[:8 * out.numel] = self.download(out).reshape(-1).view(np.uint8)
+
+    def shard_combine_float(self, op, out, gathered: Storage, ranks, nout, count):
+        from homura_b200.host import F64
+        g = gathered.array[:8 * ranks * nout].view(np.float64).reshape(ranks, nout)
+        acc = np.ones(nout) if op == ffi.HMC_REDUCE_PROD else np.zeros(nout)
+        with np.errstate(all="ignore"):
+            for r in range(ranks):
+                acc = acc * g[r] if op == ffi.HMC_REDUCE_PROD else acc + g[r]
+            if op == ffi.HMC_REDUCE_MEAN:
+                acc = acc / float(count)
+        self.copy(out, self.upload(acc, F64, out.shape))
+
+    def shard_combine_int(self, op, out, gathered: Storage, ranks, nout):
+        g = gathered.array[:8 * ranks * nout].view(np.uint64).reshape(ranks, nout)
+        acc = np.ones(nout, dtype=np.uint64) if op == ffi.HMC_REDUCE_PROD else np.zeros(nout, dtype=np.uint64)
+        with np.errstate(over="ignore"):
+            for r in range(ranks):
+                acc = acc * g[r] if op == ffi.HMC_REDUCE_PROD else acc + g[r]
+        out.storage.array[out.offset:out.offset + nout] = acc.view(np.int64)
+
+    def shard_combine_extreme(self, is_max, values, indices, gathered_values: Storage, dtype, gathered_indices, offsets,
+                              ranks, nout):
+        """First NaN, then first of equals, in rank order (src/backend/cpu/reduce.rs:75-86)."""
+        from values import is_nan_raw, storage_to_f64
+        gv = gathered_values.array[:SIZE[dtype] * ranks * nout].view(STORAGE[dtype]).reshape(ranks, nout)
+        gi = None if gathered_indices is None else gathered_indices.array[:8 * ranks * nout].view(np.int64).reshape(ranks, nout)
+        best, best_i = gv[0].copy(), (gi[0] + offsets[0] if gi is not None else np.zeros(nout, dtype=np.int64))
+        for r in range(1, ranks):
+            x = gv[r]
+            kx, kb = storage_to_f64(x, dtype), storage_to_f64(best, dtype)
+            if dtype == 5:  # I64: compare exactly
+                kx, kb = x, best
+            better = (kx > kb) if is_max else (kx < kb)
+            take = ~is_nan_raw(best, dtype) & (is_nan_raw(x, dtype) | better)
+            best = np.where(take, x, best)
+            if gi is not None:
+                best_i = np.where(take, gi[r] + offsets[r], best_i)
+        if values is not None:
+            values.storage.array[values.offset:values.offset + nout] = best
+        if indices is not None:
+            indices.storage.array[indices.offset:indices.offset + nout] = best_i
+
     def adamw_step(self, param, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, weight_decay, step):
         """The op-by-op sequence of homura's optimizer on contiguous copies, written back in place."""
         def flat(t):

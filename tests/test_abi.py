@@ -26,6 +26,12 @@ def test_every_declared_symbol_is_exported():
         for name in names:
             assert hasattr(lib, name), f"{name} is declared in {header} but not exported"
             assert name in ffi.FUNCTIONS, f"{name} has no binding"
+    # the sharding header is served by two libraries: the NCCL entry points live in their own
+    shard = homura_b200.load_shard()
+    for name in declared(ROOT / "include" / "homura_cuda_shard.h"):
+        home = shard if name.startswith("hmc_comm_") else lib
+        assert hasattr(home, name), f"{name} is declared in homura_cuda_shard.h but not exported"
+        assert name in ffi.FUNCTIONS, f"{name} has no binding"
 
 
 def test_binding_is_up_to_date():

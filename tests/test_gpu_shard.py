@@ -1,0 +1,104 @@
+"""The sharded reductions on real GPUs: one process per GPU, NCCL all-gather of the partials, rank-ordered
+combine. Needs at least two GPUs (skipped otherwise); every rank must hold the same bits, which must match the
+CPU checker's result on the whole tensor (bit for bit for integers, extremes and indices; within 2 ulp for the
+f64-accumulated float sums)."""
+import ctypes
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = pytest.mark.gpu
+
+
+def _device_count():
+    import homura_b200
+    n = ctypes.c_int32()
+    homura_b200.load().hmc_device_count(ctypes.byref(n))
+    return n.value
+
+
+def _worker(rank, world, unique_id, results):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        from frontend import T
+        from homura_b200 import ffi
+        from homura_b200.host import BF16, F32, I32, I64, CudaBackend
+        from homura_b200.shard import NcclComm, ShardedReducer, split_rows
+        from oracle_backend import OracleBackend
+        from values import assert_bitwise, assert_ulp, f64_to_storage
+
+        be = CudaBackend(rank)
+        comm = NcclComm(be, world, rank, unique_id)
+        oracle = OracleBackend()
+        rows, cols = 4099, 1030
+        blocks = split_rows(rows, world)
+        start, length = blocks[rank]
+        red = ShardedReducer(be, comm, [b[0] for b in blocks], rows)
+        rng = np.random.default_rng(11)
+        data = {F32: rng.standard_normal((rows, cols)).astype(np.float32),
+                BF16: f64_to_storage(rng.standard_normal((rows, cols)), BF16),
+                I32: rng.integers(-1000, 1001, size=(rows, cols), dtype=np.int32)}
+        data[F32][rows - 5, 5] = np.nan
+        data[F32][3, 7] = data[F32][rows - 3, 7] = 9.0
+        digest = []
+        for dt, full in data.items():
+            whole = T(oracle, oracle.upload(full, dt))
+            shard = be.upload(full[start:start + length], dt)
+            is_f = dt != I32
+            for mask, shape in (([True, False], (cols,)), ([True, True], ())):
+                dims = [d for d, m in enumerate(mask) if m]
+                ops = [("sum", ffi.HMC_REDUCE_SUM), ("max", ffi.HMC_REDUCE_MAX), ("min", ffi.HMC_REDUCE_MIN)]
+                if is_f:
+                    ops.append(("mean", ffi.HMC_REDUCE_MEAN))
+                for name, op in ops:
+                    out_dt = dt if (is_f or name in ("max", "min")) else I64
+                    out = be.empty(shape, out_dt)
+                    red.reduce(op, out, shard, mask)
+                    want, got = whole._red(name, dims).raw(), be.download(out)
+                    if is_f and name in ("sum", "mean"):
+                        assert_ulp(got, want, dt, 2, f"{name} {mask}")
+                    else:
+                        assert_bitwise(got, want, out_dt, f"{name} {mask}")
+                    digest.append(got.tobytes())
+            for is_max in (True, False):
+                v, i = be.empty((cols,), dt), be.empty((cols,), I64)
+                red.arg_reduce(v, i, shard, is_max)
+                wv, wi = whole.max_dim(0) if is_max else whole.min_dim(0)
+                assert_bitwise(be.download(i), wi.raw(), I64, "global indices")
+                assert_bitwise(be.download(v), wv.raw(), dt, "values")
+        be.synchronize()
+        comm.close()
+        be.close()
+        import hashlib
+        results[rank] = "ok " + hashlib.sha256(b"".join(digest)).hexdigest()
+    except BaseException as e:
+        import traceback
+        results[rank] = "".join(traceback.format_exception(e))
+
+
+def test_sharded_reductions_over_nccl():
+    n = _device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    world = min(n, 4)
+    import multiprocessing as mp
+    from homura_b200.shard import NcclComm
+    uid = NcclComm.unique_id()
+    ctx = mp.get_context("spawn")
+    manager = ctx.Manager()
+    results = manager.dict()
+    procs = [ctx.Process(target=_worker, args=(r, world, uid, results)) for r in range(world)]
+    [p.start() for p in procs]
+    [p.join(timeout=300) for p in procs]
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    got = dict(results)
+    assert len(got) == world and all(v.startswith("ok ") for v in got.values()), "\n".join(str(v) for v in got.values())
+    assert len(set(got.values())) == 1, "ranks disagree on the bits of the results"

@@ -1,0 +1,103 @@
+"""The multi-rank path on the CPU: two gloo ranks run the sharded-reduction orchestration
+(homura_b200/shard.py: split, local partials, all-gather, rank-ordered combine) with host stand-ins for the
+device steps, and every rank must reproduce the single-rank result: bit for bit for integers, extremes and
+indices, within 2 ulp for f64-accumulated float sums."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+class GlooComm:
+    def __init__(self, ranks, rank):
+        self.ranks, self.rank = ranks, rank
+
+    def allgather(self, send, recv, nbytes):
+        mine = torch.from_numpy(send.array.reshape(-1).view(np.uint8)[:nbytes].copy())
+        parts = [torch.empty(nbytes, dtype=torch.uint8) for _ in range(self.ranks)]
+        dist.all_gather(parts, mine)
+        for r, p in enumerate(parts):
+            recv.array.reshape(-1).view(np.uint8)[r * nbytes:(r + 1) * nbytes] = p.numpy()
+
+
+def _worker(rank, world, port, results):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from frontend import T
+        from homura_b200 import ffi
+        from homura_b200.host import F32, BF16, I32, I64
+        from homura_b200.shard import ShardedReducer, split_rows
+        from oracle_backend import OracleBackend
+        from values import assert_bitwise, assert_ulp, f64_to_storage, values
+
+        be = OracleBackend()
+        rows, cols = 37, 53  # 37 rows over 2 ranks: 19 + 18
+        blocks = split_rows(rows, world)
+        start, length = blocks[rank]
+        red = ShardedReducer(be, GlooComm(world, rank), [b[0] for b in blocks], rows)
+        rng = np.random.default_rng(7)
+        data = {F32: rng.standard_normal((rows, cols)).astype(np.float32),
+                BF16: f64_to_storage(rng.standard_normal((rows, cols)), BF16),
+                I32: rng.integers(-1000, 1001, size=(rows, cols), dtype=np.int32)}
+        data[F32][20, 5] = np.nan          # a NaN in the second shard only
+        data[F32][3, 7] = data[F32][30, 7] = 9.0  # equal maxima in both shards
+        for dt, full in data.items():
+            whole = T(be, be.upload(full, dt))
+            shard = be.upload(full[start:start + length], dt)
+            is_f = dt != I32
+            for mask, shape in (([True, False], (cols,)), ([True, True], ())):
+                dims = [d for d, m in enumerate(mask) if m]
+                ops = [("sum", ffi.HMC_REDUCE_SUM), ("max", ffi.HMC_REDUCE_MAX), ("min", ffi.HMC_REDUCE_MIN)]
+                if is_f:
+                    ops.append(("mean", ffi.HMC_REDUCE_MEAN))
+                for name, op in ops:
+                    out_dt = dt if (is_f or name in ("max", "min")) else I64
+                    out = be.empty(shape, out_dt)
+                    red.reduce(op, out, shard, mask)
+                    want = whole._red(name, dims).raw()
+                    got = be.download(out)
+                    if is_f and name in ("sum", "mean"):
+                        assert_ulp(got, want, dt, 2, f"{name} {mask}")
+                    else:
+                        assert_bitwise(got, want, out_dt, f"{name} {mask}")
+            for is_max in (True, False):
+                v, i = be.empty((cols,), dt), be.empty((cols,), I64)
+                red.arg_reduce(v, i, shard, is_max)
+                wv, wi = whole.max_dim(0) if is_max else whole.min_dim(0)
+                assert_bitwise(be.download(i), wi.raw(), I64, "global indices")
+                assert_bitwise(be.download(v), wv.raw(), dt, "values")
+        results[rank] = "ok"
+    except BaseException as e:  # report to the parent instead of dying silently
+        import traceback
+        results[rank] = "".join(traceback.format_exception(e))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_single_rank_results():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
+    assert dict(results) == {0: "ok", 1: "ok"}, "\n".join(str(v) for v in results.values())
+
+
+def test_split_rows():
+    from homura_b200.shard import split_rows
+    assert split_rows(10, 4) == [(0, 3), (3, 3), (6, 3), (9, 1)]
+    assert split_rows(8, 8) == [(i, 1) for i in range(8)]
+    assert split_rows(3, 4) == [(0, 1), (1, 1), (2, 1), (3, 0)]
+    assert split_rows(1 << 32, 8)[7] == (7 << 29, 1 << 29)
