@@ -257,9 +257,9 @@ class C5Workload:
 
     name = "c5_flat_elementwise_adamw"
 
-    def __init__(self, be, seed: int = 0, log2n: int = 29):
+    def __init__(self, be, seed: int = 0, log2n: int = 29, reducer=None):
         from homura_b200.host import F32, F64
-        self.be = be
+        self.be, self.reducer = be, reducer
         n = 1 << log2n
         base = [be.upload(philox_normal(1 << 22, 41 + seed + j), F32) for j in range(3)]
         self.a, self.b, self.c = (be.empty((n,), F32) for _ in range(3))
@@ -286,14 +286,20 @@ class C5Workload:
             self.step_no += 1
             be.adamw_step(self.p, self.g, self.m, self.v, lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01,
                           step=float(self.step_no))
+        # with several ranks the tensors are shards of a global one: the three reductions fold the sharded
+        # dimension, so they gather the ranks' partials over NCCL and combine them in rank order
+        if self.reducer is not None:
+            reduce = lambda op: self.reducer.reduce(op, self.s, self.t, [True])
+        else:
+            reduce = lambda op: be.reduce(op, self.s, self.t, [True])
         return [
             ("mul", lambda: be.binary(ffi.HMC_BINARY_MUL, self.t, self.a, self.b)),
             ("add", lambda: be.binary(ffi.HMC_BINARY_ADD, self.t, self.t, self.c)),
-            ("sum", lambda: be.reduce(ffi.HMC_REDUCE_SUM, self.s, self.t, [True])),
-            ("max", lambda: be.reduce(ffi.HMC_REDUCE_MAX, self.s, self.t, [True])),
+            ("sum", lambda: reduce(ffi.HMC_REDUCE_SUM)),
+            ("max", lambda: reduce(ffi.HMC_REDUCE_MAX)),
             ("adamw", adamw),
             ("grad_sq", lambda: be.binary(ffi.HMC_BINARY_MUL, self.t, self.g, self.g)),
-            ("grad_sum", lambda: be.reduce(ffi.HMC_REDUCE_SUM, self.s, self.t, [True])),
+            ("grad_sum", lambda: reduce(ffi.HMC_REDUCE_SUM)),
         ]
 
     def step(self):
@@ -408,6 +414,14 @@ def main() -> None:
     if args.workload == "c2":
         w = Workload(be, seed=rank)
         workload_name, step_bytes = WORKLOAD, STEP_BYTES
+    elif args.workload == "c5" and world > 1:
+        from homura_b200.shard import NcclComm, ShardedReducer
+        box = [NcclComm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        comm = NcclComm(be, world, rank, box[0])
+        n_local = 1 << 29
+        w = C5Workload(be, seed=rank, log2n=29, reducer=ShardedReducer(be, comm, [r * n_local for r in range(world)], world * n_local))
+        workload_name, step_bytes = w.name + "_sharded", sum(w.op_bytes.values())
     else:
         w = {"c3": C3Workload, "c4": C4Workload, "c5": C5Workload}[args.workload](be, seed=rank)
         workload_name, step_bytes = w.name, sum(w.op_bytes.values())
