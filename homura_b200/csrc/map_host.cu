@@ -1,6 +1,7 @@
 // Host side of the elementwise engine: validation of descriptions and the launch geometry.
 #include "map.cuh"
 
+#include <algorithm>
 #include <utility>
 
 namespace hmc {
@@ -127,6 +128,42 @@ void build_map_args(MapArgs &a, const hmc_tensor_desc *out, const MapOperand *in
     int64_t rpb = kThreads / tpr;
     a.items = ceil_div(a.rows, rpb) * a.segs;
     a.rows_fit32 = a.rows < (int64_t{1} << 31) ? 1 : 0;
+    // Division of an item index below 2^31 by segs as a multiplication: with l = ceil(log2(segs)) and
+    // M = floor(2^(31+l) / segs) + 1, floor(n / segs) = (n * M) >> (31 + l) for every n < 2^31.
+    if (a.segs > 1 && a.items < (int64_t{1} << 31)) {
+        int l = 0;
+        while ((int64_t{1} << l) < a.segs) ++l;
+        a.segs_shift = 31 + l;
+        a.segs_magic = static_cast<uint64_t>((static_cast<unsigned __int128>(1) << a.segs_shift) / static_cast<uint64_t>(a.segs)) + 1;
+    }
+}
+
+bool build_lean_args(LeanArgs &lean, const MapArgs &a, const int *elem_size, int vec) {
+    if (a.ndim > 2 || a.n0 >= (int64_t{1} << 31)) return false;
+    // short rows leave most of a block idle here; the general kernel packs several rows into a block
+    if (a.rows > 1 && a.n0 < 64 * static_cast<int64_t>(vec)) return false;
+    const int last = a.ndim - 1;
+    lean = LeanArgs{};
+    lean.n0 = static_cast<uint32_t>(a.n0);
+    lean.rows = a.rows;
+    lean.constant_mask = a.constant_mask;
+    for (int k = 0; k < kOperands; ++k) {
+        if (elem_size[k] == 0) continue;  // an absent input
+        lean.constant[k] = a.constant[k];
+        if (a.constant_mask & (1u << k)) continue;
+        const int64_t inner = a.strides[k][last];
+        const int64_t row_stride = a.ndim == 2 ? a.strides[k][0] : 0;
+        if (inner != 1 && !(inner == 0 && k > 0)) return false;
+        const int64_t vec_bytes = std::min<int64_t>(16, static_cast<int64_t>(vec) * elem_size[k]);
+        if (inner == 1) {
+            if (reinterpret_cast<uintptr_t>(a.base[k]) % vec_bytes != 0) return false;
+            if (a.rows > 1 && (row_stride * elem_size[k]) % vec_bytes != 0) return false;
+        }
+        lean.base[k] = a.base[k];
+        lean.row_stride[k] = row_stride;
+        lean.inner[k] = inner == 1 ? 1u : 0u;
+    }
+    return true;
 }
 
 }  // namespace hmc

@@ -58,7 +58,10 @@ __global__ void __launch_bounds__(kThreads) adamw_kernel(const __grid_constant__
         int64_t rg, seg;
         if (a.rows == 1) { rg = 0; seg = item; }
         else if (a.segs == 1) { rg = item; seg = 0; }
-        else { rg = item / a.segs; seg = item - rg * a.segs; }
+        else if (a.segs_shift != 0) {
+            rg = static_cast<int64_t>((static_cast<uint64_t>(item) * a.segs_magic) >> a.segs_shift);
+            seg = item - rg * a.segs;
+        } else { rg = item / a.segs; seg = item - rg * a.segs; }
         const int64_t row = rg * rpb + rib;
         if (row >= a.rows) continue;
         int64_t off[kOperands];

@@ -127,6 +127,16 @@ __device__ __forceinline__ typename Op::Acc group_combine(const Op &op, typename
     }
 }
 
+// acc folded with element x (index j of output o), where j is larger than every index already in acc: what a
+// lane does element by element. Ops may give a cheaper form of it than combine(acc, load(x)).
+template <class Op, class = void> struct has_step : std::false_type {};
+template <class Op> struct has_step<Op, std::void_t<decltype(&Op::step)>> : std::true_type {};
+template <class Op>
+__device__ __forceinline__ typename Op::Acc fold_step(const Op &op, typename Op::Acc acc, typename Op::T x, int64_t o, int64_t j) {
+    if constexpr (has_step<Op>::value) return op.step(acc, x, j);
+    else return op.combine(acc, op.load(x, o, j));
+}
+
 template <class T, int VEC>
 struct alignas(sizeof(T) * VEC >= 16 ? 16 : sizeof(T) * VEC) RVec {
     T v[VEC];
@@ -158,7 +168,7 @@ __device__ __forceinline__ typename Op::Acc fold_range(const Op &op, const Reduc
             if (v < v_end && v * VEC < lo) {
                 for (int e = 0; e < VEC; ++e) {
                     const int64_t i = v * VEC + e;
-                    if (i >= lo && i < hi) acc = op.combine(acc, op.load(p[i], o, first + i));
+                    if (i >= lo && i < hi) acc = fold_step(op, acc, p[i], o, first + i);
                 }
                 v += G;
             }
@@ -170,7 +180,7 @@ __device__ __forceinline__ typename Op::Acc fold_range(const Op &op, const Reduc
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) acc = op.combine(acc, op.load(x[u].v[e], o, first + (v + u * G) * VEC + e));
+                    for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x[u].v[e], o, first + (v + u * G) * VEC + e);
                 }
                 v += UNR * G;
             }
@@ -179,11 +189,11 @@ __device__ __forceinline__ typename Op::Acc fold_range(const Op &op, const Reduc
                 if (i0 + VEC <= hi) {
                     RVec<T, VEC> x = *reinterpret_cast<const RVec<T, VEC> *>(p + i0);
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) acc = op.combine(acc, op.load(x.v[e], o, first + i0 + e));
+                    for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x.v[e], o, first + i0 + e);
                 } else {
                     for (int e = 0; e < VEC; ++e) {
                         const int64_t i = i0 + e;
-                        if (i < hi) acc = op.combine(acc, op.load(p[i], o, first + i));
+                        if (i < hi) acc = fold_step(op, acc, p[i], o, first + i);
                     }
                 }
             }
@@ -193,7 +203,7 @@ __device__ __forceinline__ typename Op::Acc fold_range(const Op &op, const Reduc
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) {
                     const int64_t i = i0 + e;
-                    if (i >= lo && i < hi) acc = op.combine(acc, op.load(p[i * step], o, first + i));
+                    if (i >= lo && i < hi) acc = fold_step(op, acc, p[i * step], o, first + i);
                 }
             }
         }
@@ -275,7 +285,7 @@ __global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_
                 for (int u = 0; u < UNR; ++u) {
 #pragma unroll
                     for (int e = 0; e < VC; ++e) {
-                        if (whole || c0 + e < p.ncols) acc[e] = op.combine(acc[e], op.load(x[u].v[e], o0 + e, j + u * 8));
+                        if (whole || c0 + e < p.ncols) acc[e] = fold_step(op, acc[e], x[u].v[e], o0 + e, j + u * 8);
                     }
                 }
             }
@@ -283,7 +293,7 @@ __global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_
                 const T *q = src + red_off(j);
 #pragma unroll
                 for (int e = 0; e < VC; ++e) {
-                    if (c0 + e < p.ncols) acc[e] = op.combine(acc[e], op.load(q[e], o0 + e, j));
+                    if (c0 + e < p.ncols) acc[e] = fold_step(op, acc[e], q[e], o0 + e, j);
                 }
             }
         }
@@ -417,6 +427,16 @@ struct Extreme {
     using Acc = Best<TT>;
     __device__ __forceinline__ Acc init() const { return Acc{TT{}, -1}; }
     __device__ __forceinline__ Acc load(T x, int64_t, int64_t j) const { return Acc{x, j}; }
+    // x comes after everything in acc: it wins only by being the first NaN or strictly better
+    // (`replaces`, src/backend/cpu/reduce.rs:75-86).
+    __device__ __forceinline__ Acc step(Acc acc, T x, int64_t j) const {
+        const auto kx = order_key(x), ka = order_key(acc.v);
+        bool take;
+        if constexpr (Tr<TT>::kind == kFloat) take = (ka == ka) && (kx != kx || (MAX ? kx > ka : kx < ka));
+        else take = MAX ? kx > ka : kx < ka;
+        take = take || acc.i < 0;
+        return take ? Acc{x, j} : acc;
+    }
     __device__ __forceinline__ Acc combine(Acc a, Acc b) const {
         if (a.i < 0) return b;
         if (b.i < 0) return a;

@@ -214,6 +214,30 @@ def test_where_and_masked_fill(oracle, cuda, dtype):
             assert_bitwise(where(gc, w, w * 2).raw(), where(oc, w, w * 2).raw(), where(oc, w, w * 2).dtype, "where scalars")
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16, U8, F64], ids=["f32", "bf16", "u8", "f64"])
+def test_long_rows_are_cut_into_segments(oracle, cuda, dtype):
+    """Several rows, each longer than one block's reach (row groups x segments), with broadcast operands and a
+    ragged tail; and a transposed operand whose tiles are not whole."""
+    rows, cols = 5, 70001
+    (oa, ga), (ob, gb) = both(oracle, cuda, values(dtype, rows * cols, 95), dtype, (rows, cols)), \
+        both(oracle, cuda, values(dtype, rows * cols, 96), dtype, (rows, cols))
+    for op in ("add", "maximum"):
+        f = lambda a, b: getattr(a, op)(b)
+        assert_bitwise(f(ga, gb).raw(), f(oa, ob).raw(), dtype, f"{op} [5, 70001]")
+        row = lambda a: getattr(a, op)(a.view(lambda d: d.narrow(0, 2, 1).expand(rows, cols)))
+        col = lambda a: getattr(a, op)(a.view(lambda d: d.narrow(1, 11, 1).expand(rows, cols)))
+        assert_bitwise(row(ga).raw(), row(oa).raw(), dtype, f"{op} row broadcast, long rows")
+        assert_bitwise(col(ga).raw(), col(oa).raw(), dtype, f"{op} column broadcast, long rows")
+        off = lambda a, b: getattr(a.view(lambda d: d.narrow(1, 3, 60000)), op)(b.view(lambda d: d.narrow(1, 1, 60000)))
+        assert_bitwise(off(ga, gb).raw(), off(oa, ob).raw(), dtype, f"{op} misaligned windows")
+    (ot, gt) = both(oracle, cuda, values(dtype, 333 * 517, 97), dtype, (333, 517))
+    (ou, gu) = both(oracle, cuda, values(dtype, 333 * 517, 98), dtype, (517, 333))
+    t = lambda a, b: a.add(b.view(lambda d: d.t()))
+    assert_bitwise(t(gt, gu).raw(), t(ot, ou).raw(), dtype, "transposed operand, ragged tiles")
+    c = lambda a: a.view(lambda d: d.t()).contiguous()
+    assert_bitwise(c(gt).raw(), c(ot).raw(), dtype, "contiguous() of a transposed view")
+
+
 def test_promoting_add_matches_cast_then_add(oracle, cuda):
     """bf16 + f32 -> f32 in one kernel has the bits of homura's cast kernels followed by add."""
     x = values(BF16, 700 * 300, 61).reshape(700, 300)
