@@ -44,6 +44,11 @@ METRIC = "hbm_gbs_algorithmic"
 UNIT = "GB/s"
 WORKLOAD = "c2_elementwise_broadcast_bf16_8192x8192"
 L2_BYTES = 126 << 20
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel of the c2 step, from one `ncu --set full`
+# capture on B200 (profiles/c2_step_elementwise_kernels.md). Writes are below the algorithmic output where the
+# tail of the output still sits in L2 when the capture ends.
+NCU_TRAFFIC_BYTES = {"silu": 222.3e6, "mul_scale": 209.3e6, "add_bias": 344.8e6, "silu_t": 220.0e6, "mul_scale_t": 209.6e6,
+                     "add_bias_t": 345.9e6, "cast": 344.4e6}
 
 
 def philox_normal(n: int, seed: int) -> np.ndarray:
@@ -485,7 +490,8 @@ def main() -> None:
     peak, peak_kind = peaks()
     achieved = w.op_bytes[dominant] / (per_op[dominant] * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": UNIT,
-                "frac": achieved / peak, "traffic": None, "share_of_step": per_op[dominant] / total_op_ms,
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(dominant) if args.workload == "c2" else None,
+                "algorithmic_bytes": w.op_bytes[dominant], "share_of_step": per_op[dominant] / total_op_ms,
                 "per_kernel_gbs": {k: w.op_bytes[k] / (v * 1e-3) / 1e9 for k, v in per_op.items()},
                 "per_kernel_ms": per_op}
 
