@@ -46,6 +46,9 @@ struct MapArgs {
     // The tiled kernel (operands read against the grain through shared memory):
     uint32_t tile_mask;     // bit k: input k has unit stride along the second-to-last dimension
     int64_t tiles_a, tiles_b, ntiles;
+    int32_t tile_stages;              // shared-memory stages of the tile ring
+    uint32_t stage_bytes;             // bytes of one stage: the tiles of the transposed inputs
+    uint32_t tile_off[kOperands];     // where input k's tile lies within a stage
     char *base[kOperands];  // data + offset, as bytes
     int64_t sizes[HMC_MAX_DIMS];
     int64_t strides[kOperands][HMC_MAX_DIMS];
@@ -465,189 +468,329 @@ bool build_lean_args(LeanArgs &lean, const MapArgs &a, const int *elem_size, int
 
 // ---- the tiled kernel ----
 // For operands whose unit stride runs along the second-to-last dimension A while the output's runs
-// along the last dimension B (a transposed view). Work is cut into 64 x 64 tiles. A tile of each such
-// operand is read with 16-byte loads along A (its grain), parked in shared memory as rows of A with
-// a 16-byte padded pitch, and read back along B: a thread produces one 32-byte sector of the output
-// (EB consecutive elements along B at one A), the lanes of a warp sit on consecutive A, so every
-// shared-memory gather is conflict free and every global access moves whole sectors. Tiles on the
-// boundary, and operands that are not 16-byte aligned, take an element-wise path through the same
-// shared-memory tile.
-constexpr int kTile = 64;
+// along the last dimension B (a transposed view). Work is cut into square tiles of (A, B): 128 x 128
+// elements when every operand has 1- or 2-byte elements, 64 x 64 otherwise, so that the runs a tile reads
+// and writes are 128 to 512 bytes long and the bookkeeping per tile is spread over at least four 16-byte
+// outputs per thread. A tile of a transposed operand comes into shared memory as rows along A (16-byte
+// asynchronous copies straight from global to shared memory), and is read back against the grain: a thread
+// produces one 16-byte piece of an output row (NB consecutive B at GA consecutive A), eight neighbouring
+// lanes produce 128 consecutive bytes of that row, so global loads and stores both move whole lines. The
+// 16-byte chunks of a shared-memory row are permuted by the row's output-chunk number (XOR), which makes
+// the against-the-grain reads conflict free when input and output elements have the same size. A block
+// keeps the copies of its next tiles in flight in a ring of stages while it computes the current one.
+// Tiles on the boundary, and operands that are not 16-byte aligned, are filled element by element into the
+// same layout.
+#ifndef HMC_TILE_MIN_BLOCKS
+#define HMC_TILE_MIN_BLOCKS 3
+#endif
+#ifndef HMC_TILE_RING_KB
+#define HMC_TILE_RING_KB 40
+#endif
+#ifndef HMC_TILE_A_FASTEST
+#define HMC_TILE_A_FASTEST 0
+#endif
+constexpr int kTileStagesMax = 4;
+constexpr int kTileKnownDevices = 64;                        // GPUs whose launch limits are remembered
+constexpr size_t kTileRingBytes = HMC_TILE_RING_KB * 1024;   // shared memory a block's ring aims for
 
-template <class T> constexpr int tile_pitch() {  // elements per shared-memory row (one B index, 64 A's)
-    if constexpr (std::is_same_v<T, Unused>) return 0;
-    else return kTile + 16 / static_cast<int>(sizeof(T));
+// The tile edge, in elements, of a functor's launches.
+template <class F> constexpr int tile_dim() {
+    constexpr int so = sizeof(typename F::Out);
+    constexpr int sa = size_or_zero<typename F::A>(), sb = size_or_zero<typename F::B>(), sc = size_or_zero<typename F::C>();
+    constexpr int m1 = so > sa ? so : sa, m2 = sb > sc ? sb : sc;
+    return (m1 > m2 ? m1 : m2) <= 2 ? 128 : 64;
 }
-template <class T> constexpr size_t tile_bytes() {
+template <class T, int TD> constexpr size_t tile_bytes() {
     if constexpr (std::is_same_v<T, Unused>) return 0;
-    else return static_cast<size_t>(kTile) * tile_pitch<T>() * sizeof(T);
+    else return static_cast<size_t>(TD) * TD * sizeof(T);
 }
-template <class TO> constexpr int tile_eb() {  // output elements per thread along B: a 32-byte sector
-    return sizeof(TO) >= 8 ? 4 : (sizeof(TO) == 4 ? 8 : 16);
+template <class TO> constexpr int tile_nb() { return 16 / static_cast<int>(sizeof(TO)); }  // B's per thread: 16 bytes of output
+template <class TO> constexpr int tile_ga() { return sizeof(TO) <= 2 ? 2 : 1; }            // A's per thread
+
+// Byte offset of element (row r along B, a along A) of a tile whose rows are cut into tasks of NB rows.
+template <class T, int NB, int TD>
+__device__ __forceinline__ uint32_t tile_offset(int r, int a) {
+    constexpr int E = sizeof(T);
+    constexpr int kChunks = TD * E / 16;
+    constexpr int kMask = (kChunks < 8 ? kChunks : 8) - 1;
+    const uint32_t byte = static_cast<uint32_t>(a) * E;
+    return static_cast<uint32_t>(r) * (TD * E) + (((byte >> 4) ^ (static_cast<uint32_t>(r / NB) & kMask)) << 4) + (byte & 15u);
 }
 
-// Fills tile[b][a] (b, a in 0..63) with operand k's elements (a0 + a, b0 + b); `p` points at (a0, b0).
-template <class T>
-__device__ __forceinline__ void tile_fill(T *tile, const T *p, int64_t sb, bool vector_ok, int na, int nb) {
+__device__ __forceinline__ void async_copy_16(void *shared_dst, const void *global_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(shared_dst))),
+                 "l"(global_src)
+                 : "memory");
+}
+__device__ __forceinline__ void async_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most `pending` of this thread's committed groups are still in flight.
+__device__ __forceinline__ void async_copy_wait(int pending) {
+    switch (pending) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    }
+}
+
+// Starts the copies of a whole, aligned tile: row r of the tile is the TD elements at p + r * sb.
+template <class T, int NB, int TD>
+__device__ __forceinline__ void tile_fetch(unsigned char *tile, const T *p, int64_t sb) {
     if constexpr (!std::is_same_v<T, Unused>) {
-        constexpr int P = tile_pitch<T>();
-        constexpr int VA = 16 / sizeof(T);
-        constexpr int CH = kTile / VA;  // 16-byte chunks per row
-        if (vector_ok) {
-            constexpr int N = kTile * CH / kThreads;
-            Pack<T, VA> v[N];
+        constexpr int E = sizeof(T);
+        constexpr int CH = TD * E / 16;  // 16-byte chunks per row
+        constexpr int N = (TD * CH + kThreads - 1) / kThreads;
+        constexpr int kMask = (CH < 8 ? CH : 8) - 1;
+        const char *src = reinterpret_cast<const char *>(p);
+        const int64_t row_bytes = sb * E;
 #pragma unroll
-            for (int i = 0; i < N; ++i) {
-                const int idx = threadIdx.x + kThreads * i;
-                const int b = idx / CH, ac = idx % CH;
-                v[i] = *reinterpret_cast<const Pack<T, VA> *>(p + b * sb + ac * VA);
-            }
-#pragma unroll
-            for (int i = 0; i < N; ++i) {
-                const int idx = threadIdx.x + kThreads * i;
-                const int b = idx / CH, ac = idx % CH;
-                *reinterpret_cast<Pack<T, VA> *>(tile + b * P + ac * VA) = v[i];
-            }
-        } else {
-            const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
-            for (int b = ty; b < nb; b += kThreads / kTile) {
-                if (tx < na) tile[b * P + tx] = p[b * sb + tx];
-            }
+        for (int i = 0; i < N; ++i) {
+            const int x = threadIdx.x + kThreads * i;
+            const int r = x / CH, c = x % CH;
+            if (TD * CH % kThreads == 0 || r < TD)
+                async_copy_16(tile + r * (TD * E) + ((c ^ ((r / NB) & kMask)) << 4), src + r * row_bytes + c * 16);
         }
     }
 }
 
-// EB elements of input k for output position (a, b .. b + EB): from the tile, a constant, or memory.
-template <class T, int EB>
-__device__ __forceinline__ void tile_gather(Pack<T, EB> &dst, const T *tile, bool tiled, const MapArgs &arg, int k,
-                                            const T *p, int64_t sa, int64_t sb, int a, int b, int nvalid) {
+// The same tile element by element, for tiles on the boundary and rows that are not 16-byte aligned.
+template <class T, int NB, int TD>
+__device__ __forceinline__ void tile_fill(unsigned char *tile, const T *p, int64_t sb, int na, int nb) {
     if constexpr (!std::is_same_v<T, Unused>) {
-        constexpr int P = tile_pitch<T>();
+        const int tx = threadIdx.x % TD;
+        for (int r = threadIdx.x / TD; r < nb; r += kThreads / TD) {
+            if (tx < na) *reinterpret_cast<T *>(tile + tile_offset<T, NB, TD>(r, tx)) = p[r * sb + tx];
+        }
+    }
+}
+
+// Input k at output positions (a0 + g, b0 + j), g < GA, j < NB, into dst.v[g * NB + j]: from the tile, a
+// constant, or memory.
+template <class T, int GA, int NB, int TD>
+__device__ __forceinline__ void tile_gather(Pack<T, GA * NB> &dst, const unsigned char *tile, bool tiled, const MapArgs &arg, int k,
+                                            const T *p, int64_t sa, int64_t sb, int a0, int b0, int na, int nvalid) {
+    if constexpr (!std::is_same_v<T, Unused>) {
         if (tiled) {
 #pragma unroll
-            for (int j = 0; j < EB; ++j) dst.v[j] = tile[(b + j) * P + a];
+            for (int j = 0; j < NB; ++j) {
+                const Pack<T, GA> w = *reinterpret_cast<const Pack<T, GA> *>(tile + tile_offset<T, NB, TD>(b0 + j, a0));
+#pragma unroll
+                for (int g = 0; g < GA; ++g) dst.v[g * NB + j] = w.v[g];
+            }
         } else if (arg.constant_mask & (1u << k)) {
             T c;
             uint64_t bits = arg.constant[k];
             memcpy(&c, &bits, sizeof(T));
 #pragma unroll
-            for (int j = 0; j < EB; ++j) dst.v[j] = c;
+            for (int j = 0; j < GA * NB; ++j) dst.v[j] = c;
         } else {
-            const T *q = p + a * sa + b * sb;
-            if (sb == 0) {
-                const T c = *q;
 #pragma unroll
-                for (int j = 0; j < EB; ++j) dst.v[j] = c;
-            } else if (sb == 1 && nvalid == EB && (reinterpret_cast<uintptr_t>(q) & 15) == 0) {
-                constexpr int V = 16 / sizeof(T);
+            for (int g = 0; g < GA; ++g) {
+                if (a0 + g >= na) continue;
+                const T *q = p + (a0 + g) * sa + b0 * sb;
+                constexpr int V = NB * sizeof(T) >= 16 ? 16 / static_cast<int>(sizeof(T)) : NB;  // elements per vector load
+                if (sb == 0) {
+                    const T c = *q;
 #pragma unroll
-                for (int j = 0; j < EB; j += V) {
-                    const Pack<T, V> x = *reinterpret_cast<const Pack<T, V> *>(q + j);
+                    for (int j = 0; j < NB; ++j) dst.v[g * NB + j] = c;
+                } else if (sb == 1 && nvalid == NB && (reinterpret_cast<uintptr_t>(q) & (V * sizeof(T) - 1)) == 0) {
 #pragma unroll
-                    for (int e = 0; e < V; ++e) dst.v[j + e] = x.v[e];
+                    for (int j = 0; j < NB; j += V) {
+                        const Pack<T, V> x = *reinterpret_cast<const Pack<T, V> *>(q + j);
+#pragma unroll
+                        for (int e = 0; e < V; ++e) dst.v[g * NB + j + e] = x.v[e];
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NB; ++j)
+                        if (j < nvalid) dst.v[g * NB + j] = q[j * sb];
                 }
-            } else {
-#pragma unroll
-                for (int j = 0; j < EB; ++j)
-                    if (j < nvalid) dst.v[j] = q[j * sb];
             }
         }
     }
 }
 
+// A tile number as coordinates: the tile index along the dimension that neighbouring tile numbers walk
+// first, along the other one, and the index over the outer dimensions. A block's tile numbers advance by
+// the grid size; the coordinates follow by carries instead of divisions.
+struct TileCursor {
+    int64_t jf, js, outer;
+};
+__device__ __forceinline__ TileCursor tile_cursor(int64_t t, int64_t fast, int64_t slow) {
+    TileCursor c;
+    if (t < (int64_t{1} << 31) && fast < (int64_t{1} << 31) && slow < (int64_t{1} << 31)) {
+        const uint32_t t32 = static_cast<uint32_t>(t), nf = static_cast<uint32_t>(fast), ns = static_cast<uint32_t>(slow);
+        const uint32_t t2 = t32 / nf, o = t2 / ns;
+        c.jf = t32 - t2 * nf;
+        c.js = t2 - o * ns;
+        c.outer = o;
+    } else {
+        c.jf = t % fast;
+        const int64_t t2 = t / fast;
+        c.js = t2 % slow;
+        c.outer = t2 / slow;
+    }
+    return c;
+}
+__device__ __forceinline__ void tile_advance(TileCursor &c, const TileCursor &step, int64_t fast, int64_t slow) {
+    c.jf += step.jf;
+    const int64_t c1 = c.jf >= fast;
+    c.jf -= c1 ? fast : 0;
+    c.js += step.js + c1;
+    const int64_t c2 = c.js >= slow;
+    c.js -= c2 ? slow : 0;
+    c.outer += step.outer + c2;
+}
+
+// Where a tile lies: pointers at its corner, its extent, and whether its transposed operands can all be
+// fetched by 16-byte asynchronous copies.
 template <class F>
-__global__ void __launch_bounds__(kThreads) map_tile_kernel(const __grid_constant__ MapArgs a, const F f) {
+struct TileGeom {
+    typename F::Out *po;
+    const typename F::A *pa;
+    const typename F::B *pb;
+    const typename F::C *pc;
+    int na, nb;
+    bool whole, async;
+};
+
+template <class T>
+__device__ __forceinline__ bool tile_rows_aligned(const T *p, int64_t sb) {
+    if constexpr (std::is_same_v<T, Unused>) return true;
+    else return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (sb * static_cast<int64_t>(sizeof(T))) % 16 == 0;
+}
+
+template <class F>
+__device__ __forceinline__ TileGeom<F> tile_geometry(const MapArgs &a, const TileCursor &c) {
     using TO = typename F::Out;
     using TA = typename F::A;
     using TB = typename F::B;
     using TC = typename F::C;
-    constexpr int EB = tile_eb<TO>();
-    constexpr int BC = kTile / EB;                 // sectors per tile row
-    constexpr int ITEMS = kTile * BC / kThreads;   // sectors per thread
-    extern __shared__ __align__(16) unsigned char tile_memory[];
-    TA *tile_a = reinterpret_cast<TA *>(tile_memory);
-    TB *tile_b = reinterpret_cast<TB *>(tile_memory + tile_bytes<TA>());
-    TC *tile_c = reinterpret_cast<TC *>(tile_memory + tile_bytes<TA>() + tile_bytes<TB>());
+    constexpr int TD = tile_dim<F>();
+    const int da = a.ndim - 2, db = a.ndim - 1;
+    const int64_t jb = HMC_TILE_A_FASTEST ? c.js : c.jf, ja = HMC_TILE_A_FASTEST ? c.jf : c.js;
+    int64_t off[kOperands] = {0, 0, 0, 0};
+    int64_t outer = c.outer;
+    for (int d = da - 1; d >= 0; --d) {
+        const int64_t size = a.sizes[d];
+        const int64_t q = outer / size;
+        const int64_t i = outer - q * size;
+#pragma unroll
+        for (int k = 0; k < kOperands; ++k) off[k] += i * a.strides[k][d];
+        outer = q;
+    }
+    const int64_t a0 = ja * TD, b0 = jb * TD;
+    const int64_t size_a = a.sizes[da], size_b = a.sizes[db];
+    TileGeom<F> g;
+    g.na = static_cast<int>(size_a - a0 < TD ? size_a - a0 : TD);
+    g.nb = static_cast<int>(size_b - b0 < TD ? size_b - b0 : TD);
+    g.whole = g.na == TD && g.nb == TD;
+    g.po = operand_row<TO>(a, 0, off[0] + a0 * a.strides[0][da] + b0);
+    g.pa = operand_row<TA>(a, 1, off[1] + a0 * a.strides[1][da] + b0 * a.strides[1][db]);
+    g.pb = operand_row<TB>(a, 2, off[2] + a0 * a.strides[2][da] + b0 * a.strides[2][db]);
+    g.pc = operand_row<TC>(a, 3, off[3] + a0 * a.strides[3][da] + b0 * a.strides[3][db]);
+    g.async = g.whole && (!(a.tile_mask & 2u) || tile_rows_aligned<TA>(g.pa, a.strides[1][db])) &&
+              (!(a.tile_mask & 4u) || tile_rows_aligned<TB>(g.pb, a.strides[2][db])) &&
+              (!(a.tile_mask & 8u) || tile_rows_aligned<TC>(g.pc, a.strides[3][db]));
+    return g;
+}
+
+template <class F>
+__global__ void __launch_bounds__(kThreads, HMC_TILE_MIN_BLOCKS) map_tile_kernel(const __grid_constant__ MapArgs a, const F f) {
+    using TO = typename F::Out;
+    using TA = typename F::A;
+    using TB = typename F::B;
+    using TC = typename F::C;
+    constexpr int TD = tile_dim<F>();
+    constexpr int NB = tile_nb<TO>();
+    constexpr int GA = tile_ga<TO>();
+    constexpr int CB = TD / NB;                     // 16-byte pieces per output row of the tile
+    constexpr int LB = CB < 8 ? CB : 8;             // neighbouring lanes along B
+    constexpr int AG = TD / GA;                     // groups of A
+    constexpr int TASKS = AG * CB;
+    constexpr int ITEMS = (TASKS + kThreads - 1) / kThreads;
+    extern __shared__ __align__(128) unsigned char tile_memory[];
     const bool ta = a.tile_mask & 2u, tb = a.tile_mask & 4u, tc = a.tile_mask & 8u;
     const int da = a.ndim - 2, db = a.ndim - 1;
-    const int64_t size_a = a.sizes[da], size_b = a.sizes[db];
     const int64_t sao = a.strides[0][da];
     const int64_t saa = a.strides[1][da], sab = a.strides[1][db];
     const int64_t sba = a.strides[2][da], sbb = a.strides[2][db];
     const int64_t sca = a.strides[3][da], scb = a.strides[3][db];
-    // A fixed number of resident blocks walk the tiles (B fastest): measured faster on B200 than one block per
-    // tile, in either grid order.
+    const int stages = a.tile_stages;
+    // A fixed number of resident blocks walk the tiles: block i takes tiles i, i + grid, i + 2 grid, ...
+    const int64_t fast = HMC_TILE_A_FASTEST ? a.tiles_a : a.tiles_b, slow = HMC_TILE_A_FASTEST ? a.tiles_b : a.tiles_a;
+    const TileCursor step = tile_cursor(gridDim.x, fast, slow);
+    TileCursor ahead = tile_cursor(blockIdx.x, fast, slow);  // the tile whose copies are started next
+    TileCursor here = ahead;                                 // the tile computed next
+    int64_t t_ahead = blockIdx.x;
+    // Starts the copies of the tile `ahead` into stage s when the tile qualifies, and closes a group either
+    // way, so that every thread's groups count tiles.
+    auto prefetch = [&](int s) {
+        if (t_ahead < a.ntiles) {
+            const TileGeom<F> g = tile_geometry<F>(a, ahead);
+            if (g.async) {
+                unsigned char *stage = tile_memory + s * a.stage_bytes;
+                if (ta) tile_fetch<TA, NB, TD>(stage + a.tile_off[1], g.pa, sab);
+                if (tb) tile_fetch<TB, NB, TD>(stage + a.tile_off[2], g.pb, sbb);
+                if (tc) tile_fetch<TC, NB, TD>(stage + a.tile_off[3], g.pc, scb);
+            }
+        }
+        async_copy_commit();
+        t_ahead += gridDim.x;
+        tile_advance(ahead, step, fast, slow);
+    };
+    for (int s = 0; s < stages - 1; ++s) prefetch(s);
+    int s = 0;
     for (int64_t t = blockIdx.x; t < a.ntiles; t += gridDim.x) {
-        int64_t jb, ja, outer;
-        if (a.ntiles < (int64_t{1} << 31)) {
-            const uint32_t t32 = static_cast<uint32_t>(t), nb32 = static_cast<uint32_t>(a.tiles_b), na32 = static_cast<uint32_t>(a.tiles_a);
-            const uint32_t t2 = t32 / nb32;
-            jb = t32 - t2 * nb32;
-            const uint32_t o = t2 / na32;
-            ja = t2 - o * na32;
-            outer = o;
-        } else {
-            jb = t % a.tiles_b;
-            const int64_t t2 = t / a.tiles_b;
-            ja = t2 % a.tiles_a;
-            outer = t2 / a.tiles_a;
+        async_copy_wait(stages - 2);  // this thread's copies of tile t have landed
+        __syncthreads();              // and everybody's; and everybody is done with the stage refilled next
+        prefetch(s == 0 ? stages - 1 : s - 1);
+        const TileGeom<F> g = tile_geometry<F>(a, here);
+        tile_advance(here, step, fast, slow);
+        unsigned char *stage = tile_memory + s * a.stage_bytes;
+        const unsigned char *tile_a = stage + a.tile_off[1], *tile_b = stage + a.tile_off[2], *tile_c = stage + a.tile_off[3];
+        if (!g.async) {
+            if (ta) tile_fill<TA, NB, TD>(stage + a.tile_off[1], g.pa, sab, g.na, g.nb);
+            if (tb) tile_fill<TB, NB, TD>(stage + a.tile_off[2], g.pb, sbb, g.na, g.nb);
+            if (tc) tile_fill<TC, NB, TD>(stage + a.tile_off[3], g.pc, scb, g.na, g.nb);
+            __syncthreads();
         }
-        int64_t off[kOperands] = {0, 0, 0, 0};
-        for (int d = da - 1; d >= 0; --d) {
-            const int64_t size = a.sizes[d];
-            const int64_t q = outer / size;
-            const int64_t i = outer - q * size;
-#pragma unroll
-            for (int k = 0; k < kOperands; ++k) off[k] += i * a.strides[k][d];
-            outer = q;
-        }
-        const int64_t a0 = ja * kTile, b0 = jb * kTile;
-        const int na = static_cast<int>(size_a - a0 < kTile ? size_a - a0 : kTile);
-        const int nb = static_cast<int>(size_b - b0 < kTile ? size_b - b0 : kTile);
-        const bool whole = na == kTile && nb == kTile;
-        // pointers at the tile's corner (a0, b0)
-        TO *po = operand_row<TO>(a, 0, off[0] + a0 * sao + b0);
-        const TA *pa = operand_row<TA>(a, 1, off[1] + a0 * saa + b0 * sab);
-        const TB *pb = operand_row<TB>(a, 2, off[2] + a0 * sba + b0 * sbb);
-        const TC *pc = operand_row<TC>(a, 3, off[3] + a0 * sca + b0 * scb);
-        if (ta) tile_fill<TA>(tile_a, pa, sab, whole && vector_aligned<TA, 16 / size_or<TA>(1)>(pa) && (sab * size_or<TA>(1)) % 16 == 0, na, nb);
-        if (tb) tile_fill<TB>(tile_b, pb, sbb, whole && vector_aligned<TB, 16 / size_or<TB>(1)>(pb) && (sbb * size_or<TB>(1)) % 16 == 0, na, nb);
-        if (tc) tile_fill<TC>(tile_c, pc, scb, whole && vector_aligned<TC, 16 / size_or<TC>(1)>(pc) && (scb * size_or<TC>(1)) % 16 == 0, na, nb);
-        __syncthreads();
-        const bool out_vector = whole && (reinterpret_cast<uintptr_t>(po) & 15) == 0 && (sao * sizeof(TO)) % 16 == 0;
+        const bool out_vector = g.whole && (reinterpret_cast<uintptr_t>(g.po) & 15) == 0 && (sao * sizeof(TO)) % 16 == 0;
 #pragma unroll
         for (int it = 0; it < ITEMS; ++it) {
-            const int idx = threadIdx.x + kThreads * it;
-            const int aa = idx % kTile, bb = (idx / kTile) * EB;
-            if (aa < na && bb < nb) {
-                const int nvalid = nb - bb < EB ? nb - bb : EB;
-                Pack<TA, EB> va;
-                Pack<TB, EB> vb;
-                Pack<TC, EB> vc;
-                tile_gather<TA, EB>(va, tile_a, ta, a, 1, pa, saa, sab, aa, bb, nvalid);
-                tile_gather<TB, EB>(vb, tile_b, tb, a, 2, pb, sba, sbb, aa, bb, nvalid);
-                tile_gather<TC, EB>(vc, tile_c, tc, a, 3, pc, sca, scb, aa, bb, nvalid);
-                Pack<TO, EB> vo;
-                apply_all<F, EB>(vo, f, va, vb, vc);
-                TO *q = po + aa * sao + bb;
-                if (out_vector) {
-                    constexpr int V = 16 / sizeof(TO);
+            const int q = threadIdx.x + kThreads * it;
+            const int rest = q / LB;
+            const int a0 = (rest % AG) * GA, b0 = ((rest / AG) * LB + q % LB) * NB;
+            if ((TASKS % kThreads == 0 || q < TASKS) && a0 < g.na && b0 < g.nb) {
+                const int nvalid = g.nb - b0 < NB ? g.nb - b0 : NB;
+                Pack<TA, GA * NB> va;
+                Pack<TB, GA * NB> vb;
+                Pack<TC, GA * NB> vc;
+                tile_gather<TA, GA, NB, TD>(va, tile_a, ta, a, 1, g.pa, saa, sab, a0, b0, g.na, nvalid);
+                tile_gather<TB, GA, NB, TD>(vb, tile_b, tb, a, 2, g.pb, sba, sbb, a0, b0, g.na, nvalid);
+                tile_gather<TC, GA, NB, TD>(vc, tile_c, tc, a, 3, g.pc, sca, scb, a0, b0, g.na, nvalid);
+                Pack<TO, GA * NB> vo;
+                apply_all<F, GA * NB>(vo, f, va, vb, vc);
 #pragma unroll
-                    for (int j = 0; j < EB; j += V) {
-                        Pack<TO, V> x;
+                for (int gg = 0; gg < GA; ++gg) {
+                    if (a0 + gg >= g.na) continue;
+                    TO *out = g.po + (a0 + gg) * sao + b0;
+                    if (out_vector) {
+                        Pack<TO, NB> x;
 #pragma unroll
-                        for (int e = 0; e < V; ++e) x.v[e] = vo.v[j + e];
-                        *reinterpret_cast<Pack<TO, V> *>(q + j) = x;
+                        for (int e = 0; e < NB; ++e) x.v[e] = vo.v[gg * NB + e];
+                        *reinterpret_cast<Pack<TO, NB> *>(out) = x;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < NB; ++j)
+                            if (j < nvalid) out[j] = vo.v[gg * NB + j];
                     }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < EB; ++j)
-                        if (j < nvalid) q[j] = vo.v[j];
                 }
             }
         }
-        __syncthreads();
+        s = s + 1 == stages ? 0 : s + 1;
     }
+    async_copy_wait(0);
 }
 
 // One operand of a launch: a description, or (for inputs) a constant given by its bits.
@@ -686,17 +829,45 @@ hmc_status launch_map(hmc_context_t ctx, const F &f, const hmc_tensor_desc *out,
         }
     }
     if (a.tile_mask != 0) {
-        const size_t smem = tile_bytes<typename F::A>() + tile_bytes<typename F::B>() + tile_bytes<typename F::C>();
-        if (smem > 48 * 1024) {
-            static bool raised = false;  // per instantiation; the attribute is sticky for the function
-            if (!raised) {
-                cudaError_t err = cudaFuncSetAttribute(map_tile_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                       static_cast<int>(smem));
-                if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute");
-                raised = true;
-            }
+        constexpr int TD = tile_dim<F>();
+        const size_t tb[kOperands] = {0, tile_bytes<typename F::A, TD>(), tile_bytes<typename F::B, TD>(), tile_bytes<typename F::C, TD>()};
+        {
+            const int da = a.ndim - 2, db = a.ndim - 1;
+            a.tiles_a = ceil_div(a.sizes[da], TD);
+            a.tiles_b = ceil_div(a.sizes[db], TD);
+            int64_t outer = 1;
+            for (int d = 0; d < da; ++d) outer *= a.sizes[d];
+            a.ntiles = outer * a.tiles_a * a.tiles_b;
         }
-        const int64_t tcap = static_cast<int64_t>(ctx->sm_count) * 32;
+        a.stage_bytes = 0;
+        for (int k = 1; k < kOperands; ++k) {
+            a.tile_off[k] = a.stage_bytes;
+            if (a.tile_mask & (1u << k)) a.stage_bytes += static_cast<uint32_t>(tb[k]);
+        }
+        const int fit = static_cast<int>(kTileRingBytes / a.stage_bytes);
+        a.tile_stages = fit < 2 ? 2 : (fit > kTileStagesMax ? kTileStagesMax : fit);
+        const size_t smem = static_cast<size_t>(a.stage_bytes) * a.tile_stages;
+        // The shared-memory limit and the number of resident blocks, per instantiation, GPU and ring size.
+        struct Known { size_t raised = 0, smem = 0; int blocks = 0; };
+        static Known known_on[kTileKnownDevices];
+        Known local;
+        Known &known = ctx->device < kTileKnownDevices ? known_on[ctx->device] : local;
+        if (smem > 48 * 1024 && smem > known.raised) {
+            cudaError_t err = cudaFuncSetAttribute(map_tile_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   static_cast<int>(smem));
+            if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute");
+            known.raised = smem;
+        }
+        if (known.smem != smem) {
+            int blocks = 0;
+            cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, map_tile_kernel<F>, kThreads, smem);
+            if (err != cudaSuccess) return cuda_fail(err, "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+            if (blocks < 1) return fail(HMC_INTERNAL_ERROR, "the tiled kernel does not fit on this GPU");
+            known.blocks = blocks;
+            known.smem = smem;
+        }
+        const int known_blocks = known.blocks;
+        const int64_t tcap = static_cast<int64_t>(ctx->sm_count) * known_blocks;
         const unsigned tgrid = static_cast<unsigned>(a.ntiles < tcap ? a.ntiles : tcap);
         map_tile_kernel<F><<<tgrid, kThreads, smem, ctx->stream>>>(a, f);
         return launch_status("tiled elementwise kernel launch");

@@ -104,13 +104,7 @@ void build_map_args(MapArgs &a, const hmc_tensor_desc *out, const MapOperand *in
             if (descs[k] == nullptr) continue;
             if (a.strides[k][da] == 1 && a.strides[k][db] > 1) a.tile_mask |= 1u << k;
         }
-        if (a.tile_mask != 0) {
-            a.tiles_a = ceil_div(a.sizes[da], 64);
-            a.tiles_b = ceil_div(a.sizes[db], 64);
-            int64_t outer = 1;
-            for (int d = 0; d < da; ++d) outer *= a.sizes[d];
-            a.ntiles = outer * a.tiles_a * a.tiles_b;
-        }
+        // (the launch, which knows the tile edge of its element types, counts the tiles)
     }
     a.n0 = a.sizes[a.ndim - 1];
     a.rows = 1;

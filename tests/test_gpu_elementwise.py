@@ -238,6 +238,31 @@ def test_long_rows_are_cut_into_segments(oracle, cuda, dtype):
     assert_bitwise(c(gt).raw(), c(ot).raw(), dtype, "contiguous() of a transposed view")
 
 
+@pytest.mark.parametrize("dtype", [BF16, F32, I64, U8], ids=["bf16", "f32", "i64", "u8"])
+def test_transposed_operands_through_the_tile_ring(oracle, cuda, dtype):
+    """Transposed inputs large enough that every block laps its ring of shared-memory stages several times:
+    whole aligned tiles (fetched by bulk copies), ragged edge tiles and windows whose rows are not 16-byte
+    aligned (filled element by element) in one launch; one, two and three transposed inputs; outer dimensions."""
+    n, m = 2200, 2120  # 35 x 34 tiles, the last of each ragged
+    (ox, gx), (oy, gy), (oz, gz) = (both(oracle, cuda, values(dtype, n * m, 300 + i), dtype, (m, n)) for i in range(3))
+    (op_, gp) = both(oracle, cuda, values(dtype, n * m, 310), dtype, (n, m))
+    tr = lambda d: d.t()
+    unary = (lambda t: t.view(tr).neg()) if dtype != U8 else (lambda t: t.view(tr).contiguous())
+    assert_bitwise(unary(gx).raw(), unary(ox).raw(), dtype, "unary on x.t()")
+    one = lambda p, x: p.add(x.view(tr))
+    assert_bitwise(one(gp, gx).raw(), one(op_, ox).raw(), dtype, "p + x.t()")
+    two = lambda x, y: x.view(tr).mul(y.view(tr))
+    assert_bitwise(two(gx, gy).raw(), two(ox, oy).raw(), dtype, "x.t() * y.t()")
+    (oc, gc) = both(oracle, cuda, values(BOOL, n * m, 311), BOOL, (m, n))
+    three = lambda c, x, y: where(c.view(tr), x.view(tr), y.view(tr))
+    assert_bitwise(three(gc, gx, gy).raw(), three(oc, ox, oy).raw(), dtype, "where on three transposed inputs")
+    window = lambda x: x.view(lambda d: d.narrow(0, 1, m - 2).narrow(1, 3, n - 5).t()).contiguous()
+    assert_bitwise(window(gz).raw(), window(oz).raw(), dtype, "misaligned window of x.t()")
+    (ob, gb) = both(oracle, cuda, values(dtype, 3 * 200 * 328, 312), dtype, (3, 200, 328))
+    batched = lambda x: x.view(lambda d: d.transpose(1, 2)).contiguous()
+    assert_bitwise(batched(gb).raw(), batched(ob).raw(), dtype, "batched transpose")
+
+
 def test_promoting_add_matches_cast_then_add(oracle, cuda):
     """bf16 + f32 -> f32 in one kernel has the bits of homura's cast kernels followed by add."""
     x = values(BF16, 700 * 300, 61).reshape(700, 300)
