@@ -131,20 +131,26 @@ __device__ __forceinline__ float fast_exp2(float t) {
     asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(t));
     return y;
 }
-__device__ __forceinline__ float fast_rcp(float v) {
-    float y;
-    asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(v));
-    return y;
-}
 __device__ __forceinline__ float fast_exp(float x) { return fast_exp2(x * 1.44269504088896341f); }
+// 1 / (1 + exp(-x)) with one special-function instruction each for the exponential and the reciprocal, both
+// in their flush-to-zero forms, which need no fix-up code. That is safe here: an exponential small enough to
+// be flushed vanishes in 1 + e anyway, and the reciprocal is taken of (1 + e) / 4, which keeps its result a
+// normal number for every finite 1 + e; the final scaling by 1/4 is an ordinary multiplication, which keeps
+// subnormal results. An overflowing exponential gives 0 like the CPU's f32 evaluation.
+__device__ __forceinline__ float fast_sigmoid(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.44269504088896341f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__fmaf_rn(e, 0.25f, 0.25f)));
+    return r * 0.25f;
+}
 
 template <int OP, class C, bool FAST = false>
 __device__ __forceinline__ C unary_math(C x) {
     const C one = 1, zero = 0, half = static_cast<C>(0.5);
     if constexpr (FAST && std::is_same_v<C, float>) {
         if constexpr (OP == HMC_UNARY_EXP) return fast_exp(x);
-        else if constexpr (OP == HMC_UNARY_SIGMOID) return fast_rcp(one + fast_exp(-x));
-        else if constexpr (OP == HMC_UNARY_SILU) return x * fast_rcp(one + fast_exp(-x));
+        else if constexpr (OP == HMC_UNARY_SIGMOID) return fast_sigmoid(x);
+        else if constexpr (OP == HMC_UNARY_SILU) return x * fast_sigmoid(x);
     }
     if constexpr (OP == HMC_UNARY_NEG) return -x;
     else if constexpr (OP == HMC_UNARY_ABS) return m_abs(x);
