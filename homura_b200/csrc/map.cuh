@@ -83,7 +83,68 @@ template <class F> constexpr int unroll_of() {
     constexpr int out_bytes = static_cast<int>(sizeof(typename F::Out)) * vec_of<F>();
     constexpr int by_in = in_bytes == 0 ? 4 : (in_bytes >= 64 ? 1 : (in_bytes >= 32 ? 2 : 4));
     constexpr int by_out = out_bytes >= 64 ? 1 : (out_bytes >= 32 ? 2 : 4);
+#ifdef HMC_UNROLL_CAP
+    return (by_in < by_out ? by_in : by_out) < HMC_UNROLL_CAP ? (by_in < by_out ? by_in : by_out) : HMC_UNROLL_CAP;
+#else
     return by_in < by_out ? by_in : by_out;
+#endif
+}
+
+// 32 bytes in one instruction (sm_100's 256-bit global accesses): a lane then moves a whole sector, where two
+// 16-byte accesses leave half of every sector to the second instruction. The address is 32-byte aligned.
+#ifndef HMC_WIDE_LOADS
+#define HMC_WIDE_LOADS 1
+#endif
+#ifndef HMC_WIDE_STORES
+#define HMC_WIDE_STORES 1
+#endif
+struct alignas(32) Bytes32 {
+    uint32_t w[8];
+};
+__device__ __forceinline__ Bytes32 load_32_bytes(const void *p) {
+    Bytes32 v;
+    // not volatile: the compiler may schedule it like any other load (measurably faster than a fixed order)
+    asm("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7])
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void store_32_bytes(void *p, const Bytes32 &v) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]),
+                 "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]), "r"(v.w[7])
+                 : "memory");
+}
+// A vector of a row; `wide`: the vector's address is a multiple of 32 (it matters for vectors of 32 and 64 bytes).
+template <class T, int VEC>
+__device__ __forceinline__ void vector_load(Pack<T, VEC> &dst, const T *p, bool wide) {
+    constexpr int kBytes = static_cast<int>(sizeof(T)) * VEC;
+    if constexpr (kBytes % 32 == 0 && HMC_WIDE_LOADS) {
+        if (wide) {
+#pragma unroll
+            for (int i = 0; i < kBytes / 32; ++i) {
+                const Bytes32 v = load_32_bytes(reinterpret_cast<const char *>(p) + 32 * i);
+                memcpy(reinterpret_cast<char *>(&dst) + 32 * i, &v, 32);
+            }
+            return;
+        }
+    }
+    dst = *reinterpret_cast<const Pack<T, VEC> *>(p);
+}
+template <class T, int VEC>
+__device__ __forceinline__ void vector_store(T *p, const Pack<T, VEC> &src, bool wide) {
+    constexpr int kBytes = static_cast<int>(sizeof(T)) * VEC;
+    if constexpr (kBytes % 32 == 0 && HMC_WIDE_STORES) {
+        if (wide) {
+#pragma unroll
+            for (int i = 0; i < kBytes / 32; ++i) {
+                Bytes32 v;
+                memcpy(&v, reinterpret_cast<const char *>(&src) + 32 * i, 32);
+                store_32_bytes(reinterpret_cast<char *>(p) + 32 * i, v);
+            }
+            return;
+        }
+    }
+    *reinterpret_cast<Pack<T, VEC> *>(p) = src;
 }
 
 // How an operand is walked along the inner dimension.
@@ -134,7 +195,7 @@ __device__ __forceinline__ void store_operand(const Pack<T, VEC> &src, const Map
     if (mode == kModeUnit) {
         T *p = row + idx;
         if (idx + VEC <= a.n0 && (reinterpret_cast<uintptr_t>(p) & (alignof(Pack<T, VEC>) - 1)) == 0) {
-            *reinterpret_cast<Pack<T, VEC> *>(p) = src;
+            vector_store<T, VEC>(p, src, (reinterpret_cast<uintptr_t>(p) & 31) == 0);
         } else {
 #pragma unroll
             for (int j = 0; j < VEC; ++j)
@@ -327,7 +388,7 @@ __global__ void __launch_bounds__(kThreads, HMC_MAP_MIN_BLOCKS) map_kernel(const
                 const int64_t idx = i0 + u * step;
                 Pack<TO, VEC> vo;
                 apply_all<F, VEC>(vo, f, va[u], vb[u], vc[u]);
-                *reinterpret_cast<Pack<TO, VEC> *>(po + idx) = vo;
+                vector_store<TO, VEC>(po + idx, vo, (reinterpret_cast<uintptr_t>(po + idx) & 31) == 0);
             }
             continue;
         }
@@ -366,14 +427,15 @@ struct LeanArgs {
     uint64_t constant[kOperands];
     uint32_t constant_mask;
     uint32_t n0;                    // inner size (< 2^31)
+    uint32_t wide_mask;             // bit k: operand k's rows start on 32-byte boundaries
     int64_t rows;
 };
 
 template <class T, int VEC>
-__device__ __forceinline__ void lean_load(Pack<T, VEC> &dst, const T *row, uint32_t inner, uint32_t col, const Pack<T, 1> &c) {
+__device__ __forceinline__ void lean_load(Pack<T, VEC> &dst, const T *row, uint32_t inner, uint32_t col, const Pack<T, 1> &c, bool wide) {
     if constexpr (!std::is_same_v<T, Unused>) {
         if (inner) {
-            dst = *reinterpret_cast<const Pack<T, VEC> *>(row + col);
+            vector_load<T, VEC>(dst, row + col, wide);
         } else {
 #pragma unroll
             for (int j = 0; j < VEC; ++j) dst.v[j] = c.v[0];
@@ -392,6 +454,7 @@ __global__ void __launch_bounds__(kThreads, 4) map_lean_kernel(const __grid_cons
     constexpr uint32_t kStep = kThreads * VEC;
     const uint32_t col0 = blockIdx.x * (kStep * UNR) + threadIdx.x * VEC;
     const bool ka = a.constant_mask & 2u, kb = a.constant_mask & 4u, kc = a.constant_mask & 8u;
+    const bool wo = a.wide_mask & 1u, wa = a.wide_mask & 2u, wb = a.wide_mask & 4u, wc = a.wide_mask & 8u;
     for (int64_t row = blockIdx.y; row < a.rows; row += gridDim.y) {
         TO *po = reinterpret_cast<TO *>(a.base[0]) + row * a.row_stride[0];
         const TA *pa = nullptr;
@@ -422,16 +485,16 @@ __global__ void __launch_bounds__(kThreads, 4) map_lean_kernel(const __grid_cons
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 const uint32_t col = col0 + u * kStep;
-                lean_load<TA, VEC>(va[u], pa, a.inner[1] && !ka, col, ca);
-                lean_load<TB, VEC>(vb[u], pb, a.inner[2] && !kb, col, cb);
-                lean_load<TC, VEC>(vc[u], pc, a.inner[3] && !kc, col, cc);
+                lean_load<TA, VEC>(va[u], pa, a.inner[1] && !ka, col, ca, wa);
+                lean_load<TB, VEC>(vb[u], pb, a.inner[2] && !kb, col, cb, wb);
+                lean_load<TC, VEC>(vc[u], pc, a.inner[3] && !kc, col, cc, wc);
             }
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 const uint32_t col = col0 + u * kStep;
                 Pack<TO, VEC> vo;
                 apply_all<F, VEC>(vo, f, va[u], vb[u], vc[u]);
-                *reinterpret_cast<Pack<TO, VEC> *>(po + col) = vo;
+                vector_store<TO, VEC>(po + col, vo, wo);
             }
         } else {
             // the ragged end of a row: whole vectors while they fit, then single elements
@@ -439,12 +502,12 @@ __global__ void __launch_bounds__(kThreads, 4) map_lean_kernel(const __grid_cons
             for (int u = 0; u < UNR; ++u) {
                 const uint32_t col = col0 + u * kStep;
                 if (col + VEC <= a.n0) {
-                    lean_load<TA, VEC>(va[0], pa, a.inner[1] && !ka, col, ca);
-                    lean_load<TB, VEC>(vb[0], pb, a.inner[2] && !kb, col, cb);
-                    lean_load<TC, VEC>(vc[0], pc, a.inner[3] && !kc, col, cc);
+                    lean_load<TA, VEC>(va[0], pa, a.inner[1] && !ka, col, ca, wa);
+                    lean_load<TB, VEC>(vb[0], pb, a.inner[2] && !kb, col, cb, wb);
+                    lean_load<TC, VEC>(vc[0], pc, a.inner[3] && !kc, col, cc, wc);
                     Pack<TO, VEC> vo;
                     apply_all<F, VEC>(vo, f, va[0], vb[0], vc[0]);
-                    *reinterpret_cast<Pack<TO, VEC> *>(po + col) = vo;
+                    vector_store<TO, VEC>(po + col, vo, wo);
                 } else if (col < a.n0) {
                     for (uint32_t e = col; e < a.n0; ++e) {
                         Pack<TA, 1> xa;

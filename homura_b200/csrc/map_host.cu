@@ -153,6 +153,8 @@ bool build_lean_args(LeanArgs &lean, const MapArgs &a, const int *elem_size, int
             if (reinterpret_cast<uintptr_t>(a.base[k]) % vec_bytes != 0) return false;
             if (a.rows > 1 && (row_stride * elem_size[k]) % vec_bytes != 0) return false;
         }
+        if (inner == 1 && reinterpret_cast<uintptr_t>(a.base[k]) % 32 == 0 && (a.rows == 1 || (row_stride * elem_size[k]) % 32 == 0))
+            lean.wide_mask |= 1u << k;
         lean.base[k] = a.base[k];
         lean.row_stride[k] = row_stride;
         lean.inner[k] = inner == 1 ? 1u : 0u;
