@@ -395,6 +395,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
+    ap.add_argument("--c4-batch", type=int, default=256,
+                    help="matrices of [2048, 2048] logits in the c4 workload (256 = [8, 32, 2048, 2048]); a smaller "
+                         "number keeps a profiler capture short")
     ap.add_argument("--profile", action="store_true",
                     help="only the warm-up and the timed steps (no per-kernel loop, end-to-end pass or CPU sample): "
                          "the short command to run under ncu")
@@ -428,8 +431,13 @@ def main() -> None:
         w = C5Workload(be, seed=rank, log2n=29, reducer=ShardedReducer(be, comm, [r * n_local for r in range(world)], world * n_local))
         workload_name, step_bytes = w.name + "_sharded", sum(w.op_bytes.values())
     else:
-        w = {"c3": C3Workload, "c4": C4Workload, "c5": C5Workload}[args.workload](be, seed=rank)
+        if args.workload == "c4":
+            w = C4Workload(be, seed=rank, batch=args.c4_batch)
+        else:
+            w = {"c3": C3Workload, "c5": C5Workload}[args.workload](be, seed=rank)
         workload_name, step_bytes = w.name, sum(w.op_bytes.values())
+        if args.workload == "c4" and args.c4_batch != 256:
+            workload_name += f"_batch{args.c4_batch}"
     ops = w.ops()
 
     def barrier():

@@ -78,6 +78,45 @@ __device__ __forceinline__ double group_sum(double v, double *scratch) {
     return v;
 }
 
+// The same reductions for the rows that live in registers as f32 values: the maximum in f32 (exact), one
+// barrier per reduction (the two scratch arrays alternate, so a warp that runs ahead cannot overwrite values
+// another warp still reads).
+template <int G>
+__device__ __forceinline__ float row_max_f32(float v, float *scratch) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
+    if constexpr (G == 256) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) scratch[warp] = v;
+        __syncthreads();
+        v = scratch[lane & 7];
+#pragma unroll
+        for (int d = 4; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
+    }
+    return v;
+}
+template <int G>
+__device__ __forceinline__ double row_sum_f64(double v, double *scratch) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
+    if constexpr (G == 256) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) scratch[warp] = v;
+        __syncthreads();
+        // every lane adds the eight partial sums in the same order: the same bits in every lane
+        v = scratch[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) v += scratch[w];
+    }
+    return v;
+}
+// max(x, y) that keeps a NaN (fmaxf drops it).
+__device__ __forceinline__ float max_keep_nan(float x, float y) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(y));
+    return r;
+}
+
 // exp(d) for d = x - max <= 0, or NaN. exp(-inf) is +0 without evaluating anything. Rows of F16, BF16 and
 // F32 tensors are rounded to at most 24 bits at the end, so their exponentials need 40 good bits, not 53:
 // they take the short polynomial; F64 rows take the full f64 exp.
@@ -99,6 +138,8 @@ __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_ker
     constexpr int P = kRThreads / G;
     constexpr int NV = CV > 0 ? CV : 1;
     __shared__ double scratch[8];
+    __shared__ double scratch_sum[8];
+    __shared__ float scratch_max[8];
     const int lane = threadIdx.x % G;
     const int slot = threadIdx.x / G;
     const int64_t tiles = (a.nrows + P - 1) / P;
@@ -133,6 +174,63 @@ __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_ker
                     if (i0 + e < a.n) po[(i0 + e) * a.so] = y.v[e];
             }
         };
+        if constexpr (CV > 0 && !std::is_same_v<T, double>) {
+            // Rows of whole, aligned vectors of F16, BF16 or F32: the row is kept as f32 values (its maximum is
+            // exact in f32), no element needs a bounds check, and the exponentials take the short f64 polynomial.
+            // An element more than 200 below the maximum is moved up to there: its exponential, below 1e-86, still
+            // rounds to 0 in the output and vanishes in the sum, and exp_short needs no range check.
+            if (fast_in && fast_out && a.n % VEC == 0) {
+                float xf[NV][VEC];
+                bool on[NV];
+                float mxf = -CUDART_INF_F;
+#pragma unroll
+                for (int c = 0; c < NV; ++c) {
+                    const int64_t v = lane + static_cast<int64_t>(c) * G;
+                    on[c] = valid && v < nvec;
+                    if (on[c]) {
+                        const RVec<T, VEC> raw = *reinterpret_cast<const RVec<T, VEC> *>(ps + v * VEC);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) {
+                            xf[c][e] = up(raw.v[e]);
+                            mxf = fmaxf(mxf, xf[c][e]);
+                        }
+                    }
+                }
+                mxf = row_max_f32<G>(mxf, scratch_max);
+                const float floor_x = mxf - 200.0f;
+                const double mx = static_cast<double>(mxf);
+                double ex[LOG ? 1 : NV][LOG ? 1 : VEC];
+                double sum = 0.0;
+#pragma unroll
+                for (int c = 0; c < NV; ++c) {
+                    if (on[c]) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) {
+                            const double ev = exp_short(static_cast<double>(max_keep_nan(xf[c][e], floor_x)) - mx);
+                            sum += ev;
+                            if constexpr (!LOG) ex[c][e] = ev;
+                        }
+                    }
+                }
+                sum = row_sum_f64<G>(sum, scratch_sum);
+                const double log_sum = LOG ? log(sum) : 0.0;
+                const double inv = LOG ? 0.0 : 1.0 / sum;
+#pragma unroll
+                for (int c = 0; c < NV; ++c) {
+                    if (on[c]) {
+                        const int64_t v = lane + static_cast<int64_t>(c) * G;
+                        RVec<T, VEC> y;
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) {
+                            if constexpr (LOG) y.v[e] = from_f64<T>((static_cast<double>(xf[c][e]) - mx) - log_sum);
+                            else y.v[e] = from_f64<T>(ex[c][e] * inv);
+                        }
+                        *reinterpret_cast<RVec<T, VEC> *>(po + v * VEC) = y;
+                    }
+                }
+                continue;
+            }
+        }
         if constexpr (CV > 0) {
             double x[NV][VEC];
             double mx = ninf;
