@@ -128,9 +128,9 @@ __device__ __forceinline__ double exp_shifted(double d) {
 }
 
 // Rows are handled one after the other inside a block (load, max, exp, sum, store are dependent phases), so
-// throughput is rows in flight per SM: the register budget is set to keep four blocks resident while a lane
-// caches up to two vectors, three for four.
-constexpr int softmax_min_blocks(int cv) { return cv <= 2 ? 4 : (cv <= 4 ? 3 : 2); }
+// throughput is rows in flight per SM: the register budget keeps three blocks resident while a lane caches up
+// to two vectors (plus the two of the row it loads ahead), two blocks beyond that.
+constexpr int softmax_min_blocks(int cv) { return cv <= 2 ? 3 : 2; }
 
 template <class T, int G, int CV, bool LOG>
 __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_kernel(const __grid_constant__ SoftmaxArgs a) {
@@ -147,6 +147,10 @@ __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_ker
     T *dst = static_cast<T *>(a.out_rows.data);
     const int64_t nvec = (a.n + VEC - 1) / VEC;
     const double ninf = -CUDART_INF;
+    // The vectors of the row a lane handles next, loaded while the current row is computed (rows are dependent
+    // phases, so a block with a single row in flight leaves the memory system idle most of the time).
+    RVec<T, VEC> ahead[NV];
+    bool have_ahead = false;
     for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const int64_t r = tile * P + slot;
         const bool valid = r < a.nrows;
@@ -181,6 +185,7 @@ __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_ker
             // rounds to 0 in the output and vanishes in the sum, and exp_short needs no range check.
             if (fast_in && fast_out && a.n % VEC == 0) {
                 float xf[NV][VEC];
+                float vmax[NV];  // the vector's maximum, NaN if it holds one
                 bool on[NV];
                 float mxf = -CUDART_INF_F;
 #pragma unroll
@@ -188,12 +193,27 @@ __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_ker
                     const int64_t v = lane + static_cast<int64_t>(c) * G;
                     on[c] = valid && v < nvec;
                     if (on[c]) {
-                        const RVec<T, VEC> raw = *reinterpret_cast<const RVec<T, VEC> *>(ps + v * VEC);
+                        if (!have_ahead) ahead[c] = *reinterpret_cast<const RVec<T, VEC> *>(ps + v * VEC);
 #pragma unroll
-                        for (int e = 0; e < VEC; ++e) {
-                            xf[c][e] = up(raw.v[e]);
-                            mxf = fmaxf(mxf, xf[c][e]);
+                        for (int e = 0; e < VEC; ++e) xf[c][e] = up(ahead[c].v[e]);
+                        vmax[c] = xf[c][0];
+#pragma unroll
+                        for (int e = 1; e < VEC; ++e) vmax[c] = max_keep_nan(vmax[c], xf[c][e]);
+                        mxf = fmaxf(mxf, vmax[c]);  // a NaN loses here; it reaches the sum below
+                    }
+                }
+                have_ahead = false;
+                if (tile + gridDim.x < tiles) {
+                    const int64_t rn = (tile + gridDim.x) * P + slot;
+                    const bool valid_n = rn < a.nrows;
+                    const T *pn = src + a.src_rows.offset + decompose(a.src_rows, valid_n ? rn : 0, a.src_rows.ndim);
+                    if ((reinterpret_cast<uintptr_t>(pn) & 15) == 0) {
+#pragma unroll
+                        for (int c = 0; c < NV; ++c) {
+                            const int64_t v = lane + static_cast<int64_t>(c) * G;
+                            if (valid_n && v < nvec) ahead[c] = *reinterpret_cast<const RVec<T, VEC> *>(pn + v * VEC);
                         }
+                        have_ahead = true;
                     }
                 }
                 mxf = row_max_f32<G>(mxf, scratch_max);
@@ -203,13 +223,20 @@ __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_ker
                 double sum = 0.0;
 #pragma unroll
                 for (int c = 0; c < NV; ++c) {
-                    if (on[c]) {
+                    if (!on[c]) continue;
+                    if (vmax[c] < floor_x) {
+                        // a vector of masked logits: its exponentials round to 0 and vanish in the sum
+                        if constexpr (!LOG) {
 #pragma unroll
-                        for (int e = 0; e < VEC; ++e) {
-                            const double ev = exp_short(static_cast<double>(max_keep_nan(xf[c][e], floor_x)) - mx);
-                            sum += ev;
-                            if constexpr (!LOG) ex[c][e] = ev;
+                            for (int e = 0; e < VEC; ++e) ex[c][e] = 0.0;
                         }
+                        continue;
+                    }
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) {
+                        const double ev = exp_short(static_cast<double>(max_keep_nan(xf[c][e], floor_x)) - mx);
+                        sum += ev;
+                        if constexpr (!LOG) ex[c][e] = ev;
                     }
                 }
                 sum = row_sum_f64<G>(sum, scratch_sum);
@@ -231,6 +258,7 @@ __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_ker
                 continue;
             }
         }
+        have_ahead = false;  // (the paths below load for themselves)
         if constexpr (CV > 0) {
             double x[NV][VEC];
             double mx = ninf;
