@@ -420,6 +420,9 @@ __global__ void __launch_bounds__(kThreads, HMC_MAP_MIN_BLOCKS) map_kernel(const
 // with a row stride of 0. Such launches need none of the general kernel's bookkeeping: a thread's vectors are
 // found with a handful of integer operations, which matters for 1- and 2-byte elements, where a kernel at HBM
 // speed has an instruction budget of about fifteen per element.
+#ifndef HMC_LEAN_MIN_BLOCKS
+#define HMC_LEAN_MIN_BLOCKS 4
+#endif
 struct LeanArgs {
     char *base[kOperands];
     int64_t row_stride[kOperands];  // elements
@@ -444,7 +447,7 @@ __device__ __forceinline__ void lean_load(Pack<T, VEC> &dst, const T *row, uint3
 }
 
 template <class F>
-__global__ void __launch_bounds__(kThreads, 4) map_lean_kernel(const __grid_constant__ LeanArgs a, const F f) {
+__global__ void __launch_bounds__(kThreads, HMC_LEAN_MIN_BLOCKS) map_lean_kernel(const __grid_constant__ LeanArgs a, const F f) {
     using TO = typename F::Out;
     using TA = typename F::A;
     using TB = typename F::B;

@@ -34,8 +34,10 @@ namespace hmc {
 
 constexpr int kRThreads = 256;
 constexpr int64_t kTargetLanes = 148 * 2048;  // fixed, so that plans do not depend on the device
-constexpr int64_t kTargetColumnBlocks = 148 * 4;
+constexpr int64_t kTargetColumnBlocks = 148 * 3;  // one wave of the column kernel's blocks (three are resident per SM)
 constexpr int64_t kMaxSplits = 4096;
+constexpr int64_t kWarpRowOutputs = 148 * 32;  // outputs from which a long row is folded by a warp
+constexpr int64_t kWarpRowLength = 1 << 16;    // and the longest such row
 constexpr int64_t kPartialBytes = 16;
 
 struct ReducePlan {
@@ -47,6 +49,9 @@ struct ReducePlan {
     int64_t row, step;  // last reduced dimension: size and source stride
     int64_t splits, chunk;
     int64_t ncols, kouter, xtiles;  // kind 1: last kept size, product of the others, column tiles
+    // kind 0, no chunks, and every output folds one unit-stride row of whole vectors (nred < 2^31): rows that
+    // start on a 16-byte boundary take a loop without the bookkeeping of ranges, dimensions and ragged ends.
+    int32_t simple;
 };
 
 struct ReduceArgs {
@@ -137,6 +142,15 @@ __device__ __forceinline__ typename Op::Acc fold_step(const Op &op, typename Op:
     else return op.combine(acc, op.load(x, o, j));
 }
 
+// An op with what it needs of output o already in registers; ops without per-output state are returned as is.
+template <class Op, class = void> struct has_bound : std::false_type {};
+template <class Op> struct has_bound<Op, std::void_t<decltype(&Op::bound)>> : std::true_type {};
+template <class Op>
+__device__ __forceinline__ Op bind_output(const Op &op, int64_t o) {
+    if constexpr (has_bound<Op>::value) return op.bound(o);
+    else return op;
+}
+
 template <class T, int VEC>
 struct alignas(sizeof(T) * VEC >= 16 ? 16 : sizeof(T) * VEC) RVec {
     T v[VEC];
@@ -211,6 +225,99 @@ __device__ __forceinline__ typename Op::Acc fold_range(const Op &op, const Reduc
     return acc;
 }
 
+// (value, index); index < 0 marks the empty fold. src/backend/cpu/reduce.rs:75-86.
+template <class TT>
+struct alignas(16) Best {
+    TT v;
+    int64_t i;
+};
+
+template <class T> __device__ __forceinline__ auto order_key(T x) {
+    if constexpr (std::is_same_v<T, F16> || std::is_same_v<T, BF16>) return up(x);
+    else if constexpr (std::is_same_v<T, Bool>) return x.b;
+    else return x;
+}
+
+// One lane's share of a simple row (plan.simple): vectors lane, lane + G, ... of the nvec vectors at p, in
+// the order and with the element indices fold_range gives them, hence the same bits.
+template <int G, class Op>
+__device__ __forceinline__ typename Op::Acc fold_simple_row(const Op &op, const typename Op::T *p, uint32_t nvec, int lane,
+                                                            int64_t o) {
+    using T = typename Op::T;
+    using Acc = typename Op::Acc;
+    constexpr int VEC = 16 / sizeof(T);
+    constexpr int UNR = 4;
+    Acc acc = op.init();
+    uint32_t v = lane;
+    for (; v + (UNR - 1) * G < nvec; v += UNR * G) {
+        RVec<T, VEC> x[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VEC> *>(p + static_cast<size_t>(v + u * G) * VEC);
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x[u].v[e], o, static_cast<int64_t>(v + u * G) * VEC + e);
+        }
+    }
+    for (; v < nvec; v += G) {
+        const RVec<T, VEC> x = *reinterpret_cast<const RVec<T, VEC> *>(p + static_cast<size_t>(v) * VEC);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x.v[e], o, static_cast<int64_t>(v) * VEC + e);
+    }
+    return acc;
+}
+
+template <class TT, bool MAX> struct Extreme;
+template <class Op> struct is_extreme : std::false_type {};
+template <class TT, bool MAX> struct is_extreme<Extreme<TT, MAX>> : std::true_type {};
+
+// The same for max / min / argmax / argmin, where the general step (first NaN, then first of equals, a 64-bit
+// index) costs about forty instructions per element. Here a lane keeps the best key, its raw value and a
+// 32-bit index, and takes a later element only if it is strictly better: "first of equals" as in the general
+// step. NaNs are not handled but detected (the sum of a vector's keys is NaN if one of them is; an
+// infinity minus infinity there raises a false alarm, which is harmless): `redo` tells the caller to fold the
+// row again with the general step.
+template <int G, class TT, bool MAX>
+__device__ __forceinline__ typename Extreme<TT, MAX>::Acc fold_simple_row_extreme(const TT *p, uint32_t nvec, int lane, bool &redo) {
+    using Acc = typename Extreme<TT, MAX>::Acc;
+    constexpr int VEC = 16 / sizeof(TT);
+    constexpr int UNR = 4;
+    constexpr bool kFloating = Tr<TT>::kind == kFloat;
+    redo = false;
+    if (static_cast<uint32_t>(lane) >= nvec) return Acc{TT{}, -1};
+    TT best = p[static_cast<size_t>(lane) * VEC];
+    auto best_key = order_key(best);
+    uint32_t best_at = lane * VEC;
+    float alarm = 0.0f;
+    auto take_vector = [&](const RVec<TT, VEC> &x, uint32_t at) {
+        if constexpr (kFloating) {
+            float s = static_cast<float>(order_key(x.v[0]));
+#pragma unroll
+            for (int e = 1; e < VEC; ++e) s += static_cast<float>(order_key(x.v[e]));
+            alarm += s;
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            const auto k = order_key(x.v[e]);
+            const bool better = MAX ? k > best_key : k < best_key;
+            best_key = better ? k : best_key;
+            best = better ? x.v[e] : best;
+            best_at = better ? at + e : best_at;
+        }
+    };
+    uint32_t v = lane;
+    for (; v + (UNR - 1) * G < nvec; v += UNR * G) {
+        RVec<TT, VEC> x[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<TT, VEC> *>(p + static_cast<size_t>(v + u * G) * VEC);
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) take_vector(x[u], (v + u * G) * VEC);
+    }
+    for (; v < nvec; v += G) take_vector(*reinterpret_cast<const RVec<TT, VEC> *>(p + static_cast<size_t>(v) * VEC), v * VEC);
+    if constexpr (kFloating) redo = alarm != alarm;
+    return Acc{best, static_cast<int64_t>(best_at)};
+}
+
 // kind 0. Grid: (tiles of 256 / G outputs, splits).
 template <int G, class Op, class Sink>
 __global__ void __launch_bounds__(kRThreads) reduce_group_kernel(const __grid_constant__ ReduceArgs a, const Op op,
@@ -227,7 +334,28 @@ __global__ void __launch_bounds__(kRThreads) reduce_group_kernel(const __grid_co
     for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const int64_t o = tile * P + slot;
         Acc acc = op.init();
-        if (o < p.nout) acc = fold_range<G>(op, a, o, a.kept.offset + decompose(a.kept, o, a.kept.ndim), j0, j1, lane);
+        if (o < p.nout) {
+            using T = typename Op::T;
+            const int64_t base = a.kept.offset + decompose(a.kept, o, a.kept.ndim);
+            const T *row = static_cast<const T *>(a.kept.data) + base;
+            bool general = true;
+            if constexpr (G > 1) {
+                if (p.simple && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+                    const uint32_t nvec = static_cast<uint32_t>(p.nred) / (16 / sizeof(T));
+                    if constexpr (is_extreme<Op>::value) {
+                        bool redo;
+                        acc = fold_simple_row_extreme<G, T, std::is_same_v<Op, Extreme<T, true>>>(row, nvec, lane, redo);
+                        // the lanes of an output agree on folding again (an output's lanes are a warp, or the block)
+                        if constexpr (G == 32) general = __any_sync(0xFFFFFFFFu, redo);
+                        else general = __syncthreads_or(redo);
+                    } else {
+                        acc = fold_simple_row<G>(op, row, nvec, lane, o);
+                        general = false;
+                    }
+                }
+            }
+            if (general) acc = fold_range<G>(op, a, o, base, j0, j1, lane);
+        }
         acc = group_combine<G>(op, acc);
         if (lane == 0 && o < p.nout) {
             if (p.splits == 1) sink.put(o, acc, p.nred);
@@ -265,6 +393,10 @@ __global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_
         Acc acc[VC];
 #pragma unroll
         for (int e = 0; e < VC; ++e) acc[e] = op.init();
+        // what the op needs to know about an output (its mean, for the squared deviations) is fetched once
+        Op ops[VC];
+#pragma unroll
+        for (int e = 0; e < VC; ++e) ops[e] = bind_output(op, c0 + e < p.ncols ? o0 + e : 0);
         const bool in_range = c0 < p.ncols;
         const bool whole = c0 + VC <= p.ncols;
         if (in_range) {
@@ -285,7 +417,7 @@ __global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_
                 for (int u = 0; u < UNR; ++u) {
 #pragma unroll
                     for (int e = 0; e < VC; ++e) {
-                        if (whole || c0 + e < p.ncols) acc[e] = fold_step(op, acc[e], x[u].v[e], o0 + e, j + u * 8);
+                        if (whole || c0 + e < p.ncols) acc[e] = fold_step(ops[e], acc[e], x[u].v[e], o0 + e, j + u * 8);
                     }
                 }
             }
@@ -293,7 +425,7 @@ __global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_
                 const T *q = src + red_off(j);
 #pragma unroll
                 for (int e = 0; e < VC; ++e) {
-                    if (c0 + e < p.ncols) acc[e] = fold_step(op, acc[e], q[e], o0 + e, j);
+                    if (c0 + e < p.ncols) acc[e] = fold_step(ops[e], acc[e], q[e], o0 + e, j);
                 }
             }
         }
@@ -316,8 +448,8 @@ __global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_
     }
 }
 
-// Folds the partials of each output in chunk order. L lanes per output (1 or 32): with 32, lane l
-// folds chunks l, l+32, ... and the lanes are combined by shuffles.
+// Folds the partials of each output in chunk order. L lanes per output (1, 32 or 256): lane l folds chunks
+// l, l + L, ... and the lanes are combined in lane order (shuffles, and shared memory for 256).
 template <int L, class Op, class Sink>
 __global__ void __launch_bounds__(kRThreads) reduce_combine_kernel(const __grid_constant__ ReduceArgs a, const Op op,
                                                                    const Sink sink) {
@@ -331,11 +463,14 @@ __global__ void __launch_bounds__(kRThreads) reduce_combine_kernel(const __grid_
         const int64_t o = t * per_block + threadIdx.x / L;
         Acc acc = op.init();
         if (o < p.nout) {
+#pragma unroll 4
             for (int64_t c = lane; c < p.splits; c += L) acc = op.combine(acc, partials[c * p.nout + o]);
         }
         if constexpr (L == 32) {
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) acc = op.combine(acc, shuffle_down(acc, d));
+        } else if constexpr (L == 256) {
+            acc = group_combine<256>(op, acc);
         }
         if (lane == 0 && o < p.nout) sink.put(o, acc, p.nred);
     }
@@ -363,7 +498,10 @@ hmc_status launch_reduce(const ReduceArgs &a, const Op &op, const Sink &sink, cu
     hmc_status s = launch_status("reduction kernel launch");
     if (s != HMC_OK) return s;
     if (p.splits > 1) {
-        if (p.splits >= 64) {
+        if (p.splits >= 512 && p.nout <= 64) {
+            // a few outputs with very many partials each (a full reduction): a block per output
+            reduce_combine_kernel<256, Op, Sink><<<clamp_grid(p.nout, 1 << 16), kRThreads, 0, stream>>>(a, op, sink);
+        } else if (p.splits >= 64) {
             const int64_t rounds = (p.nout + 7) / 8;
             reduce_combine_kernel<32, Op, Sink><<<clamp_grid(rounds, 1 << 16), kRThreads, 0, stream>>>(a, op, sink);
         } else {
@@ -408,19 +546,6 @@ struct Truth {
     __device__ __forceinline__ Acc combine(Acc a, Acc b) const { return ALL ? (a & b) : (a | b); }
 };
 
-// (value, index); index < 0 marks the empty fold. src/backend/cpu/reduce.rs:75-86.
-template <class TT>
-struct alignas(16) Best {
-    TT v;
-    int64_t i;
-};
-
-template <class T> __device__ __forceinline__ auto order_key(T x) {
-    if constexpr (std::is_same_v<T, F16> || std::is_same_v<T, BF16>) return up(x);
-    else if constexpr (std::is_same_v<T, Bool>) return x.b;
-    else return x;
-}
-
 template <class TT, bool MAX>
 struct Extreme {
     using T = TT;
@@ -462,6 +587,9 @@ struct SquaredDeviation {
     __device__ __forceinline__ Acc load(T x, int64_t o, int64_t) const {
         const double d = widen(x) - (means != nullptr ? means[o] : mean);
         return d * d;
+    }
+    __device__ __forceinline__ SquaredDeviation bound(int64_t o) const {
+        return SquaredDeviation{nullptr, means != nullptr ? means[o] : mean};
     }
     __device__ __forceinline__ Acc combine(Acc a, Acc b) const { return a + b; }
 };

@@ -38,14 +38,17 @@ __global__ void __launch_bounds__(kRThreads) deviations_kernel(const __grid_cons
         const int64_t o = tile * P + slot;
         const bool valid = o < p.nout;
         const int64_t base = valid ? a.kept.offset + decompose(a.kept, o, a.kept.ndim) : 0;
-        double sum = valid ? fold_range<G>(fold, a, o, base, 0, p.nred, lane) : 0.0;
+        const T *row = static_cast<const T *>(a.kept.data) + base;
+        const bool simple = G > 1 && p.simple && (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+        const uint32_t nvec = static_cast<uint32_t>(p.nred) / (16 / sizeof(T));
+        double sum = !valid ? 0.0 : (simple ? fold_simple_row<G>(fold, row, nvec, lane, o) : fold_range<G>(fold, a, o, base, 0, p.nred, lane));
         sum = group_combine<G>(fold, sum);
         if (lane == 0) mean_of[slot] = sum / static_cast<double>(p.nred);
         if constexpr (G > 1) {
             if constexpr (G == 32) __syncwarp(); else __syncthreads();
         }
         SquaredDeviation<T> dev{nullptr, mean_of[slot]};
-        double sq = valid ? fold_range<G>(dev, a, o, base, 0, p.nred, lane) : 0.0;
+        double sq = !valid ? 0.0 : (simple ? fold_simple_row<G>(dev, row, nvec, lane, o) : fold_range<G>(dev, a, o, base, 0, p.nred, lane));
         sq = group_combine<G>(dev, sq);
         if (lane == 0 && valid) sink.put(o, sq, p.nred);
         if constexpr (G == 256) __syncthreads();

@@ -35,7 +35,8 @@ ReducePlan make_reduce_plan(const hmc_tensor_desc &kept, const hmc_tensor_desc &
         p.xtiles = ceil_div(p.ncols, 32 * p.vc);
         const int64_t blocks = p.kouter * p.xtiles;
         if (blocks < kTargetColumnBlocks) {
-            const int64_t want = ceil_div(kTargetColumnBlocks, blocks);
+            // as many chunks as still fit into one wave of blocks: equal blocks, no tail
+            const int64_t want = kTargetColumnBlocks / blocks;
             const int64_t worth = p.nred / 64;
             p.splits = std::max<int64_t>(1, std::min({want, worth, kMaxSplits}));
         }
@@ -43,13 +44,18 @@ ReducePlan make_reduce_plan(const hmc_tensor_desc &kept, const hmc_tensor_desc &
         p.splits = ceil_div(p.nred, p.chunk);
         return p;
     }
+    // A block of 256 lanes per output for long rows, a warp for short ones; and a warp also for long rows when
+    // there are enough outputs to give every warp of the GPU one (a lane's set-up and the group's combination
+    // are then paid once per 1/32 of a row instead of once per 1/256).
     p.group = p.nred >= 1024 ? 256 : (p.nred >= 64 ? 32 : 1);
+    if (p.group == 256 && p.nout >= kWarpRowOutputs && p.nred <= kWarpRowLength) p.group = 32;
     const int64_t lanes = p.nout * p.group;
     if (lanes < kTargetLanes) {
         const int64_t want = ceil_div(kTargetLanes, lanes);
         const int64_t worth = p.nred / (static_cast<int64_t>(p.group) * p.vec * 16);
         p.splits = std::max<int64_t>(1, std::min({want, worth, kMaxSplits}));
     }
+    p.simple = p.splits == 1 && p.group > 1 && red.ndim == 1 && p.step == 1 && p.nred % p.vec == 0 && p.nred < (int64_t{1} << 31);
     if (p.splits > 1) {
         // Whole vectors per lane and chunk, so that only a range's two ends can be partial.
         const int64_t unit = static_cast<int64_t>(p.group) * p.vec;

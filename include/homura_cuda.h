@@ -244,7 +244,7 @@ hmc_status hmc_softmax(hmc_context_t ctx, const hmc_tensor_desc *out_rows,
  * Same results, bit for bit, as hmc_reduce. The entry point allocates nothing. All calls share the one
  * array: calls that overlap on a GPU race, calls on one context are ordered by its stream. The first
  * call on a device also looks up the array's device address; make it before any stream capture. */
-#define HMC_NOALLOC_SCRATCH_BYTES 4194304
+#define HMC_NOALLOC_SCRATCH_BYTES 1048576
 hmc_status hmc_reduce_noalloc(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
                               const hmc_tensor_desc *kept, const hmc_tensor_desc *red);
 

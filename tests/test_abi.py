@@ -106,8 +106,10 @@ def test_reduce_plans_depend_on_sizes_and_strides_only():
         ws = ctypes.c_int64()
         assert lib.hmc_reduce_workspace(ctypes.byref(k), ctypes.byref(r), 0, ctypes.byref(ws)) == 0
         return kind.value, splits.value, chunk.value, ws.value
-    # rows of [16384, 4096]: a block per row, no split, no workspace
-    assert plan([(16384, 4096)], [(4096, 1)]) == (1256, 1, 4096, 0)
+    # rows of [16384, 4096]: enough rows to give every warp one, no split, no workspace
+    assert plan([(16384, 4096)], [(4096, 1)]) == (1032, 1, 4096, 0)
+    # rows of [1000, 4096]: a block per row
+    assert plan([(1000, 4096)], [(4096, 1)]) == (1256, 1, 4096, 0)
     # columns of [16384, 4096]: adjacent outputs, the reduced range cut into chunks with partials
     kind, splits, chunk, ws = plan([(4096, 1)], [(16384, 4096)])
     assert kind == 1 and splits > 1 and splits * chunk >= 16384 and ws == splits * 4096 * 16

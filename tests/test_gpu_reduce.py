@@ -22,6 +22,8 @@ SHAPES = [
     ((37, 1000), [1]), ((37, 1000), [0]), ((37, 1000), []), ((5, 7, 9), [1]), ((5, 7, 9), [0, 2]), ((5, 7, 9), [2]),
     ((1031,), []), ((3, 70000), [1]), ((70000, 3), [0]), ((70000, 3), [1]), ((300, 40), [0]), ((2, 3, 4, 5), [1, 3]),
     ((64, 2048), [1]), ((2048, 64), [0]), ((1 << 20,), []), ((4, 5), [0, 1]), ((1, 1), [0]), ((6, 0), [1]), ((0, 6), [1]),
+    # long rows folded by one warp each (many outputs): whole vectors, and a ragged row length
+    ((4800, 1028), [1]), ((4740, 1026), [1]),
 ]
 
 

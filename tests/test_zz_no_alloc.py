@@ -58,14 +58,14 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point(cuda):
 
 
 def test_a_reduction_beyond_the_built_in_scratch_is_refused(cuda):
-    # 150000 adjacent u8 outputs folded over 2048 rows: two chunks of 16-byte partials, 4.8 MB
+    # 56000 adjacent u8 outputs folded over 2048 rows: two chunks of 16-byte partials, 1.8 MB
     k, r, o = ffi.hmc_tensor_desc(), ffi.hmc_tensor_desc(), ffi.hmc_tensor_desc()
     dummy = cuda.empty((16,), U8)
     for d, dt in ((k, U8), (r, U8), (o, I64)):
         d.data, d.dtype, d.ndim = dummy.storage.ptr, dt, 1
-    k.sizes[0], k.strides[0] = 150000, 1
-    r.sizes[0], r.strides[0] = 2048, 150000
-    o.sizes[0], o.strides[0] = 150000, 1
+    k.sizes[0], k.strides[0] = 56000, 1
+    r.sizes[0], r.strides[0] = 2048, 56000
+    o.sizes[0], o.strides[0] = 56000, 1
     need = ctypes.c_int64()
     assert cuda.lib.hmc_reduce_workspace(ctypes.byref(k), ctypes.byref(r), 0, ctypes.byref(need)) == ffi.HMC_OK
     assert need.value > ffi.HMC_NOALLOC_SCRATCH_BYTES
