@@ -520,6 +520,74 @@ class CudaBackend:
         self._check(self.lib.hmc_softmax(self.ctx, o, s, n, so, si, int(log), ws.ptr if ws else None,
                                          ws.nbytes if ws else 0))
 
+    # ---- the callers either side of the path: samplers, the mask builder, flip ----
+    def random_uniform(self, out: TensorData, gen: "Generator", low: float, high: float) -> None:
+        """`out` (contiguous, float) filled with uniform samples of [low, high): rocm_random_tensor's Uniform arm
+        (src/ops/random.rs:303-311)."""
+        assert out.is_contiguous() and out.dtype in FLOATS
+        per_block = 2 if out.dtype == F64 else 4
+        seed, start = gen.reserve(-(-out.numel // per_block))
+        self._check(self.lib.hmc_random_uniform(self.ctx, _flat_desc(out), seed, start, float(low), float(high)))
+
+    def random_normal(self, out: TensorData, gen: "Generator", mean: float, std: float) -> None:
+        """src/ops/random.rs:312-317."""
+        assert out.is_contiguous() and out.dtype in FLOATS
+        seed, start = gen.reserve(-(-out.numel // 2))
+        self._check(self.lib.hmc_random_normal(self.ctx, _flat_desc(out), seed, start, float(mean), float(std)))
+
+    def random_int(self, out: TensorData, gen: "Generator", low: int, high: int) -> None:
+        """`out` (contiguous, I64) filled with uniform integers of [low, high): the batches of rocm_random_tensor's
+        Int arm (src/ops/random.rs:318-356): each reserves a block per two values still needed, the device reports
+        how many words it accepted, and the tail of the last batch is dropped."""
+        assert out.is_contiguous() and out.dtype == I64 and low < high
+        n = out.numel
+        rng, threshold = int_range(low, high)
+        ws = None
+        if threshold != 0 and n > 0:
+            tiles = -(-(-(-n // 2)) // ffi.HMC_RANDOM_INT_TILE)
+            ws = self.storage((2 * tiles + 1) * 8)
+        flat = out.reshape(n) if n != 1 else out
+        done = 0
+        while done < n:
+            needed = n - done
+            blocks = -(-needed // 2)
+            seed, start = gen.reserve(blocks)
+            part = flat.narrow(0, done, needed) if n != 1 else flat
+            self._check(self.lib.hmc_random_int(self.ctx, _flat_desc(part), seed, start, blocks, low, rng, threshold,
+                                                ws.ptr if ws else None))
+            if ws is None:
+                done += needed
+            else:
+                tiles = -(-blocks // ffi.HMC_RANDOM_INT_TILE)
+                accepted = np.empty(1, dtype=np.uint64)
+                self._check(self.lib.hmc_copy_to_host(self.ctx, accepted.ctypes.data, ws.ptr + 2 * tiles * 8, 8))
+                done += min(int(accepted[0]), needed)
+
+    def triangle(self, out: TensorData, src: TensorData, diagonal: int, upper: bool) -> None:
+        """tril / triu over the last two dimensions (src/backend/rocm/elementwise.rs, hmr_triangle): the batch
+        dimensions are merged, the last two are passed as they are."""
+        assert tuple(out.shape) == tuple(src.shape) and len(src.shape) >= 2 and out.dtype == src.dtype
+        if src.numel == 0:
+            return
+        batch = merge_dims(src.shape[:-2], [out.strides[:-2], src.strides[:-2]])
+        dims = list(batch) + [(src.shape[-2], [out.strides[-2], src.strides[-2]]), (src.shape[-1], [out.strides[-1], src.strides[-1]])]
+        o, i = descs_with_dims("triangle", [out, src], [out.offset, src.offset], dims)
+        self._check(self.lib.hmc_triangle(self.ctx, o, i, int(diagonal), int(bool(upper))))
+
+    def flip(self, out: TensorData, src: TensorData, dims: Sequence[int]) -> None:
+        """out = src flipped along `dims` (src/backend/rocm/copy.rs flip: the source is described with negative strides
+        along the flipped dimensions and its offset at the element that comes first)."""
+        assert tuple(out.shape) == tuple(src.shape) and out.dtype == src.dtype
+        if src.numel == 0:
+            return
+        strides, offset = list(src.strides), src.offset
+        for d in dims:
+            offset += (src.shape[d] - 1) * strides[d]
+            strides[d] = -strides[d]
+        flipped = TensorData(src.storage, src.dtype, tuple(src.shape), tuple(strides), offset)
+        o, i = descs("flip", [out, flipped])
+        self._check(self.lib.hmc_flip(self.ctx, o, i))
+
     def adamw_step(self, param: TensorData, grad: TensorData, exp_avg: TensorData, exp_avg_sq: TensorData, *,
                    lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: float) -> None:
         """The fused AdamW update (hmc_adamw_step) with the scalars homura's optimizer derives
@@ -529,6 +597,34 @@ class CudaBackend:
             return
         sc = adamw_scalars(param.dtype, lr, beta1, beta2, eps, weight_decay, step)
         self._check(self.lib.hmc_adamw_step(self.ctx, d[0], d[1], d[2], d[3], ctypes.byref(sc)))
+
+
+DEFAULT_SEED = 67280421310721  # PyTorch's default seed, as homura uses it (src/ops/random.rs:15-16)
+
+
+class Generator:
+    """homura's process-wide Philox generator (src/ops/random.rs:18-27, 53-73): a seed and the number of 128-bit
+    blocks handed out since seeding; samplers reserve their blocks before they launch."""
+
+    def __init__(self, seed: int = DEFAULT_SEED):
+        self.manual_seed(seed)
+
+    def manual_seed(self, seed: int) -> None:
+        self.seed = seed & (2**64 - 1)
+        self.offset = 0
+
+    def reserve(self, blocks: int) -> tuple[int, int]:
+        start = self.offset
+        self.offset = (self.offset + blocks) & (2**64 - 1)
+        return self.seed, start
+
+
+def int_range(low: int, high: int) -> tuple[int, int]:
+    """(number of values in [low, high), threshold below which a 64-bit word is rejected).
+    src/ops/random.rs:201-207."""
+    rng = high - low
+    assert 1 <= rng <= 2**64 - 1
+    return rng, (2**64 - rng) % rng
 
 
 def _flat_desc(t: TensorData) -> hmc_tensor_desc:

@@ -233,6 +233,48 @@ hmc_status hmc_softmax(hmc_context_t ctx, const hmc_tensor_desc *out_rows,
                        int64_t src_stride, int32_t log, void *workspace,
                        int64_t workspace_bytes);
 
+/* ---- the callers either side of the path: samplers and the mask builder ---- */
+
+/* Random sampling with the Philox4x32-10 counter of src/ops/random.rs:29-51: block n has the counter
+ * [n, n >> 32, 0, 0] under the key [seed, seed >> 32]; the caller reserves the blocks of a call from
+ * `offset` on, as the CPU does (random.rs:65-83), and advances its generator. `out` is flat and
+ * contiguous (ndim <= 1, stride 1).
+ * hmc_random_uniform (sample_float, random.rs:162-183; the clamp at random.rs:268-277): from + u * (to - from)
+ *   in f64 for a float `out`; u comes from 53 bits (two words per value, two values per block) for F64 and
+ *   from the dtype's significand bits (one word per value, four per block) otherwise; the result is rounded
+ *   to the dtype, and one that reaches `to` (with from < to) becomes `from`. Bit for bit the CPU's samples.
+ * hmc_random_normal (random.rs:184-197): Box-Muller in f64, two values per block (cosine, then sine),
+ *   rounded to the dtype; log, cos and sin are this library's, so a sample may differ from the CPU's in the
+ *   last place.
+ * csrc/homura_rocm.h:265-281 */
+hmc_status hmc_random_uniform(hmc_context_t ctx, const hmc_tensor_desc *out, uint64_t seed, uint64_t offset,
+                              double from, double to);
+hmc_status hmc_random_normal(hmc_context_t ctx, const hmc_tensor_desc *out, uint64_t seed, uint64_t offset,
+                             double mean, double std);
+
+/* The Philox blocks of one tile of hmc_random_int. */
+#define HMC_RANDOM_INT_TILE 256
+
+/* One batch of the CPU's integer rejection sampling (sample_int, random.rs:213-238): the 64-bit words of
+ * `blocks` blocks from `offset` on, two per block, [w0 w1] then [w2 w3]; the words >= `threshold`, in that
+ * order, become low + word % range (wrapping) and fill the I64 `out` until it is full; the rest are dropped.
+ * With threshold 0 every word is taken and `workspace` may be NULL. Otherwise `workspace` holds
+ * 2 * tiles + 1 64-bit words of device memory, tiles = ceil(blocks / HMC_RANDOM_INT_TILE), and the number of
+ * words >= threshold of the batch (which may exceed out's elements) is left in its last word.
+ * csrc/homura_rocm.h:283-295 */
+hmc_status hmc_random_int(hmc_context_t ctx, const hmc_tensor_desc *out, uint64_t seed, uint64_t offset,
+                          uint64_t blocks, int64_t low, uint64_t range, uint64_t threshold, void *workspace);
+
+/* cpu::triangle (src/backend/cpu/misc.rs:347-381): out = src where the column minus the row index (the last
+ * two dimensions, ndim >= 2) is at least (upper) or at most `diagonal`, else 0; tril / triu, and the causal
+ * mask in front of a softmax. csrc/homura_rocm.h:257-260 */
+hmc_status hmc_triangle(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src,
+                        int64_t diagonal, int32_t upper);
+
+/* cpu::flip (src/backend/cpu/misc.rs:384-411): out = src for one dtype, where src's strides may be negative
+ * (the flipped dimensions, with the offset at the element that comes first). csrc/homura_rocm.h:262-263 */
+hmc_status hmc_flip(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src);
+
 /* ---- additions of this backend (no counterpart in csrc/homura_rocm.h) ---- */
 
 /* hmc_reduce without a workspace argument, for callers that cannot allocate one when they need the

@@ -863,6 +863,164 @@ int orc_adamw_step(int32_t dtype, int64_t n, void *param, const void *grad, void
     return rc;
 }
 
+// ---- random sampling (src/ops/random.rs) ----
+
+// One Philox4x32-10 block. src/ops/random.rs:29-51.
+void orc_philox(const uint32_t counter[4], const uint32_t key[2], uint32_t out[4]) {
+    const uint64_t M0 = 0xD2511F53ull, M1 = 0xCD9E8D57ull;
+    const uint32_t W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+    uint32_t c[4] = {counter[0], counter[1], counter[2], counter[3]};
+    uint32_t k[2] = {key[0], key[1]};
+    for (int round = 0; round < 10; ++round) {
+        if (round > 0) { k[0] += W0; k[1] += W1; }
+        const uint64_t p0 = M0 * c[0], p1 = M1 * c[2];
+        const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k[0], n1 = (uint32_t)p1;
+        const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k[1], n3 = (uint32_t)p0;
+        c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+    }
+    for (int i = 0; i < 4; ++i) out[i] = c[i];
+}
+
+}  // extern "C"
+
+namespace {
+// Block n of a generator seeded with `seed` (reserve, src/ops/random.rs:75-83).
+void block_of(uint64_t seed, uint64_t n, uint32_t out[4]) {
+    const uint32_t counter[4] = {(uint32_t)n, (uint32_t)(n >> 32), 0, 0};
+    const uint32_t key[2] = {(uint32_t)seed, (uint32_t)(seed >> 32)};
+    orc_philox(counter, key, out);
+}
+// src/ops/random.rs:86-95.
+double unit_f64(uint32_t hi, uint32_t lo) {
+    const uint64_t bits = ((uint64_t)hi << 21) ^ ((uint64_t)lo >> 11);
+    return (double)bits * (1.0 / 9007199254740992.0);
+}
+double unit_bits(uint32_t x, int bits) { return (double)(x >> (32 - bits)) / (double)(1ull << bits); }
+int float_digits(int dtype) { return dtype == HMC_F16 ? 11 : dtype == HMC_BF16 ? 8 : dtype == HMC_F32 ? 24 : 53; }
+}  // namespace
+
+extern "C" {
+
+// sample_float's Uniform arm and the conversion of random_tensor: n values of a float dtype into the flat
+// `out`, from block `offset` on. src/ops/random.rs:162-183, 262-281.
+int orc_random_uniform(int32_t dtype, void *out, int64_t n, uint64_t seed, uint64_t offset, double from, double to) {
+    return dispatch_float(dtype, [&](auto t) {
+        using T = decltype(t);
+        T *po = (T *)out;
+        const int per_block = dtype == HMC_F64 ? 2 : 4;
+        const int bits = float_digits(dtype);
+        for (int64_t i = 0; i < n; ++i) {
+            uint32_t b[4];
+            block_of(seed, offset + (uint64_t)(i / per_block), b);
+            const int j = (int)(i % per_block);
+            const double u = per_block == 2 ? unit_f64(b[2 * j], b[2 * j + 1]) : unit_bits(b[j], bits);
+            const double x = from + u * (to - from);
+            T v = from_f64<T>(x);
+            if (from < to && to_f64(v) >= to) v = from_f64<T>(from);
+            po[i] = v;
+        }
+        return 0;
+    });
+}
+
+// sample_float's Normal arm. src/ops/random.rs:184-197.
+int orc_random_normal(int32_t dtype, void *out, int64_t n, uint64_t seed, uint64_t offset, double mean, double std_) {
+    return dispatch_float(dtype, [&](auto t) {
+        using T = decltype(t);
+        T *po = (T *)out;
+        for (int64_t i = 0; i < n; i += 2) {
+            uint32_t b[4];
+            block_of(seed, offset + (uint64_t)(i / 2), b);
+            const double u1 = 1.0 - unit_f64(b[0], b[1]);
+            const double u2 = unit_f64(b[2], b[3]);
+            const double r = std::sqrt(-2.0 * std::log(u1));
+            const double theta = 2.0 * 3.14159265358979323846 * u2;
+            po[i] = from_f64<T>(mean + std_ * r * std::cos(theta));
+            if (i + 1 < n) po[i + 1] = from_f64<T>(mean + std_ * r * std::sin(theta));
+        }
+        return 0;
+    });
+}
+
+// One batch of sample_int (src/ops/random.rs:213-238): the words of `blocks` blocks from `offset` on, in the
+// order the CPU pops them ([w0 w1], then [w2 w3] of each block); words >= threshold become
+// low + word % range and fill out[0 .. nout); returns how many words of the batch were >= threshold.
+int64_t orc_random_int_batch(int64_t *out, int64_t nout, uint64_t seed, uint64_t offset, uint64_t blocks, int64_t low,
+                             uint64_t range, uint64_t threshold) {
+    int64_t accepted = 0;
+    for (uint64_t i = 0; i < blocks; ++i) {
+        uint32_t b[4];
+        block_of(seed, offset + i, b);
+        const uint64_t w[2] = {((uint64_t)b[0] << 32) | b[1], ((uint64_t)b[2] << 32) | b[3]};
+        for (int j = 0; j < 2; ++j) {
+            if (w[j] >= threshold) {
+                if (accepted < nout) out[accepted] = (int64_t)((uint64_t)low + w[j] % range);
+                accepted += 1;
+            }
+        }
+    }
+    return accepted;
+}
+
+// The whole of sample_int: batches until n values are there; *blocks_used gets the blocks reserved.
+// src/ops/random.rs:213-238 (and int_range, :201-207, for range and threshold).
+int orc_random_int(int64_t *out, int64_t n, uint64_t seed, uint64_t offset, int64_t low, int64_t high, uint64_t *blocks_used) {
+    const uint64_t range = (uint64_t)high - (uint64_t)low;
+    const uint64_t threshold = (0 - range) % range;
+    int64_t done = 0;
+    uint64_t used = 0;
+    while (done < n) {
+        const int64_t needed = n - done;
+        const uint64_t blocks = (uint64_t)((needed + 1) / 2);
+        const int64_t got = orc_random_int_batch(out + done, needed, seed, offset + used, blocks, low, range, threshold);
+        used += blocks;
+        done += got < needed ? got : needed;
+    }
+    if (blocks_used) *blocks_used = used;
+    return 0;
+}
+
+// cpu::triangle. src/backend/cpu/misc.rs:347-381.
+int orc_triangle(const hmc_tensor_desc *out, const hmc_tensor_desc *src, int64_t diagonal, int32_t upper) {
+    if (out->dtype != src->dtype || !same_shape(out, src) || src->ndim < 2) return 2;
+    const int nd = src->ndim;
+    const int64_t rows = src->sizes[nd - 2], cols = src->sizes[nd - 1];
+    return dispatch_all(src->dtype, [&](auto t) {
+        using T = decltype(t);
+        const T *ps = (const T *)src->data;
+        T *po = (T *)out->data;
+        const int64_t *st[2] = {out->strides, src->strides};
+        int64_t base[2] = {out->offset, src->offset};
+        walk<2>(nd - 2, src->sizes, st, base, [&](const int64_t *oi) {
+            for (int64_t r = 0; r < rows; ++r) {
+                for (int64_t c = 0; c < cols; ++c) {
+                    const int64_t d = c - r;
+                    const bool keep = upper ? d >= diagonal : d <= diagonal;
+                    T zero{};
+                    po[oi[0] + r * out->strides[nd - 2] + c * out->strides[nd - 1]] =
+                        keep ? ps[oi[1] + r * src->strides[nd - 2] + c * src->strides[nd - 1]] : zero;
+                }
+            }
+        });
+        return 0;
+    });
+}
+
+// cpu::flip, given like the device entry point: src's strides are negative along the flipped dimensions and
+// its offset is at the element that comes first. src/backend/cpu/misc.rs:384-411.
+int orc_flip(const hmc_tensor_desc *out, const hmc_tensor_desc *src) {
+    if (out->dtype != src->dtype || !same_shape(out, src)) return 2;
+    return dispatch_all(src->dtype, [&](auto t) {
+        using T = decltype(t);
+        const T *ps = (const T *)src->data;
+        T *po = (T *)out->data;
+        const int64_t *st[2] = {out->strides, src->strides};
+        int64_t base[2] = {out->offset, src->offset};
+        walk<2>(src->ndim, src->sizes, st, base, [&](const int64_t *oi) { po[oi[0]] = ps[oi[1]]; });
+        return 0;
+    });
+}
+
 // Scalar conversions exposed for the tests of the cast tables (src/dtype.rs:543-665).
 uint16_t orc_f32_to_f16(float f) { return f32_to_f16(f); }
 uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16(f); }

@@ -32,6 +32,9 @@ def _load_oracle():
         "orc_reduce": [i32, D, D, D], "orc_var": [D, D, D, f64, i32], "orc_arg_reduce": [D, D, D, D, i32],
         "orc_softmax": [D, D, i64, i64, i64, i32],
         "orc_adamw_step": [i32, i64, vp, vp, vp, vp, f64, f64, f64, f64, f64, f64],
+        "orc_random_uniform": [i32, vp, i64, u64, u64, f64, f64], "orc_random_normal": [i32, vp, i64, u64, u64, f64, f64],
+        "orc_random_int": [vp, i64, u64, u64, i64, i64, ctypes.POINTER(u64)],
+        "orc_triangle": [D, D, i64, i32], "orc_flip": [D, D],
     }
     for name, args in protos.items():
         fn = getattr(lib, name)
@@ -41,6 +44,8 @@ def _load_oracle():
     lib.orc_f16_to_f32.restype, lib.orc_f16_to_f32.argtypes = ctypes.c_float, [ctypes.c_uint16]
     lib.orc_bf16_to_f32.restype, lib.orc_bf16_to_f32.argtypes = ctypes.c_float, [ctypes.c_uint16]
     lib.orc_erf.restype, lib.orc_erf.argtypes = f64, [f64]
+    lib.orc_philox.restype, lib.orc_philox.argtypes = None, [ctypes.POINTER(ctypes.c_uint32)] * 3
+    lib.orc_random_int_batch.restype, lib.orc_random_int_batch.argtypes = i64, [vp, i64, u64, u64, u64, i64, u64, u64]
     return lib
 
 
@@ -174,6 +179,45 @@ class OracleBackend:
             return
         (o, s), n, so, si = ln
         self._check(self.lib.orc_softmax(o, s, n, so, si, int(log)))
+
+    # ---- samplers, the mask builder, flip ----
+    def _data(self, t: TensorData) -> int:
+        assert t.is_contiguous()
+        return t.storage.array.ctypes.data + t.offset * SIZE[t.dtype]
+
+    def random_uniform(self, out, gen, low, high):
+        per_block = 2 if out.dtype == ffi.HMC_F64 else 4
+        seed, start = gen.reserve(-(-out.numel // per_block))
+        self._check(self.lib.orc_random_uniform(out.dtype, self._data(out), out.numel, seed, start, float(low), float(high)))
+
+    def random_normal(self, out, gen, mean, std):
+        seed, start = gen.reserve(-(-out.numel // 2))
+        self._check(self.lib.orc_random_normal(out.dtype, self._data(out), out.numel, seed, start, float(mean), float(std)))
+
+    def random_int(self, out, gen, low, high):
+        used = ctypes.c_uint64()
+        self._check(self.lib.orc_random_int(self._data(out), out.numel, gen.seed, gen.offset, low, high, ctypes.byref(used)))
+        gen.reserve(used.value)
+
+    def triangle(self, out, src, diagonal, upper):
+        from homura_b200.host import descs_with_dims, merge_dims
+        if src.numel == 0:
+            return
+        batch = merge_dims(src.shape[:-2], [out.strides[:-2], src.strides[:-2]])
+        dims = list(batch) + [(src.shape[-2], [out.strides[-2], src.strides[-2]]), (src.shape[-1], [out.strides[-1], src.strides[-1]])]
+        o, i = descs_with_dims("triangle", [out, src], [out.offset, src.offset], dims)
+        self._check(self.lib.orc_triangle(o, i, int(diagonal), int(bool(upper))))
+
+    def flip(self, out, src, dims):
+        if src.numel == 0:
+            return
+        strides, offset = list(src.strides), src.offset
+        for d in dims:
+            offset += (src.shape[d] - 1) * strides[d]
+            strides[d] = -strides[d]
+        flipped = TensorData(src.storage, src.dtype, tuple(src.shape), tuple(strides), offset)
+        o, i = descs("flip", [out, flipped])
+        self._check(self.lib.orc_flip(o, i))
 
     # ---- the sharded reductions' local and combine steps, restated on the host for the CPU tests ----
     def storage(self, nbytes: int) -> Storage:
