@@ -312,6 +312,49 @@ class C5Workload:
             f()
 
 
+class InputsWorkload:
+    """The step before the path in every config: the samplers that make the inputs (rand bf16 [8192, 8192],
+    randn f32 [16384, 4096], randint over a range that rejects words and one that does not) and the causal mask
+    in front of C4's softmax (triu on f32 [64, 2048, 2048], and the Bool mask itself). Bytes are those written,
+    plus the triangle's reads of the kept half."""
+
+    name = "inputs_samplers_and_mask"
+
+    def __init__(self, be, seed: int = 0):
+        from homura_b200.host import BF16, BOOL, F32, I64, Generator
+        self.be = be
+        self.gen = Generator(1234 + seed)
+        self.u = be.empty((8192 * 8192,), BF16)
+        self.n = be.empty((16384 * 4096,), F32)
+        self.i = be.empty((1 << 26,), I64)
+        b, m = 64, 2048
+        self.logits = be.empty((b, m, m), F32)
+        be.fill(self.logits, 1.0)
+        self.masked = be.empty((b, m, m), F32)
+        self.ones = be.empty((m, m), BOOL)
+        be.fill(self.ones, True)
+        self.mask = be.empty((m, m), BOOL)
+        e = b * m * m
+        self.op_bytes = {"rand_bf16": 2 * self.u.numel, "randn_f32": 4 * self.n.numel, "randint_pow2": 8 * self.i.numel,
+                         "randint_reject": 8 * self.i.numel, "triu_f32": 4 * e + 2 * e, "mask_bool": m * m + m * m // 2}
+        self.launches_per_step = 9
+
+    def ops(self):
+        be = self.be
+        return [
+            ("rand_bf16", lambda: be.random_uniform(self.u, self.gen, 0.0, 1.0)),
+            ("randn_f32", lambda: be.random_normal(self.n, self.gen, 0.0, 1.0)),
+            ("randint_pow2", lambda: be.random_int(self.i, self.gen, 0, 1 << 16)),
+            ("randint_reject", lambda: be.random_int(self.i, self.gen, -3, 50257)),
+            ("triu_f32", lambda: be.triangle(self.masked, self.logits, 1, True)),
+            ("mask_bool", lambda: be.triangle(self.mask, self.ones, 1, True)),
+        ]
+
+    def step(self):
+        for _, f in self.ops():
+            f()
+
+
 class Events:
     def __init__(self, be):
         self.be = be
@@ -394,7 +437,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "inputs"])
     ap.add_argument("--c4-batch", type=int, default=256,
                     help="matrices of [2048, 2048] logits in the c4 workload (256 = [8, 32, 2048, 2048]); a smaller "
                          "number keeps a profiler capture short")
@@ -434,7 +477,7 @@ def main() -> None:
         if args.workload == "c4":
             w = C4Workload(be, seed=rank, batch=args.c4_batch)
         else:
-            w = {"c3": C3Workload, "c5": C5Workload}[args.workload](be, seed=rank)
+            w = {"c3": C3Workload, "c5": C5Workload, "inputs": InputsWorkload}[args.workload](be, seed=rank)
         workload_name, step_bytes = w.name, sum(w.op_bytes.values())
         if args.workload == "c4" and args.c4_batch != 256:
             workload_name += f"_batch{args.c4_batch}"

@@ -38,12 +38,12 @@ __device__ __forceinline__ Words4 philox_block(uint64_t n, uint64_t seed) {
             k0 += kW0;
             k1 += kW1;
         }
-        const uint32_t h0 = __umulhi(kM0, c0), l0 = kM0 * c0;
-        const uint32_t h1 = __umulhi(kM1, c2), l1 = kM1 * c2;
-        c0 = h1 ^ c1 ^ k0;
-        c1 = l1;
-        c2 = h0 ^ c3 ^ k1;
-        c3 = l0;
+        const uint64_t p0 = static_cast<uint64_t>(kM0) * c0;  // one wide multiplication each
+        const uint64_t p1 = static_cast<uint64_t>(kM1) * c2;
+        c0 = static_cast<uint32_t>(p1 >> 32) ^ c1 ^ k0;
+        c1 = static_cast<uint32_t>(p1);
+        c2 = static_cast<uint32_t>(p0 >> 32) ^ c3 ^ k1;
+        c3 = static_cast<uint32_t>(p0);
     }
     return Words4{{c0, c1, c2, c3}};
 }

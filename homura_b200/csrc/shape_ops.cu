@@ -31,15 +31,21 @@ __global__ void __launch_bounds__(kTriThreads) triangle_kernel(const __grid_cons
     W *out = reinterpret_cast<W *>(a.out);
     const W *src = reinterpret_cast<const W *>(a.src);
     for (int64_t line = blockIdx.y; line < a.lines; line += gridDim.y) {
-        int64_t batch = line / a.rows;
+        // (32-bit division where the line number allows: a 64-bit one costs several times as much, per thread)
+        int64_t batch = a.lines < (int64_t{1} << 31) ? static_cast<int64_t>(static_cast<uint32_t>(line) / static_cast<uint32_t>(a.rows))
+                                                      : line / a.rows;
         const int64_t r = line - batch * a.rows;
         int64_t oo = r * a.out_row, so = r * a.src_row;
-        for (int d = a.nbatch - 1; d >= 0; --d) {
+        for (int d = a.nbatch - 1; d > 0; --d) {
             const int64_t q = batch / a.batch_sizes[d];
             const int64_t i = batch - q * a.batch_sizes[d];
             oo += i * a.out_batch[d];
             so += i * a.src_batch[d];
             batch = q;
+        }
+        if (a.nbatch > 0) {
+            oo += batch * a.out_batch[0];
+            so += batch * a.src_batch[0];
         }
         // kept columns: c - r >= diagonal (upper) or c - r <= diagonal (lower)
         const int64_t edge = r + a.diagonal;  // upper keeps c >= edge, lower keeps c <= edge
@@ -138,7 +144,8 @@ HMC_API hmc_status hmc_triangle(hmc_context_t ctx, const hmc_tensor_desc *out, c
         const int64_t reach = a.rows + a.cols + 1;
         if (a.diagonal > reach) a.diagonal = reach;
         if (a.diagonal < -reach) a.diagonal = -reach;
-        const int64_t per_line = ceil_div(a.cols, kTriThreads * (16 / es));
+        // up to four vectors per thread, so that a thread's share of finding its line is spread over 64 bytes
+        const int64_t per_line = ceil_div(a.cols, 4 * kTriThreads * (16 / es));
         dim3 grid(static_cast<unsigned>(per_line < 1 ? 1 : (per_line < 65535 ? per_line : 65535)),
                   static_cast<unsigned>(a.lines < 65535 ? a.lines : 65535));
         return by_size(src->dtype, [&](auto w) -> hmc_status {
