@@ -132,6 +132,25 @@ __device__ __forceinline__ typename Op::Acc group_combine(const Op &op, typename
     }
 }
 
+// (value, index); index < 0 marks the empty fold. src/backend/cpu/reduce.rs:75-86.
+template <class TT>
+struct alignas(16) Best {
+    TT v;
+    int64_t i;
+};
+
+template <class T> __device__ __forceinline__ auto order_key(T x) {
+    if constexpr (std::is_same_v<T, F16> || std::is_same_v<T, BF16>) return up(x);
+    else if constexpr (std::is_same_v<T, Bool>) return x.b;
+    else return x;
+}
+
+template <class TT, bool MAX> struct Extreme;
+template <class Op> struct is_extreme : std::false_type {};
+template <class TT, bool MAX> struct is_extreme<Extreme<TT, MAX>> : std::true_type {};
+template <class Op> struct extreme_is_max : std::false_type {};
+template <class TT> struct extreme_is_max<Extreme<TT, true>> : std::true_type {};
+
 // acc folded with element x (index j of output o), where j is larger than every index already in acc: what a
 // lane does element by element. Ops may give a cheaper form of it than combine(acc, load(x)).
 template <class Op, class = void> struct has_step : std::false_type {};
@@ -191,10 +210,40 @@ __device__ __forceinline__ typename Op::Acc fold_range(const Op &op, const Reduc
                 RVec<T, VEC> x[UNR];
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VEC> *>(p + (v + u * G) * VEC);
+                bool general = true;
+                if constexpr (is_extreme<Op>::value) {
+                    // The best of the batch by plain comparisons (a later element wins only if strictly better), then
+                    // one general combination with what came before; a NaN in the batch (seen in the sum of the
+                    // keys) sends the batch through the general step instead.
+                    constexpr bool kMax = extreme_is_max<Op>::value;
+                    auto best_key = order_key(x[0].v[0]);
+                    T best = x[0].v[0];
+                    int code = 0;
+                    float alarm = 0.0f;
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) {
+                    for (int u = 0; u < UNR; ++u) {
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x[u].v[e], o, first + (v + u * G) * VEC + e);
+                        for (int e = 0; e < VEC; ++e) {
+                            const auto k = order_key(x[u].v[e]);
+                            if constexpr (Tr<T>::kind == kFloat) alarm += static_cast<float>(k);
+                            const bool better = kMax ? k > best_key : k < best_key;
+                            best_key = better ? k : best_key;
+                            best = better ? x[u].v[e] : best;
+                            code = better ? u * VEC + e : code;
+                        }
+                    }
+                    if (alarm == alarm) {
+                        const int64_t at = first + (v + (code / VEC) * G) * VEC + code % VEC;
+                        acc = op.combine(acc, Acc{best, at});
+                        general = false;
+                    }
+                }
+                if (general) {
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x[u].v[e], o, first + (v + u * G) * VEC + e);
+                    }
                 }
                 v += UNR * G;
             }
@@ -223,19 +272,6 @@ __device__ __forceinline__ typename Op::Acc fold_range(const Op &op, const Reduc
         }
     }
     return acc;
-}
-
-// (value, index); index < 0 marks the empty fold. src/backend/cpu/reduce.rs:75-86.
-template <class TT>
-struct alignas(16) Best {
-    TT v;
-    int64_t i;
-};
-
-template <class T> __device__ __forceinline__ auto order_key(T x) {
-    if constexpr (std::is_same_v<T, F16> || std::is_same_v<T, BF16>) return up(x);
-    else if constexpr (std::is_same_v<T, Bool>) return x.b;
-    else return x;
 }
 
 // One lane's share of a simple row (plan.simple): vectors lane, lane + G, ... of the nvec vectors at p, in
@@ -267,9 +303,6 @@ __device__ __forceinline__ typename Op::Acc fold_simple_row(const Op &op, const 
     return acc;
 }
 
-template <class TT, bool MAX> struct Extreme;
-template <class Op> struct is_extreme : std::false_type {};
-template <class TT, bool MAX> struct is_extreme<Extreme<TT, MAX>> : std::true_type {};
 
 // The same for max / min / argmax / argmin, where the general step (first NaN, then first of equals, a 64-bit
 // index) costs about forty instructions per element. Here a lane keeps the best key, its raw value and a
@@ -642,6 +675,7 @@ struct VarSink {
 // Internal launchers, one translation unit each.
 hmc_status reduce_float(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out, ReduceArgs &a);
 hmc_status reduce_float_partial(hmc_context_t ctx, int32_t op, double *partial, ReduceArgs &a);
+hmc_status reduce_var_partial(hmc_context_t ctx, double *partial, ReduceArgs &a, const double *means);
 hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs &a, double correction, int take_sqrt,
                       double *means);
 hmc_status reduce_int(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out, ReduceArgs &a);

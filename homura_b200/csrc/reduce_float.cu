@@ -20,6 +20,14 @@ hmc_status reduce_float_partial(hmc_context_t ctx, int32_t op, double *partial, 
     });
 }
 
+// The f64 sums of squared deviations from given f64 means, one per output (a shard's share of a variance).
+hmc_status reduce_var_partial(hmc_context_t ctx, double *partial, ReduceArgs &a, const double *means) {
+    return dispatch_float(a.kept.dtype, [&](auto t) {
+        using T = decltype(t);
+        return launch_reduce(a, SquaredDeviation<T>{means, 0.0}, FloatSink<T>{nullptr, partial, 3}, ctx->stream);
+    });
+}
+
 namespace {
 
 // Sum, mean and squared deviations of each output in one kernel, for plans without chunks: the

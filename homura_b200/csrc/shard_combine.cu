@@ -19,6 +19,25 @@ __global__ void combine_float_kernel(T *out, const double *gathered, int ranks, 
     }
 }
 
+__global__ void combine_means_kernel(double *means, const double *gathered, int ranks, int64_t nout, double count) {
+    for (int64_t o = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; o < nout;
+         o += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        double acc = 0.0;
+        for (int r = 0; r < ranks; ++r) acc += gathered[r * nout + o];
+        means[o] = acc / count;
+    }
+}
+
+template <class T>
+__global__ void combine_var_kernel(VarSink<T> sink, const double *gathered, int ranks, int64_t nout, int64_t count) {
+    for (int64_t o = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; o < nout;
+         o += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        double acc = 0.0;
+        for (int r = 0; r < ranks; ++r) acc += gathered[r * nout + o];
+        sink.put(o, acc, count);
+    }
+}
+
 __global__ void combine_int_kernel(int64_t *out, const int64_t *gathered, int ranks, int64_t nout, int prod) {
     for (int64_t o = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; o < nout;
          o += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -171,6 +190,61 @@ HMC_API hmc_status hmc_shard_combine_extreme(hmc_context_t ctx, int32_t is_max, 
             const T *gv = static_cast<const T *>(gathered_values);
             if (is_max) combine_extreme_kernel<T, true><<<blocks_for(nout), 256, 0, ctx->stream>>>(v, i, gv, gathered_indices, offsets, ranks, nout);
             else combine_extreme_kernel<T, false><<<blocks_for(nout), 256, 0, ctx->stream>>>(v, i, gv, gathered_indices, offsets, ranks, nout);
+            return launch_status("shard combine launch");
+        });
+    });
+}
+
+HMC_API hmc_status hmc_shard_combine_means(hmc_context_t ctx, double *means, const double *gathered, int32_t ranks, int64_t nout,
+                                           int64_t total_count) {
+    return guarded([&]() -> hmc_status {
+        HMC_ENTER(ctx);
+        if (ranks < 1 || nout < 0 || total_count < 0) return fail(HMC_INVALID, "bad rank, output or element count");
+        if (nout == 0) return HMC_OK;
+        if (means == nullptr || gathered == nullptr) return fail(HMC_INVALID, "null means or partials");
+        combine_means_kernel<<<blocks_for(nout), 256, 0, ctx->stream>>>(means, gathered, ranks, nout, static_cast<double>(total_count));
+        return launch_status("shard combine launch");
+    });
+}
+
+HMC_API hmc_status hmc_var_partial(hmc_context_t ctx, double *partial, const hmc_tensor_desc *kept, const hmc_tensor_desc *red,
+                                   const double *means, void *workspace, int64_t workspace_bytes) {
+    return guarded([&]() -> hmc_status {
+        HMC_ENTER(ctx);
+        hmc_status s = check_desc(kept, "the kept dimensions");
+        if (s != HMC_OK) return s;
+        s = check_desc(red, "the reduced dimensions");
+        if (s != HMC_OK) return s;
+        if (!dtype_is_float(kept->dtype) || red->dtype != kept->dtype) return fail(HMC_INVALID, "hmc_var_partial takes a floating point tensor");
+        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr};
+        if (a.plan.nout == 0) return HMC_OK;
+        if (partial == nullptr || means == nullptr) return fail(HMC_INVALID, "null partials or means");
+        if (a.plan.nred > 0 && kept->data == nullptr) return fail(HMC_INVALID, "null data pointer");
+        const int64_t need = plan_partial_bytes(a.plan);
+        if (need > 0 && (workspace == nullptr || workspace_bytes < need)) {
+            return fail(HMC_INVALID, "the workspace of a reduction is too small: " + std::to_string(need) + " bytes needed");
+        }
+        a.partials = need > 0 ? workspace : nullptr;
+        return reduce_var_partial(ctx, partial, a, means);
+    });
+}
+
+HMC_API hmc_status hmc_shard_combine_var(hmc_context_t ctx, const hmc_tensor_desc *out, const double *gathered, int32_t ranks,
+                                         int64_t nout, int64_t total_count, double correction, int32_t take_sqrt) {
+    return guarded([&]() -> hmc_status {
+        HMC_ENTER(ctx);
+        if (ranks < 1 || nout < 0 || total_count < 0) return fail(HMC_INVALID, "bad rank, output or element count");
+        hmc_status s = check_flat_output(out, nout, "the output");
+        if (s != HMC_OK) return s;
+        if (!dtype_is_float(out->dtype)) return fail(HMC_INVALID, "the output is a floating point tensor");
+        if (nout == 0) return HMC_OK;
+        if (gathered == nullptr) return fail(HMC_INVALID, "null partials");
+        double divisor = static_cast<double>(total_count) - correction;
+        if (!(divisor > 0.0)) divisor = 0.0;
+        return dispatch_float(out->dtype, [&](auto t) -> hmc_status {
+            using T = decltype(t);
+            VarSink<T> sink{static_cast<T *>(out->data) + out->offset, divisor, take_sqrt};
+            combine_var_kernel<T><<<blocks_for(nout), 256, 0, ctx->stream>>>(sink, gathered, ranks, nout, total_count);
             return launch_status("shard combine launch");
         });
     });

@@ -495,6 +495,26 @@ class CudaBackend:
         self._check(self.lib.hmc_shard_combine_float(self.ctx, op, d, ctypes.cast(gathered.ptr, ctypes.POINTER(ctypes.c_double)),
                                                      ranks, nout, count))
 
+    def shard_combine_means(self, means: Storage, gathered: Storage, ranks: int, nout: int, count: int) -> None:
+        f64p = ctypes.POINTER(ctypes.c_double)
+        self._check(self.lib.hmc_shard_combine_means(self.ctx, ctypes.cast(means.ptr, f64p), ctypes.cast(gathered.ptr, f64p),
+                                                     ranks, nout, count))
+
+    def var_partial(self, partial: Storage, src: TensorData, mask: Sequence[bool], means: Storage) -> None:
+        """f64 sums of this shard's squared deviations from the given f64 means, one per output."""
+        r = describe("var_partial", src, mask)
+        if r is None:
+            return
+        ws = self._plan_workspace(r, False)
+        f64p = ctypes.POINTER(ctypes.c_double)
+        self._check(self.lib.hmc_var_partial(self.ctx, ctypes.cast(partial.ptr, f64p), r.kept, r.red, ctypes.cast(means.ptr, f64p),
+                                             ws.ptr if ws else None, ws.nbytes if ws else 0))
+
+    def shard_combine_var(self, out: TensorData, gathered: Storage, ranks: int, nout: int, count: int, correction: float,
+                          take_sqrt: bool) -> None:
+        self._check(self.lib.hmc_shard_combine_var(self.ctx, _flat_desc(out), ctypes.cast(gathered.ptr, ctypes.POINTER(ctypes.c_double)),
+                                                   ranks, nout, count, float(correction), int(take_sqrt)))
+
     def shard_combine_int(self, op: int, out: TensorData, gathered: Storage, ranks: int, nout: int) -> None:
         d = _flat_desc(out)
         self._check(self.lib.hmc_shard_combine_int(self.ctx, op, d, ctypes.cast(gathered.ptr, ctypes.POINTER(ctypes.c_int64)),
@@ -588,6 +608,21 @@ class CudaBackend:
         o, i = descs("flip", [out, flipped])
         self._check(self.lib.hmc_flip(self.ctx, o, i))
 
+    def addr(self, out: TensorData, v1: TensorData, v2: TensorData, input: Optional[TensorData], alpha, beta) -> None:
+        """out = beta * input + alpha * outer(v1, v2) with the CPU kernel's steps (hmc_addr)."""
+        d, a, b, ai, bi = addr_operands("addr", out, v1, v2, input, alpha, beta)
+        if d is None:
+            return
+        self._check(self.lib.hmc_addr(self.ctx, d[0], d[1], d[2], d[3] if len(d) > 3 else None, a, b, ai, bi))
+
+    def exclusive_cumprod(self, out: TensorData, src: TensorData, dim: int, reverse: bool) -> None:
+        """hmc_exclusive_cumprod along `dim` (out contiguous, as the CPU kernel requires)."""
+        ln = lines("exclusive_cumprod", out, src, dim, out.strides)
+        if ln is None:
+            return
+        (o, s), n, so, si = ln
+        self._check(self.lib.hmc_exclusive_cumprod(self.ctx, o, s, n, so, si, int(bool(reverse))))
+
     def adamw_step(self, param: TensorData, grad: TensorData, exp_avg: TensorData, exp_avg_sq: TensorData, *,
                    lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: float) -> None:
         """The fused AdamW update (hmc_adamw_step) with the scalars homura's optimizer derives
@@ -597,6 +632,37 @@ class CudaBackend:
             return
         sc = adamw_scalars(param.dtype, lr, beta1, beta2, eps, weight_decay, step)
         self._check(self.lib.hmc_adamw_step(self.ctx, d[0], d[1], d[2], d[3], ctypes.byref(sc)))
+
+
+def addr_operands(kernel: str, out: TensorData, v1: TensorData, v2: TensorData, input: Optional[TensorData], alpha, beta):
+    """The descriptions and coefficients of addr as homura's glue passes them (src/backend/rocm/elementwise.rs, addr):
+    v1 [n] and v2 [m] as [n, m] views with a stride of 0 along the other dimension, the input broadcast to [n, m] and left
+    out when beta is zero; float coefficients rounded to the dtype, integer and Bool ones as integers."""
+    n, m = out.shape
+    assert tuple(v1.shape) == (n,) and tuple(v2.shape) == (m,)
+    a_view = TensorData(v1.storage, v1.dtype, (n, m), (v1.strides[0], 0), v1.offset)
+    b_view = TensorData(v2.storage, v2.dtype, (n, m), (0, v2.strides[0]), v2.offset)
+    if out.dtype in FLOATS:
+        round_to = lambda v: bits_to_float(scalar_bits(float(v), out.dtype), out.dtype)
+        a, b, ai, bi = round_to(alpha), round_to(beta), 0, 0
+        reads = b != 0.0
+    else:
+        a, b = 0.0, 0.0
+        ai, bi = (int(bool(alpha)), int(bool(beta))) if out.dtype == BOOL else (int(alpha), int(beta))
+        reads = bi != 0
+    operands = [out, a_view, b_view] + ([input.expand(n, m)] if reads else [])
+    return descs(kernel, operands), a, b, ai, bi
+
+
+def bits_to_float(bits: int, dtype: int) -> float:
+    """The value of a float element given by its bits."""
+    if dtype == F64:
+        return float(np.array([bits], dtype=np.uint64).view(np.float64)[0])
+    if dtype == F32:
+        return float(np.array([bits], dtype=np.uint32).view(np.float32)[0])
+    if dtype == BF16:
+        return float(np.array([bits << 16], dtype=np.uint32).view(np.float32)[0])
+    return float(np.array([bits], dtype=np.uint16).view(np.float16)[0])
 
 
 DEFAULT_SEED = 67280421310721  # PyTorch's default seed, as homura uses it (src/ops/random.rs:15-16)

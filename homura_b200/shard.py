@@ -101,8 +101,32 @@ class ShardedReducer:
             gathered = self._gather(local.storage, SIZE[shard.dtype] * nout)
             be.shard_combine_extreme(op == ffi.HMC_REDUCE_MAX, out, None, gathered, shard.dtype, None, None,
                                      self.comm.ranks, nout)
+        elif op in (ffi.HMC_REDUCE_ALL, ffi.HMC_REDUCE_ANY):
+            # every rank's result is 0 or 1 in out's dtype (Bool, or U8 for U8 tensors): all = the minimum over
+            # the ranks, any = the maximum
+            local = be.empty(out.shape, out.dtype)
+            be.reduce(op, local, shard, mask)
+            gathered = self._gather(local.storage, SIZE[out.dtype] * nout)
+            be.shard_combine_extreme(op == ffi.HMC_REDUCE_ANY, out, None, gathered, out.dtype, None, None,
+                                     self.comm.ranks, nout)
         else:
             raise BackendError(ffi.HMC_INVALID, "this reduction is not available across shards")
+
+    def var(self, out: TensorData, shard: TensorData, mask: Sequence[bool], correction: float, take_sqrt: bool) -> None:
+        """Variance (standard deviation with take_sqrt) of the global tensor over the dimensions in `mask` (which
+        include dimension 0), in two rounds as on one GPU: the f64 means of the whole tensor, then the squared
+        deviations from them."""
+        assert len(mask) == len(shard.shape) and mask[0], "the sharded (first) dimension must be reduced"
+        assert is_float(shard.dtype)
+        be, nout = self.be, out.numel
+        count = self.global_rows * math.prod(n for n, m in zip(shard.shape[1:], mask[1:]) if m)
+        sums = be.storage(8 * nout)
+        be.reduce_partial(ffi.HMC_REDUCE_SUM, sums, shard, mask)
+        means = be.storage(8 * nout)
+        be.shard_combine_means(means, self._gather(sums, 8 * nout), self.comm.ranks, nout, count)
+        squares = be.storage(8 * nout)
+        be.var_partial(squares, shard, mask, means)
+        be.shard_combine_var(out, self._gather(squares, 8 * nout), self.comm.ranks, nout, count, correction, take_sqrt)
 
     def arg_reduce(self, values: Optional[TensorData], indices: TensorData, shard: TensorData, is_max: bool) -> None:
         """Index (global, along the sharded dimension 0) and optionally value of the maximum or minimum."""

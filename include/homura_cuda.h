@@ -275,6 +275,25 @@ hmc_status hmc_triangle(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc
  * (the flipped dimensions, with the offset at the element that comes first). csrc/homura_rocm.h:262-263 */
 hmc_status hmc_flip(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src);
 
+/* cpu::addr (src/backend/cpu/linalg.rs:227-410): out[i][j] = beta * input[i][j] + alpha * v1[i] * v2[j] with the
+ * steps of the CPU kernel, for every dtype. All four descriptions have the output's two dimensions [n, m]: v1 with
+ * stride 0 along the columns, v2 along the rows, and the input broadcast; `input` is NULL when beta is zero (it is
+ * not read).
+ *   floats (coefficients rounded to the dtype, in `alpha` and `beta`): a = alpha * v1[i] (skipped for alpha == 1),
+ *     p = a * v2[j], out = p or (beta == 1 ? c : beta * c) + p, each step in the computation type rounded to the dtype;
+ *   integers (`alpha_int`, `beta_int`): wrapping, alpha * (v1[i] * v2[j]) + beta * c;
+ *   Bool (`alpha_int`, `beta_int` 0 or 1): (v1[i] and alpha and v2[j]) or c.
+ * csrc/homura_rocm.h:231-244 */
+hmc_status hmc_addr(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *v1, const hmc_tensor_desc *v2,
+                    const hmc_tensor_desc *input, double alpha, double beta, int64_t alpha_int, int64_t beta_int);
+
+/* cpu::exclusive_cumprod (src/backend/cpu/reduce.rs:286-329) along lines of `n` elements, described as for
+ * hmc_softmax: element k of a line gets the product of the elements before it (after it with `reverse`), 1 for
+ * the first (last); the product is accumulated one element at a time in f32 for F16 / BF16 and f64 for F32 / F64 and
+ * rounded to the dtype as it is written. Floats only. csrc/homura_rocm.h:348-351 */
+hmc_status hmc_exclusive_cumprod(hmc_context_t ctx, const hmc_tensor_desc *out_lines, const hmc_tensor_desc *src_lines,
+                                 int64_t n, int64_t out_stride, int64_t src_stride, int32_t reverse);
+
 /* ---- additions of this backend (no counterpart in csrc/homura_rocm.h) ---- */
 
 /* hmc_reduce without a workspace argument, for callers that cannot allocate one when they need the

@@ -11,7 +11,8 @@
  * A reduction that folds the sharded dimension runs in three steps, all on the contexts' streams:
  *   1. every rank folds its shard into per-output partials that keep the accumulator's precision
  *      (f64 for float sums, products and means: hmc_reduce_partial; integer sums, max/min values and
- *      their indices are exact already and come from hmc_reduce / hmc_arg_reduce);
+ *      their indices, and the 0/1 results of all / any are exact already and come from hmc_reduce /
+ *      hmc_arg_reduce; all / any combine as the minimum / maximum of the ranks' results);
  *   2. the partials of all ranks are gathered into every rank's own memory (hmc_comm_allgather: one NCCL
  *      all-gather of a few bytes per output, latency bound);
  *   3. every rank folds the gathered partials in rank order (hmc_shard_combine_*): the same bits on every
@@ -54,6 +55,21 @@ hmc_status hmc_shard_combine_extreme(hmc_context_t ctx, int32_t is_max, const hm
                                      const hmc_tensor_desc *out_indices, const void *gathered_values, int32_t dtype,
                                      const int64_t *gathered_indices, const int64_t *index_offsets, int32_t ranks,
                                      int64_t nout);
+
+/* Variance / standard deviation across shards, two rounds as on one GPU (cpu::var, src/backend/cpu/reduce.rs:135-170:
+ * the mean in f64, then the squared deviations from it):
+ *   round 1: hmc_reduce_partial(SUM) -> all-gather -> hmc_shard_combine_means: means[o] = (sum over the ranks in
+ *            rank order) / total_count, kept in f64 (one per output, device memory);
+ *   round 2: hmc_var_partial: partial[o] = the f64 sum over this shard of (x - means[o])^2 (workspace as for
+ *            hmc_reduce) -> all-gather -> hmc_shard_combine_var: out[o] = round(sum over the ranks / (total_count -
+ *            correction)), its square root with take_sqrt, NaN when total_count is 0, infinity or NaN when the
+ *            divisor is not positive (as hmc_var). */
+hmc_status hmc_shard_combine_means(hmc_context_t ctx, double *means, const double *gathered, int32_t ranks, int64_t nout,
+                                   int64_t total_count);
+hmc_status hmc_var_partial(hmc_context_t ctx, double *partial, const hmc_tensor_desc *kept, const hmc_tensor_desc *red,
+                           const double *means, void *workspace, int64_t workspace_bytes);
+hmc_status hmc_shard_combine_var(hmc_context_t ctx, const hmc_tensor_desc *out, const double *gathered, int32_t ranks,
+                                 int64_t nout, int64_t total_count, double correction, int32_t take_sqrt);
 
 /* ---- NCCL (libhomura_cuda_shard.so) ---- */
 #define HMC_COMM_ID_BYTES 128

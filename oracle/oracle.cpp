@@ -1021,6 +1021,82 @@ int orc_flip(const hmc_tensor_desc *out, const hmc_tensor_desc *src) {
     });
 }
 
+// cpu::addr with the steps of FloatOuter / IntOuter / BoolOuter; the operands are given like the device entry point
+// (all four as [n, m] views, v1 and v2 broadcast). src/backend/cpu/linalg.rs:227-410.
+int orc_addr(const hmc_tensor_desc *out, const hmc_tensor_desc *v1, const hmc_tensor_desc *v2, const hmc_tensor_desc *input,
+             double alpha, double beta, int64_t alpha_int, int64_t beta_int) {
+    const int dt = out->dtype;
+    if (v1->dtype != dt || v2->dtype != dt || (input && input->dtype != dt)) return 2;
+    if (is_float(dt)) {
+        return dispatch_float(dt, [&](auto t) {
+            using T = decltype(t);
+            using C = typename Comp<T>::C;
+            const C a = (C)alpha, b = (C)beta;
+            auto row = [=](T x) { return a == (C)1 ? x : down<T>(up(x) * a); };
+            if (b == (C)0) return map2<T, T, T>(out, v1, v2, [=](T x, T y) { return down<T>(up(row(x)) * up(y)); });
+            if (!input) return 2;
+            return map3<T, T, T, T>(out, v1, v2, input, [=](T x, T y, T c) {
+                const T p = down<T>(up(row(x)) * up(y));
+                const T cc = b == (C)1 ? c : down<T>(up(c) * b);
+                return down<T>(up(cc) + up(p));
+            });
+        });
+    }
+    if (dt == HMC_BOOL) {
+        const bool a = alpha_int != 0;
+        if (beta_int == 0) return map2<Bool, Bool, Bool>(out, v1, v2, [=](Bool x, Bool y) { return Bool{(uint8_t)(x.b && a && y.b)}; });
+        if (!input) return 2;
+        return map3<Bool, Bool, Bool, Bool>(out, v1, v2, input,
+                                            [=](Bool x, Bool y, Bool c) { return Bool{(uint8_t)(c.b || (x.b && a && y.b))}; });
+    }
+    return dispatch_int(dt, [&](auto t) {
+        using T = decltype(t);
+        auto product = [=](T x, T y) {
+            uint64_t p = (uint64_t)(int64_t)x * (uint64_t)(int64_t)y;
+            return alpha_int == 1 ? p : p * (uint64_t)alpha_int;
+        };
+        if (beta_int == 0) return map2<T, T, T>(out, v1, v2, [=](T x, T y) { return (T)(int64_t)product(x, y); });
+        if (!input) return 2;
+        return map3<T, T, T, T>(out, v1, v2, input, [=](T x, T y, T c) {
+            const uint64_t cc = beta_int == 1 ? (uint64_t)(int64_t)c : (uint64_t)(int64_t)c * (uint64_t)beta_int;
+            return (T)(int64_t)(cc + product(x, y));
+        });
+    });
+}
+
+// cpu::exclusive_cumprod on lines given as for orc_softmax. src/backend/cpu/reduce.rs:228-329.
+int orc_exclusive_cumprod(const hmc_tensor_desc *out_lines, const hmc_tensor_desc *src_lines, int64_t n, int64_t so, int64_t si,
+                          int32_t reverse) {
+    if (out_lines->dtype != src_lines->dtype || !same_shape(out_lines, src_lines)) return 2;
+    return dispatch_float(src_lines->dtype, [&](auto t) {
+        using T = decltype(t);
+        const T *ps = (const T *)src_lines->data;
+        T *po = (T *)out_lines->data;
+        const int64_t *st[2] = {out_lines->strides, src_lines->strides};
+        int64_t base[2] = {out_lines->offset, src_lines->offset};
+        walk<2>(out_lines->ndim, out_lines->sizes, st, base, [&](const int64_t *oi) {
+            if constexpr (std::is_same_v<T, F16> || std::is_same_v<T, BF16>) {
+                float acc = 1.0f;
+                for (int64_t k = 0; k < n; ++k) {
+                    const int64_t at = reverse ? n - 1 - k : k;
+                    const T x = ps[oi[1] + at * si];
+                    po[oi[0] + at * so] = down<T>(acc);
+                    acc = acc * up(x);
+                }
+            } else {
+                double acc = 1.0;
+                for (int64_t k = 0; k < n; ++k) {
+                    const int64_t at = reverse ? n - 1 - k : k;
+                    const T x = ps[oi[1] + at * si];
+                    po[oi[0] + at * so] = from_f64<T>(acc);
+                    acc = acc * to_f64(x);
+                }
+            }
+        });
+        return 0;
+    });
+}
+
 // Scalar conversions exposed for the tests of the cast tables (src/dtype.rs:543-665).
 uint16_t orc_f32_to_f16(float f) { return f32_to_f16(f); }
 uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16(f); }

@@ -35,6 +35,7 @@ def _load_oracle():
         "orc_random_uniform": [i32, vp, i64, u64, u64, f64, f64], "orc_random_normal": [i32, vp, i64, u64, u64, f64, f64],
         "orc_random_int": [vp, i64, u64, u64, i64, i64, ctypes.POINTER(u64)],
         "orc_triangle": [D, D, i64, i32], "orc_flip": [D, D],
+        "orc_addr": [D, D, D, D, f64, f64, i64, i64], "orc_exclusive_cumprod": [D, D, i64, i64, i64, i32],
     }
     for name, args in protos.items():
         fn = getattr(lib, name)
@@ -219,6 +220,20 @@ class OracleBackend:
         o, i = descs("flip", [out, flipped])
         self._check(self.lib.orc_flip(o, i))
 
+    def addr(self, out, v1, v2, input, alpha, beta):
+        from homura_b200.host import addr_operands
+        d, a, b, ai, bi = addr_operands("addr", out, v1, v2, input, alpha, beta)
+        if d is None:
+            return
+        self._check(self.lib.orc_addr(d[0], d[1], d[2], d[3] if len(d) > 3 else None, a, b, ai, bi))
+
+    def exclusive_cumprod(self, out, src, dim, reverse):
+        ln = lines("exclusive_cumprod", out, src, dim, out.strides)
+        if ln is None:
+            return
+        (o, s), n, so, si = ln
+        self._check(self.lib.orc_exclusive_cumprod(o, s, n, so, si, int(bool(reverse))))
+
     # ---- the sharded reductions' local and combine steps, restated on the host for the CPU tests ----
     def storage(self, nbytes: int) -> Storage:
         return Storage(nbytes, array=np.zeros(max(nbytes, 1), dtype=np.uint8))
@@ -243,6 +258,43 @@ class OracleBackend:
             if op == ffi.HMC_REDUCE_MEAN:
                 acc = acc / float(count)
         self.copy(out, self.upload(acc, F64, out.shape))
+
+    def shard_combine_means(self, means: Storage, gathered: Storage, ranks, nout, count):
+        g = gathered.array[:8 * ranks * nout].view(np.float64).reshape(ranks, nout)
+        acc = np.zeros(nout)
+        with np.errstate(all="ignore"):
+            for r in range(ranks):
+                acc = acc + g[r]
+            acc = acc / float(count)
+        means.array[:8 * nout] = acc.view(np.uint8)
+
+    def var_partial(self, partial: Storage, src, mask, means: Storage):
+        """f64 sums of (x - mean)^2 in the CPU's fold order."""
+        from homura_b200.host import F64
+        wide = self.empty(src.shape, F64)
+        self.copy(wide, src)
+        kept = [n for n, m in zip(src.shape, mask) if not m]
+        m = means.array[:8 * math.prod(kept)].view(np.float64).reshape([n if not r else 1 for n, r in zip(src.shape, mask)])
+        with np.errstate(all="ignore"):
+            d = self.download(wide) - m
+            sq = self.upload(d * d, F64, src.shape)
+        out = self.empty(kept, F64)
+        self.reduce(ffi.HMC_REDUCE_SUM, out, sq, mask)
+        partial.array[:8 * out.numel] = self.download(out).reshape(-1).view(np.uint8)
+
+    def shard_combine_var(self, out, gathered: Storage, ranks, nout, count, correction, take_sqrt):
+        from homura_b200.host import F64
+        g = gathered.array[:8 * ranks * nout].view(np.float64).reshape(ranks, nout)
+        acc = np.zeros(nout)
+        with np.errstate(all="ignore"):
+            for r in range(ranks):
+                acc = acc + g[r]
+            divisor = float(count) - correction
+            divisor = divisor if divisor > 0.0 else 0.0
+            v = np.full(nout, np.nan) if count == 0 else acc / divisor
+            if take_sqrt:
+                v = np.sqrt(v)
+        self.copy(out, self.upload(v, F64, out.shape))
 
     def shard_combine_int(self, op, out, gathered: Storage, ranks, nout):
         g = gathered.array[:8 * ranks * nout].view(np.uint64).reshape(ranks, nout)

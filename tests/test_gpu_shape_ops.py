@@ -70,3 +70,55 @@ def test_flip_on_every_layout(oracle, cuda, dtype):
     oracle.flip(oo, view(os_), [0, 1])
     cuda.flip(go, view(gs), [0, 1])
     assert_bitwise(cuda.download(go), oracle.download(oo), dtype, "flip of a transposed window")
+
+
+@pytest.mark.parametrize("dtype", ALL_DTYPES, ids=DTYPE_NAMES)
+def test_addr_on_every_dtype(oracle, cuda, dtype):
+    """out = beta * input + alpha * outer(v1, v2), every rounding where the CPU kernel has it: bit for bit."""
+    floats = dtype in (BF16, F32, F64) or DTYPE_NAMES[dtype] == "f16"
+    for n, m in ((1, 1), (7, 5), (130, 257), (1000, 520)):
+        v1o, v1g = both(oracle, cuda, values(dtype, n, 420), dtype, (n,))
+        v2o, v2g = both(oracle, cuda, values(dtype, m, 421), dtype, (m,))
+        ino, ing = both(oracle, cuda, values(dtype, n * m, 422), dtype, (n, m))
+        coefficients = [(1, 1), (1, 0), (0.5, 2.0), (-3, 0), (2, 1)] if floats else [(1, 1), (1, 0), (3, -2), (0, 1), (-1, 0)]
+        for alpha, beta in coefficients:
+            oo, go = oracle.empty((n, m), dtype), cuda.empty((n, m), dtype)
+            oracle.addr(oo, v1o, v2o, ino, alpha, beta)
+            cuda.addr(go, v1g, v2g, ing, alpha, beta)
+            assert_bitwise(cuda.download(go), oracle.download(oo), dtype, f"addr [{n}, {m}] alpha={alpha} beta={beta}")
+    # strided vectors, a broadcast input (a row [m] and a single element), and a transposed input
+    n, m = 300, 260
+    bigo, bigg = both(oracle, cuda, values(dtype, 2 * n + 3 * m + n * m, 423), dtype, (2 * n + 3 * m + n * m,))
+    cut = lambda t: (t.narrow(0, 0, 2 * n).reshape(n, 2).select(1, 1), t.narrow(0, 2 * n, 3 * m).reshape(m, 3).select(1, 0),
+                     t.narrow(0, 2 * n + 3 * m, n * m).reshape(m, n).t())
+    for inp in (lambda v1, v2, c: c, lambda v1, v2, c: v2, lambda v1, v2, c: v1.narrow(0, 2, 1)):
+        oo, go = oracle.empty((n, m), dtype), cuda.empty((n, m), dtype)
+        a1, a2, ac = cut(bigo)
+        b1, b2, bc = cut(bigg)
+        oracle.addr(oo, a1, a2, inp(a1, a2, ac), 1, 1)
+        cuda.addr(go, b1, b2, inp(b1, b2, bc), 1, 1)
+        assert_bitwise(cuda.download(go), oracle.download(oo), dtype, "addr on strided vectors and a broadcast input")
+
+
+@pytest.mark.parametrize("dtype", [BF16, F32, F64], ids=["bf16", "f32", "f64"])
+def test_exclusive_cumprod(oracle, cuda, dtype):
+    """The sequential product in the accumulation type (f32 for the half dtypes, f64 otherwise): bit for bit."""
+    from values import f64_to_storage, words
+    for shape in ((1,), (9,), (5, 300), (300, 5), (3, 40, 7), (2, 1025)):
+        n = int(np.prod(shape))
+        w = words(430, n)
+        near_one = 0.5 + (w >> np.uint64(11)).astype(np.float64) / float(1 << 53) * 1.5   # products neither vanish nor overflow
+        raw = f64_to_storage(np.where(w % np.uint64(97) == 0, -near_one, near_one), dtype)
+        so, sg = both(oracle, cuda, raw, dtype, shape)
+        for dim in range(len(shape)):
+            for reverse in (False, True):
+                oo, go = oracle.empty(shape, dtype), cuda.empty(shape, dtype)
+                oracle.exclusive_cumprod(oo, so, dim, reverse)
+                cuda.exclusive_cumprod(go, sg, dim, reverse)
+                assert_bitwise(cuda.download(go), oracle.download(oo), dtype, f"exclusive_cumprod {shape} dim {dim} reverse {reverse}")
+    # special values and a transposed source
+    so, sg = both(oracle, cuda, values(dtype, 64 * 33, 431), dtype, (64, 33))
+    oo, go = oracle.empty((33, 64), dtype), cuda.empty((33, 64), dtype)
+    oracle.exclusive_cumprod(oo, so.t(), 1, False)
+    cuda.exclusive_cumprod(go, sg.t(), 1, False)
+    assert_bitwise(cuda.download(go), oracle.download(oo), dtype, "exclusive_cumprod of special values, transposed")

@@ -28,7 +28,7 @@ def _worker(rank, world, unique_id, results):
     try:
         from frontend import T
         from homura_b200 import ffi
-        from homura_b200.host import BF16, F32, I32, I64, CudaBackend
+        from homura_b200.host import BF16, BOOL, F32, I32, I64, CudaBackend
         from homura_b200.shard import NcclComm, ShardedReducer, split_rows
         from oracle_backend import OracleBackend
         from values import assert_bitwise, assert_ulp, f64_to_storage
@@ -66,6 +66,19 @@ def _worker(rank, world, unique_id, results):
                     else:
                         assert_bitwise(got, want, out_dt, f"{name} {mask}")
                     digest.append(got.tobytes())
+                # all / any (0/1 results combine as minimum / maximum); variance and standard deviation in two rounds
+                for name, op in (("all", ffi.HMC_REDUCE_ALL), ("any", ffi.HMC_REDUCE_ANY)):
+                    out = be.empty(shape, BOOL)
+                    red.reduce(op, out, shard, mask)
+                    assert_bitwise(be.download(out), whole._red(name, dims).raw(), BOOL, f"{name} {mask}")
+                if is_f:
+                    for correction, take_sqrt in ((1, False), (0, True)):
+                        out = be.empty(shape, dt)
+                        red.var(out, shard, mask, correction, take_sqrt)
+                        w = whole.std_dim(dims, correction) if take_sqrt else whole.var_dim(dims, correction)
+                        got = be.download(out)
+                        assert_ulp(got, w.raw(), dt, 2, f"var/std {mask} correction {correction}")
+                        digest.append(got.tobytes())
             for is_max in (True, False):
                 v, i = be.empty((cols,), dt), be.empty((cols,), I64)
                 red.arg_reduce(v, i, shard, is_max)

@@ -125,3 +125,29 @@ def test_exhaustive_half_conversions_agree_with_numpy(oracle):
         g = lib.orc_bf16_to_f32(int(b))
         back = lib.orc_f32_to_bf16(g)
         assert back == (b | 0x0040 if (b & 0x7FFF) > 0x7F80 else b)
+
+
+def test_addr_and_exclusive_cumprod_by_hand(oracle):
+    """The checker's addr and exclusive_cumprod on cases worked by hand (homura's tests/linalg.rs and tests/reduce.rs hold
+    the same identities: addr with beta 0 ignores the input, integers wrap, the first product of a line is 1)."""
+    from homura_b200.host import F32, I8
+    v1 = oracle.upload(np.array([1.0, 2.0, 3.0], dtype=np.float32), F32)
+    v2 = oracle.upload(np.array([10.0, 20.0], dtype=np.float32), F32)
+    inp = oracle.upload(np.full((3, 2), np.nan, dtype=np.float32), F32)
+    out = oracle.empty((3, 2), F32)
+    oracle.addr(out, v1, v2, inp, 2.0, 0.0)   # beta 0: the NaNs of the input are not read
+    assert (oracle.download(out) == np.array([[20, 40], [40, 80], [60, 120]], dtype=np.float32)).all()
+    oracle.addr(out, v1, v2, oracle.upload(np.ones((3, 2), dtype=np.float32), F32), 1.0, 0.5)
+    assert (oracle.download(out) == np.array([[10.5, 20.5], [20.5, 40.5], [30.5, 60.5]], dtype=np.float32)).all()
+    a = oracle.upload(np.array([100, -7], dtype=np.int8), I8)
+    b = oracle.upload(np.array([3], dtype=np.int8), I8)
+    c = oracle.upload(np.array([[5], [6]], dtype=np.int8), I8)
+    o8 = oracle.empty((2, 1), I8)
+    oracle.addr(o8, a, b, c, 2, -1)            # 2 * 300 - 5 = 595 -> 83 (mod 256); 2 * -21 - 6 = -48
+    assert oracle.download(o8).reshape(-1).tolist() == [83, -48]
+    x = oracle.upload(np.array([[2.0, 3.0, 4.0], [0.5, 0.0, 7.0]], dtype=np.float32), F32)
+    y = oracle.empty((2, 3), F32)
+    oracle.exclusive_cumprod(y, x, 1, False)
+    assert (oracle.download(y) == np.array([[1, 2, 6], [1, 0.5, 0]], dtype=np.float32)).all()
+    oracle.exclusive_cumprod(y, x, 1, True)
+    assert (oracle.download(y) == np.array([[12, 4, 1], [0, 7, 1]], dtype=np.float32)).all()

@@ -36,7 +36,7 @@ def _worker(rank, world, port, results):
     try:
         from frontend import T
         from homura_b200 import ffi
-        from homura_b200.host import F32, BF16, I32, I64
+        from homura_b200.host import BOOL, F32, BF16, I32, I64
         from homura_b200.shard import ShardedReducer, split_rows
         from oracle_backend import OracleBackend
         from values import assert_bitwise, assert_ulp, f64_to_storage, values
@@ -71,6 +71,18 @@ def _worker(rank, world, port, results):
                         assert_ulp(got, want, dt, 2, f"{name} {mask}")
                     else:
                         assert_bitwise(got, want, out_dt, f"{name} {mask}")
+                # all / any (0/1 results combine as minimum / maximum); variance and standard deviation in two rounds
+                for name, op in (("all", ffi.HMC_REDUCE_ALL), ("any", ffi.HMC_REDUCE_ANY)):
+                    out = be.empty(shape, BOOL)
+                    red.reduce(op, out, shard, mask)
+                    assert_bitwise(be.download(out), whole._red(name, dims).raw(), BOOL, f"{name} {mask}")
+                if is_f:
+                    for correction, take_sqrt in ((1, False), (0, True)):
+                        out = be.empty(shape, dt)
+                        red.var(out, shard, mask, correction, take_sqrt)
+                        w = whole.std_dim(dims, correction) if take_sqrt else whole.var_dim(dims, correction)
+                        got = be.download(out)
+                        assert_ulp(got, w.raw(), dt, 2, f"var/std {mask} correction {correction}")
             for is_max in (True, False):
                 v, i = be.empty((cols,), dt), be.empty((cols,), I64)
                 red.arg_reduce(v, i, shard, is_max)
