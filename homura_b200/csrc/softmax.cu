@@ -26,7 +26,7 @@ struct SoftmaxArgs {
 
 struct SoftmaxPlan {
     int kind;   // 0: row in registers, 1: streaming
-    int group;  // 32 or 256
+    int group;  // 32, 128 or 256
     int cache;  // vectors a lane keeps (kind 0)
 };
 
@@ -34,7 +34,9 @@ SoftmaxPlan softmax_plan(int dtype, int64_t n) {
     const int64_t vec = 16 / element_size(dtype);
     const int64_t nvec = ceil_div(n, vec);
     SoftmaxPlan p{};
-    p.group = nvec <= 64 ? 32 : 256;
+    // a warp for short rows; 128 lanes (two rows per block) while a lane then holds at most four vectors: the work
+    // done once per row and lane (reductions, the reciprocal, addresses) is then spread over twice the elements
+    p.group = nvec <= 64 ? 32 : (nvec <= 4 * 128 ? 128 : 256);
     const int64_t per = ceil_div(nvec, p.group);
     p.kind = per <= 8 ? 0 : 1;
     p.cache = 0;
@@ -45,6 +47,19 @@ SoftmaxPlan softmax_plan(int dtype, int64_t n) {
     return p;
 }
 
+// A barrier over the G lanes of a row: the whole block for 256, a named barrier per row for 128 (two rows share
+// a block and may take different paths), nothing for a warp.
+template <int G>
+__device__ __forceinline__ void row_barrier() {
+    if constexpr (G == 256) {
+        __syncthreads();
+    } else if constexpr (G == 128) {
+        // (barrier numbers as immediates: a number in a register makes the compiler reserve all sixteen)
+        if (threadIdx.x < 128) asm volatile("bar.sync 1, 128;" ::: "memory");
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
+    }
+}
+// The warps of a row: W = G / 32 of them, the first at index `first` of the block's eight.
 template <int G>
 __device__ __forceinline__ double group_max(double v, double *scratch) {
 #pragma unroll
@@ -52,13 +67,14 @@ __device__ __forceinline__ double group_max(double v, double *scratch) {
         double o = __shfl_xor_sync(0xFFFFFFFFu, v, d);
         v = o > v ? o : v;
     }
-    if constexpr (G == 256) {
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        __syncthreads();
+    if constexpr (G > 32) {
+        constexpr int W = G / 32;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, first = warp / W * W;
+        row_barrier<G>();
         if (lane == 0) scratch[warp] = v;
-        __syncthreads();
-        v = scratch[0];
-        for (int w = 1; w < 8; ++w) v = scratch[w] > v ? scratch[w] : v;
+        row_barrier<G>();
+        v = scratch[first];
+        for (int w = 1; w < W; ++w) v = scratch[first + w] > v ? scratch[first + w] : v;
     }
     return v;
 }
@@ -67,13 +83,14 @@ template <int G>
 __device__ __forceinline__ double group_sum(double v, double *scratch) {
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
-    if constexpr (G == 256) {
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        __syncthreads();
+    if constexpr (G > 32) {
+        constexpr int W = G / 32;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, first = warp / W * W;
+        row_barrier<G>();
         if (lane == 0) scratch[warp] = v;
-        __syncthreads();
-        v = scratch[0];
-        for (int w = 1; w < 8; ++w) v += scratch[w];
+        row_barrier<G>();
+        v = scratch[first];
+        for (int w = 1; w < W; ++w) v += scratch[first + w];
     }
     return v;
 }
@@ -85,13 +102,14 @@ template <int G>
 __device__ __forceinline__ float row_max_f32(float v, float *scratch) {
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
-    if constexpr (G == 256) {
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if constexpr (G > 32) {
+        constexpr int W = G / 32;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, first = warp / W * W;
         if (lane == 0) scratch[warp] = v;
-        __syncthreads();
-        v = scratch[lane & 7];
+        row_barrier<G>();
+        v = scratch[first + (lane & (W - 1))];
 #pragma unroll
-        for (int d = 4; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
+        for (int d = W / 2; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
     }
     return v;
 }
@@ -99,14 +117,15 @@ template <int G>
 __device__ __forceinline__ double row_sum_f64(double v, double *scratch) {
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
-    if constexpr (G == 256) {
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if constexpr (G > 32) {
+        constexpr int W = G / 32;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, first = warp / W * W;
         if (lane == 0) scratch[warp] = v;
-        __syncthreads();
-        // a butterfly over the eight partial sums: every lane adds the same pairs, so all lanes hold the same bits
-        v = scratch[lane & 7];
+        row_barrier<G>();
+        // a butterfly over the warps' partial sums: every lane adds the same pairs, so all lanes hold the same bits
+        v = scratch[first + (lane & (W - 1))];
 #pragma unroll
-        for (int d = 4; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
+        for (int d = W / 2; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
     }
     return v;
 }
@@ -378,6 +397,14 @@ hmc_status launch_softmax_cv(hmc_context_t ctx, const SoftmaxArgs &a, bool log) 
 
 template <class T, int G>
 hmc_status launch_softmax_g(hmc_context_t ctx, const SoftmaxArgs &a, const SoftmaxPlan &p, bool log) {
+    if constexpr (G == 128) {
+        // the plan gives 128 lanes only to rows that fit four vectors per lane
+        switch (p.cache) {
+            case 1: return launch_softmax_cv<T, G, 1>(ctx, a, log);
+            case 2: return launch_softmax_cv<T, G, 2>(ctx, a, log);
+            default: return launch_softmax_cv<T, G, 4>(ctx, a, log);
+        }
+    }
     switch (p.kind == 0 ? p.cache : 0) {
         case 1: return launch_softmax_cv<T, G, 1>(ctx, a, log);
         case 2: return launch_softmax_cv<T, G, 2>(ctx, a, log);
@@ -448,6 +475,7 @@ HMC_API hmc_status hmc_softmax(hmc_context_t ctx, const hmc_tensor_desc *out_row
         return dispatch_float(src_rows->dtype, [&](auto t) -> hmc_status {
             using T = decltype(t);
             if (p.group == 32) return launch_softmax_g<T, 32>(ctx, a, p, log != 0);
+            if (p.group == 128) return launch_softmax_g<T, 128>(ctx, a, p, log != 0);
             return launch_softmax_g<T, 256>(ctx, a, p, log != 0);
         });
     });
