@@ -69,6 +69,13 @@ struct BinaryFloat {
     __device__ __forceinline__ Compute compute(T x, T y) const { return binary_math<OP, Compute>(up(x), up(y)); }
 };
 
+// Two 2-byte inputs and a 2-byte output: 40 registers are enough, and six resident blocks instead of four measured
+// 5 % faster on B200 for a bf16 product with a row-broadcast operand (latency bound).
+template <class T, int OP>
+struct LeanMinBlocks<BinaryFloat<T, OP>> {
+    static constexpr int value = sizeof(T) <= 2 && OP != HMC_BINARY_POW && OP != HMC_BINARY_DIV ? 6 : 4;
+};
+
 // out = op(cast(a), cast(b)) in the promoted float dtype P: the bits of homura's separate cast
 // kernels followed by the binary kernel.
 template <class P, class TA, class TB, int OP>

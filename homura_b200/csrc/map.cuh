@@ -83,21 +83,11 @@ template <class F> constexpr int unroll_of() {
     constexpr int out_bytes = static_cast<int>(sizeof(typename F::Out)) * vec_of<F>();
     constexpr int by_in = in_bytes == 0 ? 4 : (in_bytes >= 64 ? 1 : (in_bytes >= 32 ? 2 : 4));
     constexpr int by_out = out_bytes >= 64 ? 1 : (out_bytes >= 32 ? 2 : 4);
-#ifdef HMC_UNROLL_CAP
-    return (by_in < by_out ? by_in : by_out) < HMC_UNROLL_CAP ? (by_in < by_out ? by_in : by_out) : HMC_UNROLL_CAP;
-#else
     return by_in < by_out ? by_in : by_out;
-#endif
 }
 
 // 32 bytes in one instruction (sm_100's 256-bit global accesses): a lane then moves a whole sector, where two
 // 16-byte accesses leave half of every sector to the second instruction. The address is 32-byte aligned.
-#ifndef HMC_WIDE_LOADS
-#define HMC_WIDE_LOADS 1
-#endif
-#ifndef HMC_WIDE_STORES
-#define HMC_WIDE_STORES 1
-#endif
 struct alignas(32) Bytes32 {
     uint32_t w[8];
 };
@@ -118,7 +108,7 @@ __device__ __forceinline__ void store_32_bytes(void *p, const Bytes32 &v) {
 template <class T, int VEC>
 __device__ __forceinline__ void vector_load(Pack<T, VEC> &dst, const T *p, bool wide) {
     constexpr int kBytes = static_cast<int>(sizeof(T)) * VEC;
-    if constexpr (kBytes % 32 == 0 && HMC_WIDE_LOADS) {
+    if constexpr (kBytes % 32 == 0) {
         if (wide) {
 #pragma unroll
             for (int i = 0; i < kBytes / 32; ++i) {
@@ -133,7 +123,7 @@ __device__ __forceinline__ void vector_load(Pack<T, VEC> &dst, const T *p, bool 
 template <class T, int VEC>
 __device__ __forceinline__ void vector_store(T *p, const Pack<T, VEC> &src, bool wide) {
     constexpr int kBytes = static_cast<int>(sizeof(T)) * VEC;
-    if constexpr (kBytes % 32 == 0 && HMC_WIDE_STORES) {
+    if constexpr (kBytes % 32 == 0) {
         if (wide) {
 #pragma unroll
             for (int i = 0; i < kBytes / 32; ++i) {
@@ -420,9 +410,9 @@ __global__ void __launch_bounds__(kThreads, HMC_MAP_MIN_BLOCKS) map_kernel(const
 // with a row stride of 0. Such launches need none of the general kernel's bookkeeping: a thread's vectors are
 // found with a handful of integer operations, which matters for 1- and 2-byte elements, where a kernel at HBM
 // speed has an instruction budget of about fifteen per element.
-#ifndef HMC_LEAN_MIN_BLOCKS
-#define HMC_LEAN_MIN_BLOCKS 4
-#endif
+// Resident blocks per SM the lean kernel is compiled for: 4 (64 registers) by default; functors that need few
+// registers can ask for more by specialising this, which puts more loads in flight for latency-bound layouts.
+template <class F> struct LeanMinBlocks { static constexpr int value = 4; };
 struct LeanArgs {
     char *base[kOperands];
     int64_t row_stride[kOperands];  // elements
@@ -447,7 +437,7 @@ __device__ __forceinline__ void lean_load(Pack<T, VEC> &dst, const T *row, uint3
 }
 
 template <class F>
-__global__ void __launch_bounds__(kThreads, HMC_LEAN_MIN_BLOCKS) map_lean_kernel(const __grid_constant__ LeanArgs a, const F f) {
+__global__ void __launch_bounds__(kThreads, LeanMinBlocks<F>::value) map_lean_kernel(const __grid_constant__ LeanArgs a, const F f) {
     using TO = typename F::Out;
     using TA = typename F::A;
     using TB = typename F::B;
@@ -551,9 +541,6 @@ bool build_lean_args(LeanArgs &lean, const MapArgs &a, const int *elem_size, int
 #endif
 #ifndef HMC_TILE_RING_KB
 #define HMC_TILE_RING_KB 40
-#endif
-#ifndef HMC_TILE_A_FASTEST
-#define HMC_TILE_A_FASTEST 0
 #endif
 constexpr int kTileStagesMax = 4;
 constexpr int kTileKnownDevices = 64;                        // GPUs whose launch limits are remembered
@@ -734,7 +721,7 @@ __device__ __forceinline__ TileGeom<F> tile_geometry(const MapArgs &a, const Til
     using TC = typename F::C;
     constexpr int TD = tile_dim<F>();
     const int da = a.ndim - 2, db = a.ndim - 1;
-    const int64_t jb = HMC_TILE_A_FASTEST ? c.js : c.jf, ja = HMC_TILE_A_FASTEST ? c.jf : c.js;
+    const int64_t jb = c.jf, ja = c.js;  // neighbouring tile numbers walk B first (either order measured the same)
     int64_t off[kOperands] = {0, 0, 0, 0};
     int64_t outer = c.outer;
     for (int d = da - 1; d >= 0; --d) {
@@ -784,7 +771,7 @@ __global__ void __launch_bounds__(kThreads, HMC_TILE_MIN_BLOCKS) map_tile_kernel
     const int64_t sca = a.strides[3][da], scb = a.strides[3][db];
     const int stages = a.tile_stages;
     // A fixed number of resident blocks walk the tiles: block i takes tiles i, i + grid, i + 2 grid, ...
-    const int64_t fast = HMC_TILE_A_FASTEST ? a.tiles_a : a.tiles_b, slow = HMC_TILE_A_FASTEST ? a.tiles_b : a.tiles_a;
+    const int64_t fast = a.tiles_b, slow = a.tiles_a;
     const TileCursor step = tile_cursor(gridDim.x, fast, slow);
     TileCursor ahead = tile_cursor(blockIdx.x, fast, slow);  // the tile whose copies are started next
     TileCursor here = ahead;                                 // the tile computed next

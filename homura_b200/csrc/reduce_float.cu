@@ -63,6 +63,146 @@ __global__ void __launch_bounds__(kRThreads) deviations_kernel(const __grid_cons
     }
 }
 
+
+// ---- variance over columns in one pass ----
+// The layout of reduce_columns_kernel (a thread owns VC adjacent outputs, the 8 warps of a block take the reduced
+// indices j, j + 8, ...), but instead of a pass for the means and a pass for the deviations a thread keeps
+// (count, mean, M2 = sum of squared deviations from that mean) per output and merges batches of four rows into
+// them with the pairwise update of Chan, Golub and LeVeque: the batch's own mean and M2 first (exact two-pass
+// on four values), then mean += d * 4 / n, M2 += M2_batch + d * d * (n - 4) * 4 / n with d = batch mean - mean.
+// All in f64: the result differs from the two-pass value by a few f64 ulps, far below the rounding to F16,
+// BF16 or F32 (F64 tensors keep the two passes). One read of the source instead of two.
+struct Moments {
+    double mean, m2;
+};
+static_assert(sizeof(Moments) == kPartialBytes, "the moments of a chunk are one partial");
+
+__device__ __forceinline__ void merge_moments(double &n, double &mean, double &m2, double nb, double mean_b, double m2_b) {
+    if (nb == 0.0) return;
+    const double total = n + nb;
+    const double d = mean_b - mean;
+    const double w = nb / total;
+    mean = n == 0.0 ? mean_b : mean + d * w;
+    m2 = n == 0.0 ? m2_b : m2 + m2_b + d * d * n * w;
+    n = total;
+}
+
+template <class T>
+__global__ void __launch_bounds__(kRThreads) var_columns_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+    constexpr int VC = (16 / sizeof(T)) > 8 ? 8 : (16 / sizeof(T));
+    constexpr int UNR = 4;
+    const ReducePlan &p = a.plan;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t chunk = blockIdx.y;
+    const int64_t j0 = chunk * p.chunk;
+    const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
+    const int last = a.kept.ndim - 1;
+    const bool single = a.red.ndim == 1;
+    auto red_off = [&](int64_t j) { return single ? j * a.red.strides[0] : decompose(a.red, j, a.red.ndim); };
+    __shared__ double stage_mean[7][32 * VC];
+    __shared__ double stage_m2[7][32 * VC];
+    __shared__ double stage_n[8];
+    const int64_t xblocks = p.kouter * p.xtiles;
+    for (int64_t bx = blockIdx.x; bx < xblocks; bx += gridDim.x) {
+        const int64_t outer = bx / p.xtiles;
+        const int64_t tile = bx - outer * p.xtiles;
+        const int64_t c0 = tile * (32 * VC) + static_cast<int64_t>(tx) * VC;
+        const int64_t base = a.kept.offset + (last > 0 ? decompose(a.kept, outer, last) : 0);
+        const int64_t o0 = outer * p.ncols + c0;
+        const T *src = static_cast<const T *>(a.kept.data) + base + c0;
+        double n = 0.0, mean[VC], m2[VC];
+#pragma unroll
+        for (int e = 0; e < VC; ++e) mean[e] = m2[e] = 0.0;
+        const bool in_range = c0 < p.ncols;
+        const bool whole = c0 + VC <= p.ncols;
+        if (in_range) {
+            int64_t j = j0 + ty;
+            for (; j + (UNR - 1) * 8 < j1; j += UNR * 8) {
+                RVec<T, VC> x[UNR];
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const T *q = src + red_off(j + u * 8);
+                    if (whole && (reinterpret_cast<uintptr_t>(q) & (alignof(RVec<T, VC>) - 1)) == 0) {
+                        x[u] = *reinterpret_cast<const RVec<T, VC> *>(q);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < VC; ++e) x[u].v[e] = c0 + e < p.ncols ? q[e] : T{};
+                    }
+                }
+                const double total = n + UNR;
+                const double w = UNR / total;
+#pragma unroll
+                for (int e = 0; e < VC; ++e) {
+                    double v[UNR];
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) v[u] = to_f64(x[u].v[e]);
+                    const double mb = ((v[0] + v[1]) + (v[2] + v[3])) * (1.0 / UNR);
+                    double sq = 0.0;
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) sq += (v[u] - mb) * (v[u] - mb);
+                    const double d = mb - mean[e];
+                    mean[e] = n == 0.0 ? mb : mean[e] + d * w;
+                    m2[e] = n == 0.0 ? sq : m2[e] + sq + d * d * n * w;
+                }
+                n = total;
+            }
+            for (; j < j1; j += 8) {
+                const T *q = src + red_off(j);
+                const double total = n + 1.0;
+                const double w = 1.0 / total;
+#pragma unroll
+                for (int e = 0; e < VC; ++e) {
+                    if (c0 + e < p.ncols) {
+                        const double v = to_f64(q[e]);
+                        const double d = v - mean[e];
+                        mean[e] = n == 0.0 ? v : mean[e] + d * w;
+                        m2[e] = n == 0.0 ? 0.0 : m2[e] + d * d * n * w;
+                    }
+                }
+                n = total;
+            }
+        }
+        if (ty > 0) {
+#pragma unroll
+            for (int e = 0; e < VC; ++e) {
+                stage_mean[ty - 1][tx * VC + e] = mean[e];
+                stage_m2[ty - 1][tx * VC + e] = m2[e];
+            }
+        }
+        if (tx == 0) stage_n[ty] = n;
+        __syncthreads();
+        if (ty == 0 && in_range) {
+#pragma unroll
+            for (int e = 0; e < VC; ++e) {
+                if (c0 + e >= p.ncols) continue;
+                double cn = n, cm = mean[e], c2 = m2[e];
+                for (int w = 0; w < 7; ++w) merge_moments(cn, cm, c2, stage_n[w + 1], stage_mean[w][tx * VC + e], stage_m2[w][tx * VC + e]);
+                if (p.splits == 1) sink.put(o0 + e, c2, p.nred);
+                else static_cast<Moments *>(a.partials)[chunk * p.nout + o0 + e] = Moments{cm, c2};
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// The chunks' moments of each output merged in chunk order (a chunk's count follows from the plan).
+template <class T>
+__global__ void __launch_bounds__(kRThreads) var_combine_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+    const ReducePlan &p = a.plan;
+    const Moments *partials = static_cast<const Moments *>(a.partials);
+    for (int64_t o = blockIdx.x * static_cast<int64_t>(kRThreads) + threadIdx.x; o < p.nout;
+         o += static_cast<int64_t>(gridDim.x) * kRThreads) {
+        double n = 0.0, mean = 0.0, m2 = 0.0;
+        for (int64_t c = 0; c < p.splits; ++c) {
+            const int64_t j0 = c * p.chunk;
+            const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
+            const Moments m = partials[c * p.nout + o];
+            merge_moments(n, mean, m2, static_cast<double>(j1 - j0), m.mean, m.m2);
+        }
+        sink.put(o, m2, p.nred);
+    }
+}
+
 }  // namespace
 
 hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs &a, double correction, int take_sqrt,
@@ -82,6 +222,16 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
             else if (p.group == 32) deviations_kernel<32, T><<<grid, kRThreads, 0, ctx->stream>>>(a, sink);
             else deviations_kernel<1, T><<<grid, kRThreads, 0, ctx->stream>>>(a, sink);
             return launch_status("var kernel launch");
+        }
+        if constexpr (!std::is_same_v<T, double>) {
+            if (p.kind == 1) {
+                dim3 grid(clamp_grid(p.kouter * p.xtiles, 1 << 20), static_cast<unsigned>(p.splits));
+                var_columns_kernel<T><<<grid, kRThreads, 0, ctx->stream>>>(a, sink);
+                hmc_status s1 = launch_status("var kernel launch");
+                if (s1 != HMC_OK || p.splits == 1) return s1;
+                var_combine_kernel<T><<<clamp_grid((p.nout + kRThreads - 1) / kRThreads, 1 << 16), kRThreads, 0, ctx->stream>>>(a, sink);
+                return launch_status("var combine kernel launch");
+            }
         }
         hmc_status s = launch_reduce(a, FloatFold<T, false>{}, FloatSink<T>{nullptr, means, 2}, ctx->stream);
         if (s != HMC_OK) return s;
