@@ -1,4 +1,5 @@
 // Float sum / prod / mean and var / std.
+#include "math.cuh"
 #include "reduce.cuh"
 
 namespace hmc {
@@ -81,7 +82,7 @@ __device__ __forceinline__ void merge_moments(double &n, double &mean, double &m
     if (nb == 0.0) return;
     const double total = n + nb;
     const double d = mean_b - mean;
-    const double w = nb / total;
+    const double w = nb * reciprocal_short(total);  // counts are small whole numbers: an ulp or two off nb / total
     mean = n == 0.0 ? mean_b : mean + d * w;
     m2 = n == 0.0 ? m2_b : m2 + m2_b + d * d * n * w;
     n = total;
@@ -203,6 +204,92 @@ __global__ void __launch_bounds__(kRThreads) var_combine_kernel(const __grid_con
     }
 }
 
+// ---- variance over rows in one pass ----
+// The same moments for rows that are one unit-stride run of whole, aligned vectors (plan.simple): a lane merges
+// batches of up to four vectors (exact two-pass moments of the 16 or 32 values in registers) into its
+// (count, mean, M2), the lanes of a row are merged in lane order by shuffles and, for 256 lanes, the warps in
+// warp order through shared memory. The row is read once; the two-pass kernel above reads it twice and misses
+// the caches for part of the second walk.
+template <class T, int N>
+__device__ __forceinline__ void batch_moments(const double (&v)[N], double &mean_b, double &m2_b) {
+    double s = 0.0;
+#pragma unroll
+    for (int i = 0; i < N; ++i) s += v[i];
+    mean_b = s * (1.0 / N);
+    double sq = 0.0;
+#pragma unroll
+    for (int i = 0; i < N; ++i) sq += (v[i] - mean_b) * (v[i] - mean_b);
+    m2_b = sq;
+}
+
+template <int G, class T>
+__global__ void __launch_bounds__(kRThreads) var_rows_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+    constexpr int P = kRThreads / G;
+    constexpr int VEC = 16 / sizeof(T);
+    constexpr int UNR = 4;
+    const ReducePlan &p = a.plan;
+    const int lane = threadIdx.x % G;
+    const int slot = threadIdx.x / G;
+    __shared__ double warp_n[8], warp_mean[8], warp_m2[8];
+    const uint32_t nvec = static_cast<uint32_t>(p.nred) / VEC;
+    const int64_t tiles = (p.nout + P - 1) / P;
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int64_t o = tile * P + slot;
+        const bool valid = o < p.nout;
+        double n = 0.0, mean = 0.0, m2 = 0.0;
+        if (valid) {
+            const T *row = static_cast<const T *>(a.kept.data) + a.kept.offset + decompose(a.kept, o, a.kept.ndim);
+            uint32_t v = lane;
+            for (; v + (UNR - 1) * G < nvec; v += UNR * G) {
+                RVec<T, VEC> x[UNR];
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VEC> *>(row + static_cast<size_t>(v + u * G) * VEC);
+                double w[UNR * VEC];
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) w[u * VEC + e] = to_f64(x[u].v[e]);
+                }
+                double mb, sq;
+                batch_moments<T, UNR * VEC>(w, mb, sq);
+                merge_moments(n, mean, m2, static_cast<double>(UNR * VEC), mb, sq);
+            }
+            for (; v < nvec; v += G) {
+                const RVec<T, VEC> x = *reinterpret_cast<const RVec<T, VEC> *>(row + static_cast<size_t>(v) * VEC);
+                double w[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) w[e] = to_f64(x.v[e]);
+                double mb, sq;
+                batch_moments<T, VEC>(w, mb, sq);
+                merge_moments(n, mean, m2, static_cast<double>(VEC), mb, sq);
+            }
+        }
+        if constexpr (G > 1) {
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                const double on = __shfl_down_sync(0xFFFFFFFFu, n, d);
+                const double om = __shfl_down_sync(0xFFFFFFFFu, mean, d);
+                const double o2 = __shfl_down_sync(0xFFFFFFFFu, m2, d);
+                merge_moments(n, mean, m2, on, om, o2);
+            }
+        }
+        if constexpr (G == 256) {
+            const int warp = threadIdx.x >> 5;
+            if ((threadIdx.x & 31) == 0) {
+                warp_n[warp] = n;
+                warp_mean[warp] = mean;
+                warp_m2[warp] = m2;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int w = 1; w < 8; ++w) merge_moments(n, mean, m2, warp_n[w], warp_mean[w], warp_m2[w]);
+            }
+            __syncthreads();
+        }
+        if (lane == 0 && valid) sink.put(o, m2, p.nred);
+    }
+}
+
 }  // namespace
 
 hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs &a, double correction, int take_sqrt,
@@ -215,6 +302,19 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
         if (!(divisor > 0.0)) divisor = 0.0;
         VarSink<T> sink{o, divisor, take_sqrt};
         if (p.kind == 0 && p.splits == 1) {
+            if constexpr (!std::is_same_v<T, double>) {
+                // every row one aligned run of whole vectors: the one-pass kernel
+                bool aligned = p.simple && p.group > 1 &&
+                               (reinterpret_cast<uintptr_t>(a.kept.data) + static_cast<uintptr_t>(a.kept.offset) * sizeof(T)) % 16 == 0;
+                for (int k = 0; k < a.kept.ndim; ++k) aligned = aligned && (a.kept.strides[k] * static_cast<int64_t>(sizeof(T))) % 16 == 0;
+                if (aligned) {
+                    const int64_t per = kRThreads / p.group;
+                    const unsigned g = clamp_grid((p.nout + per - 1) / per, 1 << 20);
+                    if (p.group == 256) var_rows_kernel<256, T><<<g, kRThreads, 0, ctx->stream>>>(a, sink);
+                    else var_rows_kernel<32, T><<<g, kRThreads, 0, ctx->stream>>>(a, sink);
+                    return launch_status("var kernel launch");
+                }
+            }
             const int64_t per_block = kRThreads / p.group;
             const int64_t tiles = (p.nout + per_block - 1) / per_block;
             unsigned grid = clamp_grid(tiles, 1 << 20);

@@ -129,15 +129,6 @@ __device__ __forceinline__ double row_sum_f64(double v, double *scratch) {
     }
     return v;
 }
-// 1 / s for a finite s >= 1 (or NaN) to within an f64 ulp or two: the hardware's 20-bit estimate and two Newton
-// steps, a quarter of the instructions of the IEEE division. For results that are rounded to 24 bits or fewer.
-__device__ __forceinline__ double reciprocal_short(double s) {
-    double r;
-    asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(r) : "d"(s));
-    r = __fma_rn(r, __fma_rn(-s, r, 1.0), r);
-    r = __fma_rn(r, __fma_rn(-s, r, 1.0), r);
-    return r;
-}
 // max(x, y) that keeps a NaN (fmaxf drops it).
 __device__ __forceinline__ float max_keep_nan(float x, float y) {
     float r;
