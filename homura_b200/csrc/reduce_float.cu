@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kRThreads) deviations_kernel(const __grid_cons
 // indices j, j + 8, ...), but instead of a pass for the means and a pass for the deviations a thread keeps
 // (count, mean, M2 = sum of squared deviations from that mean) per output and merges batches of four rows into
 // them with the pairwise update of Chan, Golub and LeVeque: the batch's own mean and M2 first (exact two-pass
-// on four values), then mean += d * 4 / n, M2 += M2_batch + d * d * (n - 4) * 4 / n with d = batch mean - mean.
+// on its B values), then mean += d * B / n, M2 += M2_batch + d * d * (n - B) * B / n with d = batch mean - mean.
 // All in f64: the result differs from the two-pass value by a few f64 ulps, far below the rounding to F16,
 // BF16 or F32 (F64 tensors keep the two passes). One read of the source instead of two.
 struct Moments {
@@ -91,7 +91,7 @@ __device__ __forceinline__ void merge_moments(double &n, double &mean, double &m
 template <class T>
 __global__ void __launch_bounds__(kRThreads) var_columns_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
     constexpr int VC = (16 / sizeof(T)) > 8 ? 8 : (16 / sizeof(T));
-    constexpr int UNR = 4;
+    constexpr int UNR = 4;  // rows of a batch, all in flight at once (8 measured slower: registers)
     const ReducePlan &p = a.plan;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int64_t chunk = blockIdx.y;
@@ -137,7 +137,10 @@ __global__ void __launch_bounds__(kRThreads) var_columns_kernel(const __grid_con
                     double v[UNR];
 #pragma unroll
                     for (int u = 0; u < UNR; ++u) v[u] = to_f64(x[u].v[e]);
-                    const double mb = ((v[0] + v[1]) + (v[2] + v[3])) * (1.0 / UNR);
+                    double sum = 0.0;
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) sum += v[u];
+                    const double mb = sum * (1.0 / UNR);
                     double sq = 0.0;
 #pragma unroll
                     for (int u = 0; u < UNR; ++u) sq += (v[u] - mb) * (v[u] - mb);
