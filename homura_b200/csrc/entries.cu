@@ -116,6 +116,14 @@ HMC_API hmc_status hmc_binary_constant(hmc_context_t ctx, int32_t op, const hmc_
             return HMC_OK;
         }
         MapOperand t = tensor_operand(a), c = constant_operand(bits);
+        // x ** 2 (the square in a norm or a variance) is x * x, as the power kernel itself evaluates it: the product
+        // kernel gives the same bits without carrying the general power's code and registers.
+        // (F16, BF16 and F32, whose power is evaluated in f32; an F64 power stays with the f64 library)
+        if (op == HMC_BINARY_POW && !constant_first && dtype_is_float(a->dtype) && a->dtype != HMC_F64 && out->dtype == a->dtype) {
+            const uint64_t two = a->dtype == HMC_F32 ? 0x40000000ull : 0x4000ull;
+            const uint64_t mask = a->dtype == HMC_F32 ? 0xFFFFFFFFull : 0xFFFFull;
+            if ((bits & mask) == two) return binary_dispatch(ctx, HMC_BINARY_MUL, a->dtype, out, t, t);
+        }
         return constant_first ? binary_dispatch(ctx, op, a->dtype, out, c, t) : binary_dispatch(ctx, op, a->dtype, out, t, c);
     });
 }
