@@ -624,9 +624,12 @@ __device__ __forceinline__ void tile_gather(Pack<T, GA * NB> &dst, const unsigne
                                             const T *p, int64_t sa, int64_t sb, int a0, int b0, int na, int nvalid) {
     if constexpr (!std::is_same_v<T, Unused>) {
         if (tiled) {
+            // b0 is a multiple of NB, so the NB rows of a task share one chunk permutation: one address, then
+            // constant row steps
+            const unsigned char *first = tile + tile_offset<T, NB, TD>(b0, a0);
 #pragma unroll
             for (int j = 0; j < NB; ++j) {
-                const Pack<T, GA> w = *reinterpret_cast<const Pack<T, GA> *>(tile + tile_offset<T, NB, TD>(b0 + j, a0));
+                const Pack<T, GA> w = *reinterpret_cast<const Pack<T, GA> *>(first + j * (TD * static_cast<int>(sizeof(T))));
 #pragma unroll
                 for (int g = 0; g < GA; ++g) dst.v[g * NB + j] = w.v[g];
             }
