@@ -47,8 +47,8 @@ L2_BYTES = 126 << 20
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel of the c2 step, from one `ncu --set full`
 # capture on B200 (profiles/c2_step_elementwise_kernels.md). Writes are below the algorithmic output where the
 # tail of the output still sits in L2 when the capture ends.
-NCU_TRAFFIC_BYTES = {"silu": 221.6e6, "mul_scale": 209.3e6, "add_bias": 346.4e6, "silu_t": 217.5e6, "mul_scale_t": 209.7e6,
-                     "add_bias_t": 345.2e6, "cast": 345.0e6}
+NCU_TRAFFIC_BYTES = {"silu": 219.4e6, "mul_scale": 215.7e6, "add_bias": 345.7e6, "silu_t": 218.6e6, "mul_scale_t": 217.0e6,
+                     "add_bias_t": 347.3e6, "cast": 346.2e6}
 
 
 def philox_normal(n: int, seed: int) -> np.ndarray:
