@@ -608,6 +608,31 @@ class CudaBackend:
         o, i = descs("flip", [out, flipped])
         self._check(self.lib.hmc_flip(self.ctx, o, i))
 
+    def index_check(self, index: TensorData, low: int, high: int, exempt=None):
+        """(position, value) of the first index element outside [low, high) that is not `exempt`, or None."""
+        if index.numel == 0:
+            return None
+        d, = descs("index_check", [index])
+        slot = self.storage(16)
+        self._check(self.lib.hmc_index_check(self.ctx, d, low, high, int(exempt is not None), exempt or 0,
+                                             ctypes.cast(slot.ptr, ctypes.POINTER(ctypes.c_uint64))))
+        words = np.empty(2, dtype=np.uint64)
+        self._check(self.lib.hmc_copy_to_host(self.ctx, words.ctypes.data, slot.ptr, 16))
+        return None if int(words[0]) == 2**64 - 1 else (int(words[0]), int(words[1:].view(np.int64)[0]))
+
+    def index_select(self, out: TensorData, src: TensorData, dim: int, index: TensorData, wrap_negative: bool = False) -> None:
+        if out.numel == 0:
+            return
+        o, s, i, at = index_select_descs("index_select", out, src, dim, index)
+        self._check(self.lib.hmc_index_select(self.ctx, o, s, i, at, int(wrap_negative)))
+
+    def gather(self, out: TensorData, src: TensorData, dim: int, index: TensorData) -> None:
+        if out.numel == 0:
+            return
+        (o, s, i), at = around("gather", [out, src, index], tuple(out.shape), dim)
+        s.sizes[at] = src.shape[dim]
+        self._check(self.lib.hmc_gather(self.ctx, o, s, i, at))
+
     def addr(self, out: TensorData, v1: TensorData, v2: TensorData, input: Optional[TensorData], alpha, beta) -> None:
         """out = beta * input + alpha * outer(v1, v2) with the CPU kernel's steps (hmc_addr)."""
         d, a, b, ai, bi = addr_operands("addr", out, v1, v2, input, alpha, beta)
@@ -632,6 +657,32 @@ class CudaBackend:
             return
         sc = adamw_scalars(param.dtype, lr, beta1, beta2, eps, weight_decay, step)
         self._check(self.lib.hmc_adamw_step(self.ctx, d[0], d[1], d[2], d[3], ctypes.byref(sc)))
+
+
+def around(kernel: str, operands: Sequence[TensorData], shape: Sequence[int], dim: int):
+    """Descriptions with the dimensions before `dim` and those after it merged, `dim` kept in between, and the position
+    of `dim` among them (src/backend/rocm/index.rs:62-84). `shape` has elements."""
+    strides = [t.strides for t in operands]
+    part = lambda lo, hi: merge_dims(shape[lo:hi], [st[lo:hi] for st in strides]) or []
+    dims = list(part(0, dim))
+    at = len(dims)
+    dims.append((shape[dim], [st[dim] for st in strides]))
+    dims.extend(part(dim + 1, len(shape)))
+    return descs_with_dims(kernel, operands, [t.offset for t in operands], dims), at
+
+
+def index_select_descs(kernel: str, out: TensorData, src: TensorData, dim: int, index: TensorData):
+    """(out, src, 1-D index, position of dim) as homura's glue passes them (src/backend/rocm/index.rs:221-270)."""
+    shape = tuple(out.shape)
+    strides = [0] * len(shape)
+    strides[dim] = index.strides[0] if len(index.shape) else 0
+    walk = TensorData(index.storage, index.dtype, shape, tuple(strides), index.offset)
+    (o, s, w), at = around(kernel, [out, src, walk], shape, dim)
+    s.sizes[at] = src.shape[dim]
+    i = hmc_tensor_desc()
+    i.data, i.offset, i.dtype, i.ndim = w.data, w.offset, w.dtype, 1
+    i.sizes[0], i.strides[0] = w.sizes[at], w.strides[at]
+    return o, s, i, at
 
 
 def addr_operands(kernel: str, out: TensorData, v1: TensorData, v2: TensorData, input: Optional[TensorData], alpha, beta):

@@ -294,6 +294,27 @@ hmc_status hmc_addr(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_ten
 hmc_status hmc_exclusive_cumprod(hmc_context_t ctx, const hmc_tensor_desc *out_lines, const hmc_tensor_desc *src_lines,
                                  int64_t n, int64_t out_stride, int64_t src_stride, int32_t reverse);
 
+/* ---- gathers (the read side of csrc/index.hip). Index tensors are I32 or I64; positions are checked first
+ * (hmc_index_check), so the gathers take them as valid. ---- */
+
+/* The first element of `index`, in row-major order of its logical positions, that is outside [low, high) and,
+ * if has_exempt, not equal to `exempt`: queues writing its position to slot[0] (UINT64_MAX if there is none) and
+ * its value to slot[1]. `slot` is two 64-bit words of device memory. csrc/homura_rocm.h:357-363 */
+hmc_status hmc_index_check(hmc_context_t ctx, const hmc_tensor_desc *index, int64_t low, int64_t high,
+                           int32_t has_exempt, int64_t exempt, uint64_t *slot);
+
+/* cpu::index_select (src/backend/cpu/misc.rs:77-103; an embedding lookup is this along dimension 0): out (src's
+ * sizes but `index`'s length along dim) gets the slices of src along dim at the positions of the 1-D `index`,
+ * negative ones counted from the end if wrap_negative. out and src have the same number of dimensions.
+ * csrc/homura_rocm.h:365-370 */
+hmc_status hmc_index_select(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src,
+                            const hmc_tensor_desc *index, int32_t dim, int32_t wrap_negative);
+
+/* cpu::gather (src/backend/cpu/misc.rs:319-342): out (index's sizes) gets src at each index position with the
+ * coordinate along dim replaced by the index element. csrc/homura_rocm.h:372-375 */
+hmc_status hmc_gather(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src,
+                      const hmc_tensor_desc *index, int32_t dim);
+
 /* ---- additions of this backend (no counterpart in csrc/homura_rocm.h) ---- */
 
 /* hmc_reduce without a workspace argument, for callers that cannot allocate one when they need the

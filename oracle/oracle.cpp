@@ -1097,6 +1097,72 @@ int orc_exclusive_cumprod(const hmc_tensor_desc *out_lines, const hmc_tensor_des
     });
 }
 
+// ---- gathers (src/backend/cpu/misc.rs) ----
+static inline int64_t index_value(const hmc_tensor_desc *index, int64_t at) {
+    return index->dtype == HMC_I32 ? (int64_t)((const int32_t *)index->data)[at] : ((const int64_t *)index->data)[at];
+}
+
+// The first index element, in row-major order, outside [low, high) and not the exempt value: slot[0] its position
+// (UINT64_MAX for none), slot[1] its value. What `positions` (src/backend/cpu/misc.rs:30-75) reports in its panic.
+int orc_index_check(const hmc_tensor_desc *index, int64_t low, int64_t high, int32_t has_exempt, int64_t exempt, uint64_t *slot) {
+    if (index->dtype != HMC_I32 && index->dtype != HMC_I64) return 2;
+    slot[0] = ~0ull;
+    slot[1] = 0;
+    const int64_t *st[1] = {index->strides};
+    int64_t base[1] = {index->offset};
+    uint64_t position = 0;
+    walk<1>(index->ndim, index->sizes, st, base, [&](const int64_t *o) {
+        const int64_t v = index_value(index, o[0]);
+        const bool bad = (v < low || v >= high) && !(has_exempt && v == exempt);
+        if (bad && slot[0] == ~0ull) { slot[0] = position; slot[1] = (uint64_t)v; }
+        position += 1;
+    });
+    return 0;
+}
+
+// cpu::index_select, operands given like the device entry point. src/backend/cpu/misc.rs:77-103.
+int orc_index_select(const hmc_tensor_desc *out, const hmc_tensor_desc *src, const hmc_tensor_desc *index, int32_t dim,
+                     int32_t wrap_negative) {
+    if (out->dtype != src->dtype || out->ndim != src->ndim || dim < 0 || dim >= out->ndim) return 2;
+    const int64_t size = src->sizes[dim];
+    const int64_t istride = index->ndim == 0 ? 0 : index->strides[0];
+    return dispatch_all(src->dtype, [&](auto t) {
+        using T = decltype(t);
+        const T *ps = (const T *)src->data;
+        T *po = (T *)out->data;
+        // walk out with src's strides, the stride along dim set to 0, and a counter along dim for the index
+        hmc_tensor_desc walk_src = *src, counter = *out;
+        walk_src.strides[dim] = 0;
+        for (int k = 0; k < out->ndim; ++k) counter.strides[k] = k == dim ? 1 : 0;
+        const int64_t *st[3] = {out->strides, walk_src.strides, counter.strides};
+        int64_t base[3] = {out->offset, src->offset, 0};
+        walk<3>(out->ndim, out->sizes, st, base, [&](const int64_t *o) {
+            int64_t j = index_value(index, index->offset + o[2] * istride);
+            if (wrap_negative && j < 0) j += size;
+            po[o[0]] = ps[o[1] + j * src->strides[dim]];
+        });
+        return 0;
+    });
+}
+
+// cpu::gather. src/backend/cpu/misc.rs:319-342.
+int orc_gather(const hmc_tensor_desc *out, const hmc_tensor_desc *src, const hmc_tensor_desc *index, int32_t dim) {
+    if (out->dtype != src->dtype || out->ndim != src->ndim || out->ndim != index->ndim || dim < 0 || dim >= out->ndim) return 2;
+    return dispatch_all(src->dtype, [&](auto t) {
+        using T = decltype(t);
+        const T *ps = (const T *)src->data;
+        T *po = (T *)out->data;
+        hmc_tensor_desc walk_src = *src;
+        walk_src.strides[dim] = 0;
+        const int64_t *st[3] = {out->strides, walk_src.strides, index->strides};
+        int64_t base[3] = {out->offset, src->offset, index->offset};
+        walk<3>(out->ndim, out->sizes, st, base, [&](const int64_t *o) {
+            po[o[0]] = ps[o[1] + index_value(index, o[2]) * src->strides[dim]];
+        });
+        return 0;
+    });
+}
+
 // Scalar conversions exposed for the tests of the cast tables (src/dtype.rs:543-665).
 uint16_t orc_f32_to_f16(float f) { return f32_to_f16(f); }
 uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16(f); }

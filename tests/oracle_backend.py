@@ -35,6 +35,8 @@ def _load_oracle():
         "orc_random_uniform": [i32, vp, i64, u64, u64, f64, f64], "orc_random_normal": [i32, vp, i64, u64, u64, f64, f64],
         "orc_random_int": [vp, i64, u64, u64, i64, i64, ctypes.POINTER(u64)],
         "orc_triangle": [D, D, i64, i32], "orc_flip": [D, D],
+        "orc_index_check": [D, i64, i64, i32, i64, ctypes.POINTER(u64)], "orc_index_select": [D, D, D, i32, i32],
+        "orc_gather": [D, D, D, i32],
         "orc_addr": [D, D, D, D, f64, f64, i64, i64], "orc_exclusive_cumprod": [D, D, i64, i64, i64, i32],
     }
     for name, args in protos.items():
@@ -219,6 +221,29 @@ class OracleBackend:
         flipped = TensorData(src.storage, src.dtype, tuple(src.shape), tuple(strides), offset)
         o, i = descs("flip", [out, flipped])
         self._check(self.lib.orc_flip(o, i))
+
+    def index_check(self, index, low, high, exempt=None):
+        if index.numel == 0:
+            return None
+        d, = descs("index_check", [index])
+        slot = (ctypes.c_uint64 * 2)()
+        self._check(self.lib.orc_index_check(d, low, high, int(exempt is not None), exempt or 0, slot))
+        return None if slot[0] == 2**64 - 1 else (int(slot[0]), int(np.array([slot[1]], dtype=np.uint64).view(np.int64)[0]))
+
+    def index_select(self, out, src, dim, index, wrap_negative=False):
+        from homura_b200.host import index_select_descs
+        if out.numel == 0:
+            return
+        o, s, i, at = index_select_descs("index_select", out, src, dim, index)
+        self._check(self.lib.orc_index_select(o, s, i, at, int(wrap_negative)))
+
+    def gather(self, out, src, dim, index):
+        from homura_b200.host import around
+        if out.numel == 0:
+            return
+        (o, s, i), at = around("gather", [out, src, index], tuple(out.shape), dim)
+        s.sizes[at] = src.shape[dim]
+        self._check(self.lib.orc_gather(o, s, i, at))
 
     def addr(self, out, v1, v2, input, alpha, beta):
         from homura_b200.host import addr_operands

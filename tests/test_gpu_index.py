@@ -1,0 +1,102 @@
+"""index_check, index_select (embedding lookups) and gather against the CPU checker through the C ABI: bit for bit,
+for every element size, I32 and I64 indices, negative positions, repeated positions, views and every dimension."""
+import numpy as np
+import pytest
+
+from homura_b200.host import BF16, BOOL, DTYPE_NAMES, F32, F64, I32, I64, U8
+from values import assert_bitwise, values, words
+
+pytestmark = pytest.mark.gpu
+
+
+def both(oracle, cuda, raw, dtype, shape):
+    return oracle.upload(raw, dtype, shape), cuda.upload(raw, dtype, shape)
+
+
+def positions(n, size, seed, negative=False):
+    w = words(seed, n)
+    p = (w % np.uint64(size)).astype(np.int64)
+    if negative:
+        p = np.where((w >> np.uint64(40)) % np.uint64(3) == 0, p - size, p)
+    return p
+
+
+@pytest.mark.parametrize("dtype", [U8, BF16, F32, F64], ids=["u8", "bf16", "f32", "f64"])
+def test_index_select_on_every_dimension(oracle, cuda, dtype):
+    for shape in ((50, 64), (7, 33, 40), (1000, 136), (5, 3, 2, 16), (9,)):
+        n = int(np.prod(shape))
+        so, sg = both(oracle, cuda, values(dtype, n, 500), dtype, shape)
+        for dim in range(len(shape)):
+            for idt, m, neg in ((I64, 77, False), (I32, 5, True), (I64, 1, False)):
+                p = positions(m, shape[dim], 501 + dim, neg)
+                io, ig = both(oracle, cuda, p.astype(np.int32) if idt == I32 else p, idt, (m,))
+                oshape = tuple(m if d == dim else s for d, s in enumerate(shape))
+                oo, go = oracle.empty(oshape, dtype), cuda.empty(oshape, dtype)
+                oracle.index_select(oo, so, dim, io, neg)
+                cuda.index_select(go, sg, dim, ig, neg)
+                assert_bitwise(cuda.download(go), oracle.download(oo), dtype, f"index_select {shape} dim {dim} m {m}")
+    # an embedding table read through views: a transposed table, a strided index, an output window
+    v, d_ = 300, 128
+    to, tg = both(oracle, cuda, values(dtype, v * d_, 510), dtype, (d_, v))
+    p = positions(64, v, 511)
+    io, ig = both(oracle, cuda, np.stack([p, p[::-1]], axis=1), I64, (64, 2))
+    bo, bg = oracle.empty((70, d_), dtype), cuda.empty((70, d_), dtype)
+    oracle.fill(bo, 0)
+    cuda.fill(bg, 0)
+    oracle.index_select(bo.narrow(0, 3, 64), to.t(), 0, io.select(1, 1))
+    cuda.index_select(bg.narrow(0, 3, 64), tg.t(), 0, ig.select(1, 1))
+    assert_bitwise(cuda.download(bg), oracle.download(bo), dtype, "index_select through views")
+
+
+@pytest.mark.parametrize("dtype", [BOOL, BF16, F32, I64], ids=["bool", "bf16", "f32", "i64"])
+def test_gather_on_every_dimension(oracle, cuda, dtype):
+    for shape, ishape in (((40, 50), (40, 50)), ((40, 50), (13, 7)), ((6, 9, 20), (6, 4, 20)), ((6, 9, 20), (2, 9, 3)), ((31,), (100,))):
+        n = int(np.prod(shape))
+        so, sg = both(oracle, cuda, values(dtype, n, 520), dtype, shape)
+        for dim in range(len(shape)):
+            # along `dim` the index may be longer or shorter than src; elsewhere it must not reach beyond it
+            ish = tuple(ishape[d] if d == dim else min(ishape[d], shape[d]) for d in range(len(shape)))
+            m = int(np.prod(ish))
+            for idt in (I64, I32):
+                p = positions(m, shape[dim], 521 + dim)
+                io, ig = both(oracle, cuda, p.astype(np.int32) if idt == I32 else p, idt, ish)
+                oo, go = oracle.empty(ish, dtype), cuda.empty(ish, dtype)
+                oracle.gather(oo, so, dim, io)
+                cuda.gather(go, sg, dim, ig)
+                got = cuda.download(go)
+                assert_bitwise(got, oracle.download(oo), dtype, f"gather {shape} index {ish} dim {dim}")
+    # numpy's take_along_axis agrees where the shapes allow it
+    so, sg = both(oracle, cuda, np.arange(12 * 9, dtype=np.int64), I64, (12, 9))
+    p = positions(12 * 9, 9, 530).reshape(12, 9)
+    _, ig = both(oracle, cuda, p, I64, (12, 9))
+    go = cuda.empty((12, 9), I64)
+    cuda.gather(go, sg, 1, ig)
+    assert (cuda.download(go) == np.take_along_axis(np.arange(108).reshape(12, 9), p, axis=1)).all()
+    # a transposed source and index
+    oo, go = oracle.empty((9, 12), I64), cuda.empty((9, 12), I64)
+    io, ig = both(oracle, cuda, p % 12, I64, (12, 9))
+    oracle.gather(oo, so.t(), 1, io.t())
+    cuda.gather(go, sg.t(), 1, ig.t())
+    assert_bitwise(cuda.download(go), oracle.download(oo), I64, "gather on transposed views")
+
+
+def test_index_check_reports_the_first_offender(oracle, cuda):
+    n = 100003
+    p = positions(n, 1000, 540)
+    for idt in (I64, I32):
+        raw = p.astype(np.int32) if idt == I32 else p.copy()
+        io, ig = both(oracle, cuda, raw, idt, (n,))
+        assert oracle.index_check(io, 0, 1000) is None and cuda.index_check(ig, 0, 1000) is None
+        bad = raw.copy()
+        bad[[77777, 500, 99999]] = [1000, -1001, 5000]
+        io, ig = both(oracle, cuda, bad, idt, (n,))
+        assert cuda.index_check(ig, 0, 1000) == oracle.index_check(io, 0, 1000) == (500, -1001)
+        assert cuda.index_check(ig, -2000, 1000) == oracle.index_check(io, -2000, 1000) == (77777, 1000)
+        # an exempt value (nll_loss's ignore_index) is not an offender
+        assert cuda.index_check(ig, 0, 1000, exempt=-1001) == oracle.index_check(io, 0, 1000, exempt=-1001) == (77777, 1000)
+    # row-major order of the logical positions of a view
+    grid = np.zeros((50, 60), dtype=np.int64)
+    grid[3, 59] = grid[40, 2] = 99
+    io, ig = both(oracle, cuda, grid, I64, (50, 60))
+    assert cuda.index_check(ig.t(), 0, 10) == oracle.index_check(io.t(), 0, 10) == (2 * 50 + 40, 99)
+    assert cuda.index_check(ig, 0, 10) == oracle.index_check(io, 0, 10) == (3 * 60 + 59, 99)
