@@ -334,14 +334,22 @@ class InputsWorkload:
         self.ones = be.empty((m, m), BOOL)
         be.fill(self.ones, True)
         self.mask = be.empty((m, m), BOOL)
+        # an embedding lookup: 32768 rows of a bf16 [128256, 4096] table (Llama-3 vocabulary and width)
+        vocab, width, tokens = 128256, 4096, 32768
+        self.table = be.empty((vocab, width), BF16)
+        be.fill(self.table, 0.5)
+        self.tokens = be.empty((tokens,), I64)
+        be.random_int(self.tokens, self.gen, 0, vocab)
+        self.embedded = be.empty((tokens, width), BF16)
         e = b * m * m
-        self.op_bytes = {"rand_bf16": 2 * self.u.numel, "randn_f32": 4 * self.n.numel, "randint_pow2": 8 * self.i.numel,
+        self.op_bytes = {"embedding_bf16": 4 * tokens * width + 8 * tokens, "rand_bf16": 2 * self.u.numel, "randn_f32": 4 * self.n.numel, "randint_pow2": 8 * self.i.numel,
                          "randint_reject": 8 * self.i.numel, "triu_f32": 4 * e + 2 * e, "mask_bool": m * m + m * m // 2}
-        self.launches_per_step = 9
+        self.launches_per_step = 10
 
     def ops(self):
         be = self.be
         return [
+            ("embedding_bf16", lambda: be.index_select(self.embedded, self.table, 0, self.tokens)),
             ("rand_bf16", lambda: be.random_uniform(self.u, self.gen, 0.0, 1.0)),
             ("randn_f32", lambda: be.random_normal(self.n, self.gen, 0.0, 1.0)),
             ("randint_pow2", lambda: be.random_int(self.i, self.gen, 0, 1 << 16)),

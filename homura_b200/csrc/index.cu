@@ -32,39 +32,60 @@ struct SelectArgs {
     int64_t items;          // work items in all
 };
 
+// Where work item `item` lies: the offsets of its output and source elements.
+template <int VEC>
+__device__ __forceinline__ void select_offsets(const SelectArgs &a, int64_t item, int64_t &oo, int64_t &so) {
+    const int last = a.out.ndim - 1;
+    // (32-bit division where the item number allows: a 64-bit one costs several times as much, per 16 bytes)
+    int64_t rest = a.items < (int64_t{1} << 31) ? static_cast<int64_t>(static_cast<uint32_t>(item) / static_cast<uint32_t>(a.inner))
+                                                : item / a.inner;
+    const int64_t c_last = (item - rest * a.inner) * VEC;
+    oo = c_last * a.out.strides[last];
+    if (last == a.at) {
+        int64_t j = index_at(a.index, a.index_dtype, c_last * a.index_stride);
+        if (a.wrap_negative && j < 0) j += a.size;
+        so = j * a.src.strides[last];
+    } else {
+        so = c_last * a.src.strides[last];
+    }
+    for (int d = last - 1; d >= 0; --d) {
+        const int64_t q = d == 0 ? 0 : rest / a.out.sizes[d];  // the outermost coordinate is what is left
+        const int64_t c = rest - q * a.out.sizes[d];
+        rest = q;
+        oo += c * a.out.strides[d];
+        if (d == a.at) {
+            int64_t j = index_at(a.index, a.index_dtype, c * a.index_stride);
+            if (a.wrap_negative && j < 0) j += a.size;
+            so += j * a.src.strides[d];
+        } else {
+            so += c * a.src.strides[d];
+        }
+    }
+}
+
 // Work item -> coordinates of out (the innermost one in units of VEC elements); the source offset takes the index
-// element in place of the coordinate along `at`.
+// element in place of the coordinate along `at`. Four items per thread and round, their loads in flight together:
+// the rows of a lookup are scattered over the table, so a thread waits for memory, not for its neighbours.
 template <class W, int VEC>
 __global__ void __launch_bounds__(kIndexThreads) index_select_kernel(const __grid_constant__ SelectArgs a) {
+    constexpr int UNR = 4;
     W *out = static_cast<W *>(a.out.data) + a.out.offset;
     const W *src = static_cast<const W *>(a.src.data) + a.src.offset;
-    const int last = a.out.ndim - 1;
-    for (int64_t item = blockIdx.x * static_cast<int64_t>(kIndexThreads) + threadIdx.x; item < a.items;
-         item += static_cast<int64_t>(gridDim.x) * kIndexThreads) {
-        int64_t rest = item / a.inner;
-        const int64_t c_last = (item - rest * a.inner) * VEC;
-        int64_t oo = c_last * a.out.strides[last], so = 0;
-        if (last == a.at) {
-            int64_t j = index_at(a.index, a.index_dtype, c_last * a.index_stride);
-            if (a.wrap_negative && j < 0) j += a.size;
-            so = j * a.src.strides[last];
-        } else {
-            so = c_last * a.src.strides[last];
-        }
-        for (int d = last - 1; d >= 0; --d) {
-            const int64_t q = rest / a.out.sizes[d];
-            const int64_t c = rest - q * a.out.sizes[d];
-            rest = q;
-            oo += c * a.out.strides[d];
-            if (d == a.at) {
-                int64_t j = index_at(a.index, a.index_dtype, c * a.index_stride);
-                if (a.wrap_negative && j < 0) j += a.size;
-                so += j * a.src.strides[d];
-            } else {
-                so += c * a.src.strides[d];
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kIndexThreads;
+    for (int64_t item = blockIdx.x * static_cast<int64_t>(kIndexThreads) + threadIdx.x; item < a.items; item += UNR * stride) {
+        int64_t oo[UNR], so[UNR];
+        Pack<W, VEC> x[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            if (item + u * stride < a.items) {
+                select_offsets<VEC>(a, item + u * stride, oo[u], so[u]);
+                x[u] = *reinterpret_cast<const Pack<W, VEC> *>(src + so[u]);
             }
         }
-        *reinterpret_cast<Pack<W, VEC> *>(out + oo) = *reinterpret_cast<const Pack<W, VEC> *>(src + so);
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            if (item + u * stride < a.items) *reinterpret_cast<Pack<W, VEC> *>(out + oo[u]) = x[u];
+        }
     }
 }
 
@@ -237,7 +258,7 @@ HMC_API hmc_status hmc_index_select(hmc_context_t ctx, const hmc_tensor_desc *ou
         a.vector = vector;
         a.inner = vector ? out->sizes[last] / vec : out->sizes[last];
         a.items = n / (vector ? vec : 1);
-        const unsigned grid = index_grid(a.items);
+        const unsigned grid = index_grid(ceil_div(a.items, 4));  // four items per thread
         return by_size(src->dtype, [&](auto w) -> hmc_status {
             using W = decltype(w);
             if (vector) index_select_kernel<W, 16 / sizeof(W)><<<grid, kIndexThreads, 0, ctx->stream>>>(a);
