@@ -633,6 +633,45 @@ class CudaBackend:
         s.sizes[at] = src.shape[dim]
         self._check(self.lib.hmc_gather(self.ctx, o, s, i, at))
 
+    def index_overwrite(self, out: TensorData, dim: int, positions: TensorData, src: TensorData) -> None:
+        """Slice i of src along dim -> slice positions[i] of out, the last of repeated positions winning
+        (src/backend/rocm/index.rs:299-340)."""
+        if src.numel == 0:
+            return
+        assert positions.is_contiguous() and positions.dtype == I64
+        (s, o), at = around("index_overwrite", [src, out], tuple(src.shape), dim)
+        o.sizes[at] = out.shape[dim]
+        p = hmc_tensor_desc()
+        p.data, p.offset, p.dtype, p.ndim = positions.storage.address, positions.offset, I64, 1
+        p.sizes[0], p.strides[0] = positions.numel, 1
+        nbytes = ctypes.c_int64()
+        self._check(self.lib.hmc_index_overwrite_workspace(out.shape[dim], ctypes.byref(nbytes)))
+        ws = self.workspace(nbytes.value)
+        self._check(self.lib.hmc_index_overwrite(self.ctx, o, s, p, at, ws.ptr if ws else None, nbytes.value))
+
+    def mask_coordinates(self, mask: TensorData) -> list:
+        """One contiguous I64 tensor of coordinates per dimension of the Bool `mask`, for its true elements in row-major
+        order (nonzero, transposed): count, read the count back, then place."""
+        rank = len(mask.shape)
+        if mask.numel == 0 or rank == 0:
+            count = int(mask.numel and bool(self.download(mask)))
+            return [self.empty((count,), I64) for _ in range(rank)]
+        d = hmc_tensor_desc()
+        d.data, d.offset, d.dtype, d.ndim = mask.storage.address, mask.offset, BOOL, rank
+        for k in range(rank):
+            d.sizes[k], d.strides[k] = mask.shape[k], mask.strides[k]
+        nbytes, word = ctypes.c_int64(), ctypes.c_int64()
+        self._check(self.lib.hmc_mask_workspace(mask.numel, ctypes.byref(nbytes), ctypes.byref(word)))
+        ws = self.storage(nbytes.value)
+        self._check(self.lib.hmc_mask_count(self.ctx, d, ws.ptr, nbytes.value))
+        total = np.empty(1, dtype=np.uint64)
+        self._check(self.lib.hmc_copy_to_host(self.ctx, total.ctypes.data, ws.ptr + 8 * word.value, 8))
+        count = int(total[0])
+        out = self.empty((rank, count), I64)
+        if count:
+            self._check(self.lib.hmc_mask_coordinates(self.ctx, d, ws.ptr, nbytes.value, _flat_desc(out)))
+        return [out.select(0, k) for k in range(rank)]
+
     def addr(self, out: TensorData, v1: TensorData, v2: TensorData, input: Optional[TensorData], alpha, beta) -> None:
         """out = beta * input + alpha * outer(v1, v2) with the CPU kernel's steps (hmc_addr)."""
         d, a, b, ai, bi = addr_operands("addr", out, v1, v2, input, alpha, beta)

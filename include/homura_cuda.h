@@ -315,6 +315,25 @@ hmc_status hmc_index_select(hmc_context_t ctx, const hmc_tensor_desc *out, const
 hmc_status hmc_gather(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src,
                       const hmc_tensor_desc *index, int32_t dim);
 
+/* cpu::index_overwrite (src/backend/cpu/misc.rs:105-125): slice i of src along dim is copied to slice positions[i] of
+ * out, the last of repeated positions winning; slices of out that no position names are left as they are. `positions`
+ * is a contiguous 1-D I64 tensor of valid positions; the workspace has hmc_index_overwrite_workspace bytes for out's
+ * size along dim. csrc/homura_rocm.h:383-390 */
+hmc_status hmc_index_overwrite_workspace(int64_t size, int64_t *bytes);
+hmc_status hmc_index_overwrite(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src,
+                               const hmc_tensor_desc *positions, int32_t dim, void *workspace, int64_t workspace_bytes);
+
+/* cpu::mask_coordinates (src/backend/cpu/misc.rs:127-151; PyTorch's nonzero, transposed) in two calls:
+ * hmc_mask_count queues counting the true elements of the BOOL mask, whose number it leaves at 64-bit word
+ * total_word of the workspace (hmc_mask_workspace bytes for the mask's number of elements); hmc_mask_coordinates
+ * then writes coordinate d of the k-th true element, in row-major order, to out[d][k] (I64, contiguous, the mask's
+ * rank x the number). The mask's description keeps the dimensions whose coordinates are wanted (it is not merged).
+ * csrc/homura_rocm.h:420-429 */
+hmc_status hmc_mask_workspace(int64_t n, int64_t *bytes, int64_t *total_word);
+hmc_status hmc_mask_count(hmc_context_t ctx, const hmc_tensor_desc *mask, void *workspace, int64_t workspace_bytes);
+hmc_status hmc_mask_coordinates(hmc_context_t ctx, const hmc_tensor_desc *mask, void *workspace, int64_t workspace_bytes,
+                                const hmc_tensor_desc *out);
+
 /* ---- additions of this backend (no counterpart in csrc/homura_rocm.h) ---- */
 
 /* hmc_reduce without a workspace argument, for callers that cannot allocate one when they need the

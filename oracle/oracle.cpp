@@ -1163,6 +1163,57 @@ int orc_gather(const hmc_tensor_desc *out, const hmc_tensor_desc *src, const hmc
     });
 }
 
+// cpu::index_overwrite: slice i of src goes to slice positions[i] of out, in order (the last of repeated positions
+// wins). src/backend/cpu/misc.rs:105-125.
+int orc_index_overwrite(const hmc_tensor_desc *out, const hmc_tensor_desc *src, const hmc_tensor_desc *positions, int32_t dim) {
+    if (out->dtype != src->dtype || out->ndim != src->ndim || dim < 0 || dim >= out->ndim || positions->dtype != HMC_I64) return 2;
+    return dispatch_all(src->dtype, [&](auto t) {
+        using T = decltype(t);
+        const T *ps = (const T *)src->data;
+        T *po = (T *)out->data;
+        const int64_t *pp = (const int64_t *)positions->data + positions->offset;
+        // walk src in row-major order (slices in order of i); out's stride along dim is applied through the position
+        hmc_tensor_desc walk_out = *out, counter = *src;
+        walk_out.strides[dim] = 0;
+        for (int k = 0; k < src->ndim; ++k) counter.strides[k] = k == dim ? 1 : 0;
+        const int64_t *st[3] = {src->strides, walk_out.strides, counter.strides};
+        int64_t base[3] = {src->offset, out->offset, 0};
+        // row-major order visits, for every outer coordinate, the slices in order of i: a later i overwrites an earlier one
+        walk<3>(src->ndim, src->sizes, st, base, [&](const int64_t *o) { po[o[1] + pp[o[2]] * out->strides[dim]] = ps[o[0]]; });
+        return 0;
+    });
+}
+
+// cpu::mask_coordinates: the number of true elements, and coordinate d of the k-th one (row-major) in out[d * count + k].
+// src/backend/cpu/misc.rs:127-151.
+int64_t orc_mask_count(const hmc_tensor_desc *mask) {
+    if (mask->dtype != HMC_BOOL) return -1;
+    int64_t count = 0;
+    const int64_t *st[1] = {mask->strides};
+    int64_t base[1] = {mask->offset};
+    walk<1>(mask->ndim, mask->sizes, st, base, [&](const int64_t *o) { count += ((const uint8_t *)mask->data)[o[0]] != 0; });
+    return count;
+}
+int orc_mask_coordinates(const hmc_tensor_desc *mask, int64_t *out, int64_t count) {
+    if (mask->dtype != HMC_BOOL) return 2;
+    int64_t index[HMC_MAX_DIMS] = {0};
+    int64_t k = 0;
+    const int64_t *st[1] = {mask->strides};
+    int64_t base[1] = {mask->offset};
+    walk<1>(mask->ndim, mask->sizes, st, base, [&](const int64_t *o) {
+        if (((const uint8_t *)mask->data)[o[0]] != 0) {
+            for (int d = 0; d < mask->ndim; ++d) out[d * count + k] = index[d];
+            k += 1;
+        }
+        for (int d = mask->ndim - 1; d >= 0; --d) {
+            index[d] += 1;
+            if (index[d] < mask->sizes[d]) break;
+            index[d] = 0;
+        }
+    });
+    return 0;
+}
+
 // Scalar conversions exposed for the tests of the cast tables (src/dtype.rs:543-665).
 uint16_t orc_f32_to_f16(float f) { return f32_to_f16(f); }
 uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16(f); }

@@ -36,7 +36,7 @@ def _load_oracle():
         "orc_random_int": [vp, i64, u64, u64, i64, i64, ctypes.POINTER(u64)],
         "orc_triangle": [D, D, i64, i32], "orc_flip": [D, D],
         "orc_index_check": [D, i64, i64, i32, i64, ctypes.POINTER(u64)], "orc_index_select": [D, D, D, i32, i32],
-        "orc_gather": [D, D, D, i32],
+        "orc_gather": [D, D, D, i32], "orc_index_overwrite": [D, D, D, i32], "orc_mask_coordinates": [D, vp, i64],
         "orc_addr": [D, D, D, D, f64, f64, i64, i64], "orc_exclusive_cumprod": [D, D, i64, i64, i64, i32],
     }
     for name, args in protos.items():
@@ -47,6 +47,7 @@ def _load_oracle():
     lib.orc_f16_to_f32.restype, lib.orc_f16_to_f32.argtypes = ctypes.c_float, [ctypes.c_uint16]
     lib.orc_bf16_to_f32.restype, lib.orc_bf16_to_f32.argtypes = ctypes.c_float, [ctypes.c_uint16]
     lib.orc_erf.restype, lib.orc_erf.argtypes = f64, [f64]
+    lib.orc_mask_count.restype, lib.orc_mask_count.argtypes = i64, [D]
     lib.orc_philox.restype, lib.orc_philox.argtypes = None, [ctypes.POINTER(ctypes.c_uint32)] * 3
     lib.orc_random_int_batch.restype, lib.orc_random_int_batch.argtypes = i64, [vp, i64, u64, u64, u64, i64, u64, u64]
     return lib
@@ -244,6 +245,29 @@ class OracleBackend:
         (o, s, i), at = around("gather", [out, src, index], tuple(out.shape), dim)
         s.sizes[at] = src.shape[dim]
         self._check(self.lib.orc_gather(o, s, i, at))
+
+    def index_overwrite(self, out, dim, positions, src):
+        from homura_b200.host import around
+        if src.numel == 0:
+            return
+        (s, o), at = around("index_overwrite", [src, out], tuple(src.shape), dim)
+        o.sizes[at] = out.shape[dim]
+        p = hmc_tensor_desc()
+        p.data, p.offset, p.dtype, p.ndim = positions.storage.address, positions.offset, ffi.HMC_I64, 1
+        p.sizes[0], p.strides[0] = positions.numel, 1
+        self._check(self.lib.orc_index_overwrite(o, s, p, at))
+
+    def mask_coordinates(self, mask):
+        rank = len(mask.shape)
+        d = hmc_tensor_desc()
+        d.data, d.offset, d.dtype, d.ndim = mask.storage.address, mask.offset, ffi.HMC_BOOL, rank
+        for k in range(rank):
+            d.sizes[k], d.strides[k] = mask.shape[k], mask.strides[k]
+        count = int(self.lib.orc_mask_count(d))
+        out = self.empty((rank, count), ffi.HMC_I64)
+        if count:
+            self._check(self.lib.orc_mask_coordinates(d, out.storage.array.ctypes.data, count))
+        return [out.select(0, k) for k in range(rank)]
 
     def addr(self, out, v1, v2, input, alpha, beta):
         from homura_b200.host import addr_operands

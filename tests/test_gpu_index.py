@@ -100,3 +100,51 @@ def test_index_check_reports_the_first_offender(oracle, cuda):
     io, ig = both(oracle, cuda, grid, I64, (50, 60))
     assert cuda.index_check(ig.t(), 0, 10) == oracle.index_check(io.t(), 0, 10) == (2 * 50 + 40, 99)
     assert cuda.index_check(ig, 0, 10) == oracle.index_check(io, 0, 10) == (3 * 60 + 59, 99)
+
+
+@pytest.mark.parametrize("dtype", [U8, BF16, F32, F64], ids=["u8", "bf16", "f32", "f64"])
+def test_index_overwrite_last_position_wins(oracle, cuda, dtype):
+    for shape, dim, size in (((300, 40), 0, 100), ((7, 300, 5), 1, 64), ((5, 9), 1, 9), ((2000,), 0, 50), ((3, 4), 0, 10)):
+        m = shape[dim]
+        n = int(np.prod(shape))
+        so, sg = both(oracle, cuda, values(dtype, n, 550), dtype, shape)
+        p = positions(m, size, 551)  # m > size in most cases: many repeated positions
+        po, pg = both(oracle, cuda, p, I64, (m,))
+        oshape = tuple(size if d == dim else s for d, s in enumerate(shape))
+        base = values(dtype, int(np.prod(oshape)), 552)
+        oo, go = both(oracle, cuda, base, dtype, oshape)
+        oracle.index_overwrite(oo, dim, po, so)
+        cuda.index_overwrite(go, dim, pg, sg)
+        assert_bitwise(cuda.download(go), oracle.download(oo), dtype, f"index_overwrite {shape} dim {dim} into {size}")
+    # numpy agrees: assignment with repeated indices keeps the last
+    src = np.arange(20 * 3, dtype=np.int64).reshape(20, 3)
+    p = positions(20, 6, 553)
+    want = np.full((6, 3), -1, dtype=np.int64)
+    want[p] = src
+    out = cuda.upload(np.full((6, 3), -1, dtype=np.int64), I64)
+    cuda.index_overwrite(out, 0, cuda.upload(p, I64), cuda.upload(src, I64))
+    assert (cuda.download(out) == want).all()
+
+
+def test_mask_coordinates_are_nonzero_transposed(oracle, cuda):
+    for shape in ((1000,), (37, 53), (5, 6, 70), (2, 3, 4, 5), (70000,)):
+        n = int(np.prod(shape))
+        for density in (0, 1, 3, 50):
+            w = words(560 + density, n)
+            raw = np.ones(n, dtype=np.uint8) if density == 0 else ((w % np.uint64(density)) == 0).astype(np.uint8)
+            if density == 50:
+                raw[:] = 0 if n > 5000 else raw  # an empty result for the long shapes
+            mo, mg = both(oracle, cuda, raw, BOOL, shape)
+            want, got = oracle.mask_coordinates(mo), cuda.mask_coordinates(mg)
+            assert len(want) == len(got) == len(shape)
+            nz = np.nonzero(raw.reshape(shape))
+            for d in range(len(shape)):
+                g = cuda.download(got[d])
+                assert (g == oracle.download(want[d])).all() and (g == nz[d]).all(), f"coordinates {shape} density {density} dim {d}"
+    # a transposed mask: coordinates follow the view's own row-major order
+    raw = ((words(570, 40 * 90) % np.uint64(4)) == 0).astype(np.uint8)
+    mo, mg = both(oracle, cuda, raw, BOOL, (40, 90))
+    want, got = oracle.mask_coordinates(mo.t()), cuda.mask_coordinates(mg.t())
+    nz = np.nonzero(raw.reshape(40, 90).T)
+    for d in range(2):
+        assert (cuda.download(got[d]) == oracle.download(want[d])).all() and (cuda.download(got[d]) == nz[d]).all()
