@@ -672,6 +672,45 @@ class CudaBackend:
             self._check(self.lib.hmc_mask_coordinates(self.ctx, d, ws.ptr, nbytes.value, _flat_desc(out)))
         return [out.select(0, k) for k in range(rank)]
 
+    def index_add(self, out: TensorData, dim: int, index: TensorData, src: TensorData) -> None:
+        """Slice i of src along dim += into slice index[i] of the contiguous out, in f64 / wrapping i64, in the order of i
+        (src/backend/rocm/index.rs:336-380)."""
+        if src.numel == 0:
+            return
+        m, size = index.numel, out.shape[dim]
+        (o, s), at = around("index_add", [out, src], tuple(out.shape), dim)
+        s.sizes[at] = m
+        i = hmc_tensor_desc()
+        i.data, i.offset, i.dtype, i.ndim = index.storage.address, index.offset, index.dtype, 1
+        i.sizes[0], i.strides[0] = m, index.strides[0] if index.shape else 1
+        nbytes = ctypes.c_int64()
+        self._check(self.lib.hmc_index_add_workspace(m, size, ctypes.byref(nbytes)))
+        ws = self.workspace(nbytes.value)
+        self._check(self.lib.hmc_index_add(self.ctx, o, s, i, at, ws.ptr if ws else None, nbytes.value))
+
+    def scatter_add(self, out: TensorData, dim: int, index: TensorData, src: TensorData) -> None:
+        """out[.., index[p], ..] += src[p] for every position p of the index, in row-major order
+        (src/backend/rocm/index.rs:382-417)."""
+        n = index.numel
+        if n == 0:
+            return
+        (i, o, s), at = around("scatter_add", [index, out, src], tuple(index.shape), dim)
+        o.sizes[at] = out.shape[dim]
+        nbytes = ctypes.c_int64()
+        self._check(self.lib.hmc_scatter_add_workspace(n, ctypes.byref(nbytes)))
+        ws = self.workspace(nbytes.value)
+        self._check(self.lib.hmc_scatter_add(self.ctx, o, s, i, at, ws.ptr if ws else None, nbytes.value))
+
+    def index_positions(self, out: TensorData, coords: Sequence[TensorData], sizes: Sequence[int]) -> None:
+        """The flat positions of advanced indexing: out (I64) = sum over k of wrapped coords[k] * contiguous stride k of
+        `sizes`, each index broadcast to out's shape; one pass per index (src/backend/rocm/index.rs:618-668)."""
+        if out.numel == 0:
+            return
+        strides = contiguous_strides(sizes)
+        for k, c in enumerate(coords):
+            d = descs("index_positions", [out, c.expand(out.shape)])
+            self._check(self.lib.hmc_index_positions(self.ctx, d[0], d[1], sizes[k], strides[k], int(k == 0)))
+
     def addr(self, out: TensorData, v1: TensorData, v2: TensorData, input: Optional[TensorData], alpha, beta) -> None:
         """out = beta * input + alpha * outer(v1, v2) with the CPU kernel's steps (hmc_addr)."""
         d, a, b, ai, bi = addr_operands("addr", out, v1, v2, input, alpha, beta)

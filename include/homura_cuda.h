@@ -323,6 +323,29 @@ hmc_status hmc_index_overwrite_workspace(int64_t size, int64_t *bytes);
 hmc_status hmc_index_overwrite(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src,
                                const hmc_tensor_desc *positions, int32_t dim, void *workspace, int64_t workspace_bytes);
 
+/* cpu::index_add (src/backend/cpu/misc.rs:258-293): slice i of src along dim is added into slice index[i] of out, each
+ * element of out summed in f64 (floats; integers wrap in i64, a Bool is the or) from its own value, in the order of i,
+ * and rounded once. `index` is a 1-D I32 or I64 tensor of m positions (negative ones count from the end; one outside
+ * the dimension adds nothing); the workspace has hmc_index_add_workspace bytes. csrc/homura_rocm.h:390-397 */
+hmc_status hmc_index_add_workspace(int64_t m, int64_t size, int64_t *bytes);
+hmc_status hmc_index_add(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src,
+                         const hmc_tensor_desc *index, int32_t dim, void *workspace, int64_t workspace_bytes);
+
+/* cpu::scatter_add (src/backend/cpu/misc.rs:295-317): src at each index position is added into out at that position
+ * with the coordinate along dim replaced by the index element, summed as hmc_index_add sums, in row-major order of the
+ * index positions. The three descriptions have the same number of dimensions; `index` gives the walked sizes, out its
+ * own size along dim. The workspace has hmc_scatter_add_workspace bytes for the index's number of elements.
+ * csrc/homura_rocm.h:399-406 */
+hmc_status hmc_scatter_add_workspace(int64_t n, int64_t *bytes);
+hmc_status hmc_scatter_add(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src,
+                           const hmc_tensor_desc *index, int32_t dim, void *workspace, int64_t workspace_bytes);
+
+/* One indexed dimension of advanced indexing (cpu::index_positions, src/backend/cpu/misc.rs:154-204): out (I64) = (if
+ * first) or += coord * stride, the coordinate wrapped by `size` when negative; `coord` (I32 or I64) has out's sizes,
+ * broadcast by strides of 0. csrc/homura_rocm.h:376-380 */
+hmc_status hmc_index_positions(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *coord,
+                               int64_t size, int64_t stride, int32_t first);
+
 /* cpu::mask_coordinates (src/backend/cpu/misc.rs:127-151; PyTorch's nonzero, transposed) in two calls:
  * hmc_mask_count queues counting the true elements of the BOOL mask, whose number it leaves at 64-bit word
  * total_word of the workspace (hmc_mask_workspace bytes for the mask's number of elements); hmc_mask_coordinates

@@ -1184,6 +1184,97 @@ int orc_index_overwrite(const hmc_tensor_desc *out, const hmc_tensor_desc *src, 
     });
 }
 
+}  // extern "C"
+
+// add_at (src/backend/cpu/misc.rs:219-256): every element of the contiguous out goes to f64 (floats) or i64 (integers,
+// wrapping; a Bool is the or), takes its contributions in order, and is rounded once. `each` calls back with
+// (offset into out counted from its first element, storage offset of src) per contribution, in the CPU's order.
+template <class T, class Each> static void add_at(T *po, int64_t n, const T *ps, Each &&each) {
+    if constexpr (Tr<T>::kind == kFloat) {
+        std::vector<double> acc(n);
+        for (int64_t k = 0; k < n; ++k) acc[k] = to_f64(po[k]);
+        each([&](int64_t o, int64_t s) { acc[o] += to_f64(ps[s]); });
+        for (int64_t k = 0; k < n; ++k) po[k] = from_f64<T>(acc[k]);
+    } else {
+        std::vector<int64_t> acc(n);
+        for (int64_t k = 0; k < n; ++k) acc[k] = to_i64(po[k]);
+        each([&](int64_t o, int64_t s) { acc[o] = (int64_t)((uint64_t)acc[o] + (uint64_t)to_i64(ps[s])); });
+        for (int64_t k = 0; k < n; ++k) po[k] = from_i64<T>(acc[k]);
+    }
+}
+
+static int64_t span_of(const hmc_tensor_desc *d) {
+    int64_t n = 1;
+    for (int k = 0; k < d->ndim; ++k) {
+        if (d->sizes[k] == 0) return 0;
+        n += (d->sizes[k] - 1) * d->strides[k];
+    }
+    return n;
+}
+
+extern "C" {
+
+// cpu::index_add: slice i of src along dim is added into slice index[i] of out (negative positions count from the
+// end). src/backend/cpu/misc.rs:258-293.
+int orc_index_add(const hmc_tensor_desc *out, const hmc_tensor_desc *src, const hmc_tensor_desc *index, int32_t dim) {
+    if (out->dtype != src->dtype || out->ndim != src->ndim || dim < 0 || dim >= out->ndim || index->dtype != HMC_I64) return 2;
+    const int64_t size = out->sizes[dim];
+    return dispatch_all(src->dtype, [&](auto t) {
+        using T = decltype(t);
+        const int64_t *pi = (const int64_t *)index->data + index->offset;
+        hmc_tensor_desc walk_out = *out, counter = *src;
+        walk_out.strides[dim] = 0;
+        for (int k = 0; k < src->ndim; ++k) counter.strides[k] = k == dim ? 1 : 0;
+        const int64_t *st[3] = {src->strides, walk_out.strides, counter.strides};
+        int64_t base[3] = {src->offset, 0, 0};
+        // row-major order over src visits, for every other coordinate, the slices in order of i
+        add_at<T>((T *)out->data + out->offset, span_of(out), (const T *)src->data, [&](auto add) {
+            walk<3>(src->ndim, src->sizes, st, base, [&](const int64_t *o) {
+                int64_t j = pi[o[2] * index->strides[0]];
+                if (j < 0) j += size;
+                add(o[1] + j * out->strides[dim], o[0]);
+            });
+        });
+        return 0;
+    });
+}
+
+// cpu::scatter_add: out[.., index[p], ..] += src[p] for every position p of the index, in row-major order.
+// src/backend/cpu/misc.rs:295-317.
+int orc_scatter_add(const hmc_tensor_desc *out, const hmc_tensor_desc *src, const hmc_tensor_desc *index, int32_t dim) {
+    if (out->dtype != src->dtype || out->ndim != src->ndim || out->ndim != index->ndim || dim < 0 || dim >= out->ndim ||
+        index->dtype != HMC_I64) {
+        return 2;
+    }
+    return dispatch_all(src->dtype, [&](auto t) {
+        using T = decltype(t);
+        const int64_t *pi = (const int64_t *)index->data;
+        hmc_tensor_desc walk_out = *out;
+        walk_out.strides[dim] = 0;
+        const int64_t *st[3] = {index->strides, walk_out.strides, src->strides};
+        int64_t base[3] = {index->offset, 0, src->offset};
+        add_at<T>((T *)out->data + out->offset, span_of(out), (const T *)src->data, [&](auto add) {
+            walk<3>(index->ndim, index->sizes, st, base, [&](const int64_t *o) { add(o[1] + pi[o[0]] * out->strides[dim], o[2]); });
+        });
+        return 0;
+    });
+}
+
+// One indexed dimension of cpu::index_positions: out = (first) or += wrapped coordinate * stride.
+// src/backend/cpu/misc.rs:154-204.
+int orc_index_positions(const hmc_tensor_desc *out, const hmc_tensor_desc *coord, int64_t size, int64_t stride, int32_t first) {
+    if (out->dtype != HMC_I64 || coord->dtype != HMC_I64 || out->ndim != coord->ndim) return 2;
+    int64_t *po = (int64_t *)out->data;
+    const int64_t *pc = (const int64_t *)coord->data;
+    const int64_t *st[2] = {out->strides, coord->strides};
+    int64_t base[2] = {out->offset, coord->offset};
+    walk<2>(out->ndim, out->sizes, st, base, [&](const int64_t *o) {
+        const int64_t v = pc[o[1]] < 0 ? pc[o[1]] + size : pc[o[1]];
+        po[o[0]] = (first ? 0 : po[o[0]]) + v * stride;
+    });
+    return 0;
+}
+
 // cpu::mask_coordinates: the number of true elements, and coordinate d of the k-th one (row-major) in out[d * count + k].
 // src/backend/cpu/misc.rs:127-151.
 int64_t orc_mask_count(const hmc_tensor_desc *mask) {

@@ -36,7 +36,8 @@ def _load_oracle():
         "orc_random_int": [vp, i64, u64, u64, i64, i64, ctypes.POINTER(u64)],
         "orc_triangle": [D, D, i64, i32], "orc_flip": [D, D],
         "orc_index_check": [D, i64, i64, i32, i64, ctypes.POINTER(u64)], "orc_index_select": [D, D, D, i32, i32],
-        "orc_gather": [D, D, D, i32], "orc_index_overwrite": [D, D, D, i32], "orc_mask_coordinates": [D, vp, i64],
+        "orc_gather": [D, D, D, i32], "orc_index_overwrite": [D, D, D, i32], "orc_index_add": [D, D, D, i32],
+        "orc_scatter_add": [D, D, D, i32], "orc_index_positions": [D, D, i64, i64, i32], "orc_mask_coordinates": [D, vp, i64],
         "orc_addr": [D, D, D, D, f64, f64, i64, i64], "orc_exclusive_cumprod": [D, D, i64, i64, i64, i32],
     }
     for name, args in protos.items():
@@ -256,6 +257,34 @@ class OracleBackend:
         p.data, p.offset, p.dtype, p.ndim = positions.storage.address, positions.offset, ffi.HMC_I64, 1
         p.sizes[0], p.strides[0] = positions.numel, 1
         self._check(self.lib.orc_index_overwrite(o, s, p, at))
+
+    def index_add(self, out, dim, index, src):
+        from homura_b200.host import around
+        if src.numel == 0:
+            return
+        (o, s), at = around("index_add", [out, src], tuple(out.shape), dim)
+        s.sizes[at] = index.numel
+        i = hmc_tensor_desc()
+        i.data, i.offset, i.dtype, i.ndim = index.storage.address, index.offset, index.dtype, 1
+        i.sizes[0], i.strides[0] = index.numel, index.strides[0] if index.shape else 1
+        self._check(self.lib.orc_index_add(o, s, i, at))
+
+    def scatter_add(self, out, dim, index, src):
+        from homura_b200.host import around
+        if index.numel == 0:
+            return
+        (i, o, s), at = around("scatter_add", [index, out, src], tuple(index.shape), dim)
+        o.sizes[at] = out.shape[dim]
+        self._check(self.lib.orc_scatter_add(o, s, i, at))
+
+    def index_positions(self, out, coords, sizes):
+        from homura_b200.host import contiguous_strides, descs
+        if out.numel == 0:
+            return
+        strides = contiguous_strides(sizes)
+        for k, c in enumerate(coords):
+            d = descs("index_positions", [out, c.expand(out.shape)])
+            self._check(self.lib.orc_index_positions(d[0], d[1], sizes[k], strides[k], int(k == 0)))
 
     def mask_coordinates(self, mask):
         rank = len(mask.shape)

@@ -3,7 +3,7 @@ for every element size, I32 and I64 indices, negative positions, repeated positi
 import numpy as np
 import pytest
 
-from homura_b200.host import BF16, BOOL, DTYPE_NAMES, F32, F64, I32, I64, U8
+from homura_b200.host import BF16, BOOL, DTYPE_NAMES, F16, F32, F64, I32, I64, U8, f32_to_half_bits
 from values import assert_bitwise, values, words
 
 pytestmark = pytest.mark.gpu
@@ -148,3 +148,98 @@ def test_mask_coordinates_are_nonzero_transposed(oracle, cuda):
     nz = np.nonzero(raw.reshape(40, 90).T)
     for d in range(2):
         assert (cuda.download(got[d]) == oracle.download(want[d])).all() and (cuda.download(got[d]) == nz[d]).all()
+
+
+ADD_DTYPES = [BOOL, U8, I32, I64, F16, BF16, F32, F64]
+
+
+def small_values(dtype, n, seed):
+    """Values whose sums stay finite in every dtype (floats of mixed magnitude, so that the order of an f64 sum shows)."""
+    w = words(seed, n)
+    if dtype in (F16, BF16, F32, F64):
+        f = ((w % np.uint64(2001)).astype(np.float64) - 1000.0) / 8.0 * (10.0 ** ((w >> np.uint64(20)) % np.uint64(7)).astype(np.float64)) / 1000.0
+        if dtype == F64:
+            return f
+        f32 = f.astype(np.float32)
+        return f32 if dtype == F32 else f32_to_half_bits(f32, dtype)
+    return values(dtype, n, seed)
+
+
+@pytest.mark.parametrize("dtype", ADD_DTYPES, ids=lambda d: f"dt{d}")
+def test_index_add_sums_in_the_order_of_the_positions(oracle, cuda, dtype):
+    for shape, dim, size in (((500, 33), 0, 40), ((6, 700, 5), 1, 90), ((9, 300), 1, 7), ((5000,), 0, 300), ((3, 4), 0, 10),
+                             ((2100, 8), 0, 1)):
+        m = shape[dim]
+        so, sg = both(oracle, cuda, small_values(dtype, int(np.prod(shape)), 600), dtype, shape)
+        p = positions(m, size, 601)
+        p[::7] -= size  # negative positions count from the end
+        po, pg = both(oracle, cuda, p, I64, (m,))
+        oshape = tuple(size if d == dim else s for d, s in enumerate(shape))
+        base = small_values(dtype, int(np.prod(oshape)), 602)
+        oo, go = both(oracle, cuda, base, dtype, oshape)
+        oracle.index_add(oo, dim, po, so)
+        cuda.index_add(go, dim, pg, sg)
+        assert_bitwise(cuda.download(go), oracle.download(oo), dtype, f"index_add {shape} dim {dim} into {size}")
+
+
+def test_index_add_of_a_view_and_against_numpy(oracle, cuda):
+    src = (words(610, 64 * 48) % np.uint64(1000)).astype(np.int64).reshape(64, 48)
+    p = positions(48, 20, 611)
+    so, sg = both(oracle, cuda, src, I64, (64, 48))
+    po, pg = both(oracle, cuda, p, I64, (48,))
+    oo, go = both(oracle, cuda, np.zeros((20, 64), dtype=np.int64), I64, (20, 64))
+    oracle.index_add(oo, 0, po, so.t())
+    cuda.index_add(go, 0, pg, sg.t())
+    want = np.zeros((20, 64), dtype=np.int64)
+    np.add.at(want, p, src.T)
+    assert (cuda.download(go) == want).all() and (oracle.download(oo) == want).all()
+
+
+@pytest.mark.parametrize("dtype", ADD_DTYPES, ids=lambda d: f"dt{d}")
+def test_scatter_add_sums_in_row_major_order(oracle, cuda, dtype):
+    for ishape, sshape, oshape, dim in (((300, 40), (300, 40), (9, 40), 0), ((50, 600), (64, 700), (50, 13), 1),
+                                        ((4, 90, 6), (4, 90, 6), (5, 3, 7), 1), ((7000,), (7000,), (100,), 0),
+                                        ((3, 4), (3, 4), (8, 4), 0)):
+        so, sg = both(oracle, cuda, small_values(dtype, int(np.prod(sshape)), 620), dtype, sshape)
+        idx = positions(int(np.prod(ishape)), oshape[dim], 621)
+        io, ig = both(oracle, cuda, idx, I64, ishape)
+        base = small_values(dtype, int(np.prod(oshape)), 622)
+        oo, go = both(oracle, cuda, base, dtype, oshape)
+        oracle.scatter_add(oo, dim, io, so)
+        cuda.scatter_add(go, dim, ig, sg)
+        assert_bitwise(cuda.download(go), oracle.download(oo), dtype, f"scatter_add {ishape} of {sshape} into {oshape} dim {dim}")
+    # numpy agrees for integers
+    src = (words(630, 30 * 20) % np.uint64(100)).astype(np.int64).reshape(30, 20)
+    idx = positions(30 * 20, 11, 631).reshape(30, 20)
+    out = cuda.upload(np.zeros((11, 20), dtype=np.int64), I64)
+    cuda.scatter_add(out, 0, cuda.upload(idx, I64), cuda.upload(src, I64))
+    want = np.zeros((11, 20), dtype=np.int64)
+    np.add.at(want, (idx, np.arange(20)[None, :].repeat(30, 0)), src)
+    assert (cuda.download(out) == want).all()
+
+
+def test_index_positions_of_broadcast_indices(oracle, cuda):
+    sizes = (7, 11, 5)
+    rows = positions(6, 7, 640).reshape(6, 1) - 7 * (np.arange(6).reshape(6, 1) % 2)  # some negative
+    cols = positions(9, 11, 641).reshape(1, 9)
+    deep = positions(54, 5, 642).reshape(6, 9)
+    got, want = [], []
+    for be, sink in ((oracle, want), (cuda, got)):
+        out = be.empty((6, 9), I64)
+        be.index_positions(out, [be.upload(rows, I64), be.upload(cols, I64), be.upload(deep, I64)], sizes)
+        sink.append(be.download(out))
+    expect = np.ravel_multi_index((np.broadcast_to(rows % 7, (6, 9)), np.broadcast_to(cols, (6, 9)), deep), sizes)
+    assert (got[0] == want[0]).all() and (got[0] == expect).all()
+
+
+def test_index_add_with_many_tiles_and_three_sort_passes(oracle, cuda):
+    m, size = 300_000, 100_000  # 17 bits of position: three passes of eight bits; 293 tiles of 1024 keys
+    so, sg = both(oracle, cuda, small_values(F32, m * 2, 650), F32, (m, 2))
+    p = positions(m, size, 651)
+    p[: m // 3] = 77  # one long run
+    po, pg = both(oracle, cuda, p, I64, (m,))
+    base = small_values(F32, size * 2, 652)
+    oo, go = both(oracle, cuda, base, F32, (size, 2))
+    oracle.index_add(oo, 0, po, so)
+    cuda.index_add(go, 0, pg, sg)
+    assert_bitwise(cuda.download(go), oracle.download(oo), F32, "index_add of 300000 slices into 100000")

@@ -151,3 +151,23 @@ def test_addr_and_exclusive_cumprod_by_hand(oracle):
     assert (oracle.download(y) == np.array([[1, 2, 6], [1, 0.5, 0]], dtype=np.float32)).all()
     oracle.exclusive_cumprod(y, x, 1, True)
     assert (oracle.download(y) == np.array([[12, 4, 1], [0, 7, 1]], dtype=np.float32)).all()
+
+
+def test_index_add_and_scatter_add_by_hand(oracle):
+    """cpu::index_add / scatter_add: f64 sums from the element's own value in the order of the contributions, one
+    rounding (src/backend/cpu/misc.rs:219-317)."""
+    import numpy as np
+    from homura_b200.host import F32, I64, U8
+    # 2^24 + 1 + 1 in f32: added one at a time in f32 the ones are lost; in f64 they are kept and the sum rounds to 2^24 + 2
+    out = oracle.upload(np.array([16777216.0, 5.0], dtype=np.float32), F32)
+    src = oracle.upload(np.array([1.0, 1.0, 2.5], dtype=np.float32), F32)
+    oracle.index_add(out, 0, oracle.upload(np.array([0, -2, 1], dtype=np.int64), I64), src)
+    assert oracle.download(out).tolist() == [16777218.0, 7.5]
+    # integers wrap once, at the end
+    out = oracle.upload(np.array([250, 0], dtype=np.uint8), U8)
+    oracle.index_add(out, 0, oracle.upload(np.array([0, 0, 1], dtype=np.int64), I64), oracle.upload(np.array([3, 4, 9], dtype=np.uint8), U8))
+    assert oracle.download(out).tolist() == [1, 9]
+    out = oracle.upload(np.zeros((2, 3), dtype=np.int64), I64)
+    idx = oracle.upload(np.array([[0, 1, 0], [0, 0, 1]], dtype=np.int64), I64)
+    oracle.scatter_add(out, 0, idx, oracle.upload(np.array([[1, 2, 3], [10, 20, 30]], dtype=np.int64), I64))
+    assert oracle.download(out).tolist() == [[11, 20, 3], [0, 2, 30]]
