@@ -63,30 +63,44 @@ template <class K> struct IndexAddArgs {
     int64_t work;          // m * rest
 };
 
-template <class T, class K>
+// One thread per (sorted position, VEC adjacent elements of its slice); only the first position of a run of equal
+// targets works, and adds the run in order. With VEC > 1 the innermost dimension is contiguous in both tensors and is
+// walked in 16-byte vectors (its size in `sizes` is then counted in vectors).
+template <class T, class K, int VEC>
 __global__ void __launch_bounds__(kAddThreads) index_add_kernel(const __grid_constant__ IndexAddArgs<K> a) {
     using S = Sum<T>;
     T *out = static_cast<T *>(a.out.data) + a.out.offset;
     const T *src = static_cast<const T *>(a.src.data) + a.src.offset;
+    const bool narrow = a.work <= 0xFFFFFFFFll;  // 32-bit divisions
+    const int last = a.out.ndim - 1;
     for (int64_t w = blockIdx.x * static_cast<int64_t>(kAddThreads) + threadIdx.x; w < a.work;
          w += static_cast<int64_t>(gridDim.x) * kAddThreads) {
-        const int64_t k = a.rest == 1 ? w : w / a.rest;
+        const int64_t k = a.rest == 1 ? w : (narrow ? static_cast<int64_t>(static_cast<uint32_t>(w) / static_cast<uint32_t>(a.rest)) : w / a.rest);
         const K key = a.keys[k];
         if (static_cast<int64_t>(key) >= a.size || (k > 0 && a.keys[k - 1] == key)) continue;  // not the first of its run
         int64_t item = w - k * a.rest, oo = 0, so = 0;
-        for (int d = a.out.ndim - 1; d >= 0; --d) {
+        for (int d = last; d >= 0; --d) {
             if (d == a.at) continue;
-            const int64_t q = item / a.out.sizes[d];
-            const int64_t c = item - q * a.out.sizes[d];
+            const int64_t q = narrow ? static_cast<int64_t>(static_cast<uint32_t>(item) / static_cast<uint32_t>(a.out.sizes[d])) : item / a.out.sizes[d];
+            const int64_t c = (item - q * a.out.sizes[d]) * (d == last ? VEC : 1);
             item = q;
             oo += c * a.out.strides[d];
             so += c * a.src.strides[d];
         }
         oo += static_cast<int64_t>(key) * a.out.strides[a.at];
-        typename S::A acc = S::load(out[oo]);
         const int64_t step = a.src.strides[a.at];
-        for (int64_t kk = k; kk < a.m && a.keys[kk] == key; ++kk) acc = S::add(acc, src[so + static_cast<int64_t>(a.vals[kk]) * step]);
-        out[oo] = S::store(acc);
+        Pack<T, VEC> x = *reinterpret_cast<const Pack<T, VEC> *>(out + oo);
+        typename S::A acc[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] = S::load(x.v[e]);
+        for (int64_t kk = k; kk < a.m && a.keys[kk] == key; ++kk) {
+            x = *reinterpret_cast<const Pack<T, VEC> *>(src + so + static_cast<int64_t>(a.vals[kk]) * step);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[e] = S::add(acc[e], x.v[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x.v[e] = S::store(acc[e]);
+        *reinterpret_cast<Pack<T, VEC> *>(out + oo) = x;
     }
 }
 
@@ -248,7 +262,23 @@ HMC_API hmc_status hmc_index_add(hmc_context_t ctx, const hmc_tensor_desc *out, 
             if (st != HMC_OK) return st;
             IndexAddArgs<K> a{*out, *src, space.keys[sorted], space.vals[sorted], dim, m, size, rest, work};
             return dispatch_all(out->dtype, [&](auto t) -> hmc_status {
-                index_add_kernel<decltype(t), K><<<add_grid(work), kAddThreads, 0, ctx->stream>>>(a);
+                using T = decltype(t);
+                constexpr int VEC = 16 / static_cast<int>(sizeof(T));
+                // 16-byte vectors along the innermost dimension where both tensors allow them
+                const int last = out->ndim - 1;
+                bool vector = VEC > 1 && dim != last && out->strides[last] == 1 && src->strides[last] == 1 && out->sizes[last] % VEC == 0 &&
+                              ((reinterpret_cast<uintptr_t>(out->data) + out->offset * sizeof(T)) & 15) == 0 &&
+                              ((reinterpret_cast<uintptr_t>(src->data) + src->offset * sizeof(T)) & 15) == 0;
+                for (int k = 0; k < last && vector; ++k) vector = out->strides[k] % VEC == 0 && src->strides[k] % VEC == 0;
+                if (vector) {
+                    IndexAddArgs<K> v = a;
+                    v.out.sizes[last] /= VEC;
+                    v.rest /= VEC;
+                    v.work /= VEC;
+                    index_add_kernel<T, K, VEC><<<add_grid(v.work), kAddThreads, 0, ctx->stream>>>(v);
+                } else {
+                    index_add_kernel<T, K, 1><<<add_grid(work), kAddThreads, 0, ctx->stream>>>(a);
+                }
                 return launch_status("index_add kernel launch");
             });
         };
