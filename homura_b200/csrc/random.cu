@@ -65,7 +65,9 @@ __device__ __forceinline__ T uniform_value(double u, double from, double width, 
     return (from < to && to_f64(v) >= to) ? first : v;
 }
 
-template <class T>
+// UNIT: from = 0 and to = 1 in a dtype narrower than f64. The sample k * 2^-BITS (k below 2^BITS) is then a value
+// of T itself, so the f64 scaling, the rounding and the comparison with `to` change nothing and are left out.
+template <class T, bool UNIT>
 __global__ void __launch_bounds__(kSampleThreads) uniform_kernel(T *out, int64_t n, uint64_t seed, uint64_t offset, double from,
                                                                   double to) {
     constexpr int PER = std::is_same_v<T, double> ? 2 : 4;
@@ -80,10 +82,14 @@ __global__ void __launch_bounds__(kSampleThreads) uniform_kernel(T *out, int64_t
         Pack<T, PER> v;
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
-            double u;
-            if constexpr (PER == 2) u = unit_f64(r.w[2 * j], r.w[2 * j + 1]);
-            else u = static_cast<double>(r.w[j] >> (32 - BITS)) * (1.0 / static_cast<double>(1u << BITS));  // exact, as the division
-            v.v[j] = uniform_value<T>(u, from, width, to, first);
+            if constexpr (UNIT && PER == 4) {
+                v.v[j] = down<T>(__uint2float_rn(r.w[j] >> (32 - BITS)) * (1.0f / static_cast<float>(1u << BITS)));  // exact
+            } else {
+                double u;
+                if constexpr (PER == 2) u = unit_f64(r.w[2 * j], r.w[2 * j + 1]);
+                else u = static_cast<double>(r.w[j] >> (32 - BITS)) * (1.0 / static_cast<double>(1u << BITS));  // exact, as the division
+                v.v[j] = uniform_value<T>(u, from, width, to, first);
+            }
         }
         const int64_t i0 = b * PER;
         if (aligned && i0 + PER <= n) {
@@ -281,7 +287,11 @@ HMC_API hmc_status hmc_random_uniform(hmc_context_t ctx, const hmc_tensor_desc *
             using T = decltype(t);
             constexpr int per = std::is_same_v<T, double> ? 2 : 4;
             T *p = static_cast<T *>(out->data) + out->offset;
-            uniform_kernel<T><<<sample_grid(ceil_div(n, per)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, from, to);
+            if (per == 4 && from == 0.0 && to == 1.0 && !std::signbit(from)) {
+                uniform_kernel<T, true><<<sample_grid(ceil_div(n, per)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, from, to);
+            } else {
+                uniform_kernel<T, false><<<sample_grid(ceil_div(n, per)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, from, to);
+            }
             return launch_status("uniform sampling kernel launch");
         });
     });
