@@ -342,7 +342,7 @@ class InputsWorkload:
         be.random_int(self.tokens, self.gen, 0, vocab)
         self.embedded = be.empty((tokens, width), BF16)
         # and its backward pass: the rows' gradients added into a table-shaped gradient in token order (index_add:
-        # keys, three sort passes of three launches, the adding kernel); about vocab * (1 - exp(-tokens / vocab))
+        # keys, three sort passes of four launches, the adding kernel); about vocab * (1 - exp(-tokens / vocab))
         # distinct rows are read and written
         self.table_grad = be.empty((vocab, width), BF16)
         be.fill(self.table_grad, 0.0)
@@ -352,7 +352,7 @@ class InputsWorkload:
         self.op_bytes = {"embedding_bf16": 4 * tokens * width + 8 * tokens,
                          "embedding_grad_bf16": 2 * tokens * width + 4 * touched * width + 8 * tokens, "rand_bf16": 2 * self.u.numel, "randn_f32": 4 * self.n.numel, "randint_pow2": 8 * self.i.numel,
                          "randint_reject": 8 * self.i.numel, "triu_f32": 4 * e + 2 * e, "mask_bool": m * m + m * m // 2}
-        self.launches_per_step = 21
+        self.launches_per_step = 24
 
     def ops(self):
         be = self.be

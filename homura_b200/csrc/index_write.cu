@@ -213,7 +213,7 @@ HMC_API hmc_status hmc_mask_count(hmc_context_t ctx, const hmc_tensor_desc *mask
         mask_kernel<false><<<grid, kScanThreads, 0, ctx->stream>>>(a);
         s = launch_status("mask count kernel launch");
         if (s != HMC_OK) return s;
-        tile_starts_kernel<<<1, 1024, 0, ctx->stream>>>(a.counts, a.starts, a.total, a.tiles);
+        launch_tile_starts(ctx->stream, a.counts, a.starts, a.total, a.tiles);
         return launch_status("mask positions kernel launch");
     });
 }

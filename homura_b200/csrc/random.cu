@@ -9,13 +9,14 @@
 //
 // Integer sampling rejects words below a threshold, so where a word lands depends on how many words before
 // it were rejected. A batch is cut into tiles of HMC_RANDOM_INT_TILE blocks: a first kernel counts the accepted
-// words of each tile, a one-block kernel turns the counts into starting positions, and a third kernel
+// words of each tile, a running sum (two launches) turns the counts into starting positions, and a last kernel
 // recomputes the words and writes the accepted ones at their positions, in the CPU's word order.
 #include <math_constants.h>
 
 #include "common.cuh"
 #include "elem.cuh"
 #include "map.cuh"
+#include "scan.cuh"
 
 namespace hmc {
 namespace {
@@ -137,6 +138,24 @@ __device__ __forceinline__ void block_words(uint64_t n, uint64_t seed, uint64_t 
     second = (static_cast<uint64_t>(r.w[2]) << 32) | r.w[3];
 }
 
+// w % range without the general 64-bit division where the range allows: a mask for a power of two; for a range of
+// at most 2^21, the high half is reduced with a 32-bit division, which leaves x = rest * 2^32 + low half below 2^53,
+// exact as an f64, so that x * (1 / range) truncated is the quotient or one beside it and one correction gives the
+// remainder. The branches are the same for every thread of a launch.
+__device__ __forceinline__ uint64_t word_mod(uint64_t w, uint64_t range) {
+    if ((range & (range - 1)) == 0) return w & (range - 1);
+    if (range <= (1u << 21)) {
+        const uint32_t r = static_cast<uint32_t>(range);
+        const uint64_t x = (static_cast<uint64_t>(static_cast<uint32_t>(w >> 32) % r) << 32) | static_cast<uint32_t>(w);
+        const int64_t q = __double2ll_rz(__ll2double_rn(static_cast<int64_t>(x)) * (1.0 / static_cast<double>(r)));
+        int64_t rem = static_cast<int64_t>(x) - q * static_cast<int64_t>(r);
+        if (rem < 0) rem += r;
+        if (rem >= static_cast<int64_t>(r)) rem -= r;
+        return static_cast<uint64_t>(rem);
+    }
+    return w % range;
+}
+
 // threshold == 0: word k of the batch is value k.
 __global__ void __launch_bounds__(kSampleThreads) int_all_kernel(int64_t *out, int64_t n, uint64_t seed, uint64_t offset,
                                                                   uint64_t blocks, int64_t low, uint64_t range) {
@@ -146,8 +165,8 @@ __global__ void __launch_bounds__(kSampleThreads) int_all_kernel(int64_t *out, i
         uint64_t w0, w1;
         block_words(offset + b, seed, w0, w1);
         Pack<int64_t, 2> v;
-        v.v[0] = static_cast<int64_t>(static_cast<uint64_t>(low) + w0 % range);
-        v.v[1] = static_cast<int64_t>(static_cast<uint64_t>(low) + w1 % range);
+        v.v[0] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w0, range));
+        v.v[1] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w1, range));
         const int64_t i0 = static_cast<int64_t>(b) * 2;
         if (aligned && i0 + 2 <= n) {
             *reinterpret_cast<Pack<int64_t, 2> *>(out + i0) = v;
@@ -201,33 +220,6 @@ __global__ void __launch_bounds__(kSampleThreads) int_count_kernel(uint64_t *cou
     }
 }
 
-// starts[t] = counts[0] + ... + counts[t - 1]; *total = the sum of all. One block.
-__global__ void __launch_bounds__(1024) int_starts_kernel(const uint64_t *counts, uint64_t *starts, uint64_t *total, uint64_t tiles) {
-    __shared__ uint64_t warp_sum[32];
-    __shared__ uint64_t carry_shared;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    uint64_t carry = 0;
-    for (uint64_t t0 = 0; t0 < tiles; t0 += 1024) {
-        const uint64_t t = t0 + threadIdx.x;
-        const uint64_t mine = t < tiles ? counts[t] : 0;
-        uint64_t inclusive = mine;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const uint64_t up = __shfl_up_sync(0xFFFFFFFFu, inclusive, d);
-            if (lane >= d) inclusive += up;
-        }
-        if (lane == 31) warp_sum[warp] = inclusive;
-        __syncthreads();
-        uint64_t before = 0;
-        for (int w = 0; w < warp; ++w) before += warp_sum[w];
-        if (t < tiles) starts[t] = carry + before + inclusive - mine;
-        if (threadIdx.x == 1023) carry_shared = carry + before + inclusive;
-        __syncthreads();
-        carry = carry_shared;
-    }
-    if (threadIdx.x == 0) *total = carry;
-}
-
 __global__ void __launch_bounds__(kSampleThreads) int_place_kernel(int64_t *out, int64_t n, const uint64_t *starts, uint64_t tiles,
                                                                     uint64_t seed, uint64_t offset, uint64_t blocks, int64_t low,
                                                                     uint64_t range, uint64_t threshold) {
@@ -245,10 +237,10 @@ __global__ void __launch_bounds__(kSampleThreads) int_place_kernel(int64_t *out,
         uint32_t total;
         uint64_t at = start + block_exclusive_count((take0 ? 1u : 0u) + (take1 ? 1u : 0u), total);
         if (take0) {
-            if (at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + w0 % range);
+            if (at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w0, range));
             at += 1;
         }
-        if (take1 && at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + w1 % range);
+        if (take1 && at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w1, range));
     }
 }
 
@@ -347,7 +339,7 @@ HMC_API hmc_status hmc_random_int(hmc_context_t ctx, const hmc_tensor_desc *out,
         int_count_kernel<<<grid, kSampleThreads, 0, ctx->stream>>>(counts, tiles, seed, offset, blocks, threshold);
         s = launch_status("integer sampling (count) kernel launch");
         if (s != HMC_OK) return s;
-        int_starts_kernel<<<1, 1024, 0, ctx->stream>>>(counts, starts, total, tiles);
+        launch_tile_starts(ctx->stream, counts, starts, total, tiles);
         s = launch_status("integer sampling (positions) kernel launch");
         if (s != HMC_OK) return s;
         if (n == 0) return HMC_OK;

@@ -1,6 +1,6 @@
 // Ordered compaction in three steps, shared by the kernels that keep "the k-th element that qualifies, in row-major
-// order": a count per tile (one thread block of 256 candidates), the tiles' starting positions by a one-block
-// running sum, and a placement pass that recomputes the candidates and ranks them inside the tile.
+// order": a count per tile (one thread block of 256 candidates), the tiles' starting positions by a running sum
+// in two launches, and a placement pass that recomputes the candidates and ranks them inside the tile.
 // Workspace layout, in 64-bit words: counts[tiles], starts[tiles], total.
 #pragma once
 
@@ -30,32 +30,58 @@ __device__ __forceinline__ uint32_t block_rank(bool flag, uint32_t &total) {
     return before + __popc(ballot & ((1u << lane) - 1u));
 }
 
-// starts[t] = counts[0] + ... + counts[t - 1]; *total = the sum of all. One block of 1024 threads.
-static __global__ void __launch_bounds__(1024) tile_starts_kernel(const uint64_t *counts, uint64_t *starts, uint64_t *total,
-                                                                  uint64_t tiles) {
-    __shared__ uint64_t warp_sum[32];
-    __shared__ uint64_t carry_shared;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    uint64_t carry = 0;
-    for (uint64_t t0 = 0; t0 < tiles; t0 += 1024) {
-        const uint64_t t = t0 + threadIdx.x;
-        const uint64_t mine = t < tiles ? counts[t] : 0;
-        uint64_t inclusive = mine;
+// starts[t] = counts[0] + ... + counts[t - 1]; *total = the sum of all: two launches of ceil(n / 1024) blocks. The
+// first gives every block of 1024 counts its own running sum and leaves the block's total in the first of its counts
+// (which nothing reads afterwards); the second adds the totals of the blocks before. `counts` is overwritten.
+constexpr int kStartsBlock = 1024;
+
+__device__ __forceinline__ uint64_t warp_inclusive_sum(uint64_t v, int lane) {
 #pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const uint64_t up = __shfl_up_sync(0xFFFFFFFFu, inclusive, d);
-            if (lane >= d) inclusive += up;
-        }
-        if (lane == 31) warp_sum[warp] = inclusive;
-        __syncthreads();
-        uint64_t before = 0;
-        for (int w = 0; w < warp; ++w) before += warp_sum[w];
-        if (t < tiles) starts[t] = carry + before + inclusive - mine;
-        if (threadIdx.x == 1023) carry_shared = carry + before + inclusive;
-        __syncthreads();
-        carry = carry_shared;
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint64_t up = __shfl_up_sync(0xFFFFFFFFu, v, d);
+        if (lane >= d) v += up;
     }
-    if (threadIdx.x == 0) *total = carry;
+    return v;
+}
+
+static __global__ void __launch_bounds__(kStartsBlock) local_starts_kernel(uint64_t *counts, uint64_t *starts, uint64_t n) {
+    __shared__ uint64_t warp_sum[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t t = static_cast<uint64_t>(blockIdx.x) * kStartsBlock + threadIdx.x;
+    const uint64_t mine = t < n ? counts[t] : 0;
+    const uint64_t inclusive = warp_inclusive_sum(mine, lane);
+    if (lane == 31) warp_sum[warp] = inclusive;
+    __syncthreads();
+    if (warp == 0) warp_sum[lane] = warp_inclusive_sum(warp_sum[lane], lane);
+    __syncthreads();
+    const uint64_t before = warp > 0 ? warp_sum[warp - 1] : 0;
+    if (t < n) starts[t] = before + inclusive - mine;
+    if (threadIdx.x == 0) counts[static_cast<uint64_t>(blockIdx.x) * kStartsBlock] = warp_sum[31];
+}
+
+static __global__ void __launch_bounds__(kStartsBlock) add_base_kernel(const uint64_t *counts, uint64_t *starts, uint64_t *total,
+                                                                       uint64_t n) {
+    __shared__ uint64_t warp_sum[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint64_t part = 0;
+    for (uint64_t b = threadIdx.x; b < blockIdx.x; b += kStartsBlock) part += counts[b * kStartsBlock];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, d);
+    if (lane == 0) warp_sum[warp] = part;
+    __syncthreads();
+    uint64_t base = 0;
+#pragma unroll
+    for (int w = 0; w < 32; ++w) base += warp_sum[w];
+    const uint64_t t = static_cast<uint64_t>(blockIdx.x) * kStartsBlock + threadIdx.x;
+    if (t < n && blockIdx.x > 0) starts[t] += base;
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *total = base + counts[static_cast<uint64_t>(blockIdx.x) * kStartsBlock];
+}
+
+// n > 0 counts.
+inline void launch_tile_starts(cudaStream_t stream, uint64_t *counts, uint64_t *starts, uint64_t *total, uint64_t n) {
+    const unsigned grid = static_cast<unsigned>((n + kStartsBlock - 1) / kStartsBlock);
+    local_starts_kernel<<<grid, kStartsBlock, 0, stream>>>(counts, starts, n);
+    add_base_kernel<<<grid, kStartsBlock, 0, stream>>>(counts, starts, total, n);
 }
 
 inline uint64_t scan_tiles(uint64_t n) { return (n + kScanThreads - 1) / kScanThreads; }

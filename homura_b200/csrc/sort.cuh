@@ -1,5 +1,5 @@
 // A stable least-significant-digit radix sort of (key, value) pairs, eight bits per pass, for the kernels that must
-// add contributions to one target in the order the CPU adds them (index_add, scatter_add). Each pass is three
+// add contributions to one target in the order the CPU adds them (index_add, scatter_add). Each pass is four
 // launches: a histogram of the digit per tile of 1024 keys (digit-major, so that one running sum over the table gives
 // every (digit, tile) its first destination), that running sum, and a placement that ranks equal digits inside the
 // tile in their order of arrival. The first pass takes the values to be 0, 1, 2, ... when none are given.
@@ -112,7 +112,7 @@ template <class K> inline hmc_status sort_pairs(cudaStream_t stream, const SortS
     bool first = true;
     for (int shift = 0; shift < bits || first; shift += 8) {
         sort_count_kernel<K><<<grid, kScanThreads, 0, stream>>>(s.keys[from], n, shift, s.counts, tiles);
-        tile_starts_kernel<<<1, 1024, 0, stream>>>(s.counts, s.starts, s.total, 256 * tiles);
+        launch_tile_starts(stream, s.counts, s.starts, s.total, 256 * tiles);
         sort_place_kernel<K><<<grid, kScanThreads, 0, stream>>>(s.keys[from], first ? nullptr : s.vals[from], s.keys[1 - from],
                                                                 s.vals[1 - from], n, shift, s.starts, tiles);
         hmc_status st = launch_status("sort kernel launch");

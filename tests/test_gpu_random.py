@@ -54,7 +54,8 @@ def test_normal_samples_match_within_the_last_place(oracle, cuda, dtype):
 
 
 def test_integers_are_the_cpu_bits(oracle, cuda):
-    cases = [(0, 2**32), (-3, 4), (0, 2**63 + 1), (-2**63, 2**63 - 1), (2**63 - 2, 2**63 - 1), (-7, 1000003), (5, 6)]
+    cases = [(0, 2**32), (-3, 4), (0, 2**63 + 1), (-2**63, 2**63 - 1), (2**63 - 2, 2**63 - 1), (-7, 1000003), (5, 6),
+             (0, 2**21), (0, 2**21 - 1), (-2, 2**21 + 3), (0, 50257), (0, 3 * 2**40), (0, 2**16)]
     for low, high in cases:
         for n in (1, 2, 301, 100001):
             go, gg = Generator(11), Generator(11)
