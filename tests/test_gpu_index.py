@@ -243,3 +243,36 @@ def test_index_add_with_many_tiles_and_three_sort_passes(oracle, cuda):
     oracle.index_add(oo, 0, po, so)
     cuda.index_add(go, 0, pg, sg)
     assert_bitwise(cuda.download(go), oracle.download(oo), F32, "index_add of 300000 slices into 100000")
+
+
+def test_add_family_with_targets_beyond_32_bits(cuda):
+    """An output of more than 2^32 elements: the sort runs on 64-bit keys (five passes for index_add's 33 bits)."""
+    size = (1 << 32) + 4096
+    out = cuda.empty((size,), U8)
+    cuda.fill(out, 7)
+    w = words(660, 3000)
+    p = (w % np.uint64(size)).astype(np.int64)
+    p[:500] = p[500:1000]            # repeated targets
+    p[1000:1010] = size - 1           # the last element, ten times
+    src = (words(661, 3000) % np.uint64(200)).astype(np.uint8)
+    want = {}
+    for j, v in zip(p.tolist(), src.tolist()):
+        want[j] = want.get(j, 7) + v
+    targets = np.array(sorted(want), dtype=np.int64)
+    expect = np.array([want[j] & 255 for j in targets.tolist()], dtype=np.uint8)
+    pg, sg, tg = cuda.upload(p, I64), cuda.upload(src, U8), cuda.upload(targets, I64)
+    got = cuda.empty((len(targets),), U8)
+
+    cuda.index_add(out, 0, pg, sg)
+    cuda.gather(got, out, 0, tg)
+    assert (cuda.download(got) == expect).all(), "index_add into 2^32 + 4096 elements"
+    neighbours = cuda.upload(np.array([0, 1, size - 2], dtype=np.int64)[~np.isin([0, 1, size - 2], targets)], I64)
+    seen = cuda.empty((neighbours.numel,), U8)
+    if neighbours.numel:
+        cuda.gather(seen, out, 0, neighbours)
+        assert (cuda.download(seen) == 7).all(), "elements no position names keep their value"
+
+    cuda.fill(out, 7)
+    cuda.scatter_add(out, 0, pg, sg)
+    cuda.gather(got, out, 0, tg)
+    assert (cuda.download(got) == expect).all(), "scatter_add into 2^32 + 4096 elements"
