@@ -216,6 +216,19 @@ HMC_API hmc_status hmc_index_check(hmc_context_t ctx, const hmc_tensor_desc *ind
     });
 }
 
+HMC_API hmc_status hmc_test_index_value(hmc_context_t ctx, const hmc_tensor_desc *index, uint64_t *slot) {
+    return guarded([&]() -> hmc_status {
+        HMC_ENTER(ctx);
+        hmc_status s = check_index_desc(index);
+        if (s != HMC_OK) return s;
+        if (slot == nullptr || (reinterpret_cast<uintptr_t>(slot) & 7) != 0) return fail(HMC_INVALID, "the status slot is missing or not 8-byte aligned");
+        if (index->data == nullptr) return fail(HMC_INVALID, "null data pointer");
+        CheckArgs a{*index, 0, 0, 0, 0, 0, reinterpret_cast<unsigned long long *>(slot)};
+        index_check_value_kernel<<<1, 1, 0, ctx->stream>>>(a);
+        return launch_status("index check (value) kernel launch");
+    });
+}
+
 HMC_API hmc_status hmc_index_select(hmc_context_t ctx, const hmc_tensor_desc *out, const hmc_tensor_desc *src,
                                     const hmc_tensor_desc *index, int32_t dim, int32_t wrap_negative) {
     return guarded([&]() -> hmc_status {

@@ -454,6 +454,10 @@ hmc_status hmc_test_reduce_plan(const hmc_tensor_desc *kept, const hmc_tensor_de
                                 int64_t *kind, int64_t *splits, int64_t *chunk);
 hmc_status hmc_test_softmax_plan(const hmc_tensor_desc *src_rows, int64_t n, int64_t src_stride,
                                  int32_t *kind, int32_t *group, int32_t *cache);
+/* The second step of hmc_index_check alone: if slot[0] (a logical position of `index`, set by the caller) is not
+ * UINT64_MAX, writes the value there to slot[1]: to test positions far beyond what a check could reach in a test
+ * (2^60 and more, in views with zero strides). `slot` is device memory. csrc/homura_rocm.h:631-634, 657-658 */
+hmc_status hmc_test_index_value(hmc_context_t ctx, const hmc_tensor_desc *index, uint64_t *slot);
 int32_t hmc_test_live_streams(void);
 hmc_status hmc_test_current_device(int32_t *device);
 hmc_status hmc_test_set_current_device(int32_t device);

@@ -276,3 +276,21 @@ def test_add_family_with_targets_beyond_32_bits(cuda):
     cuda.scatter_add(out, 0, pg, sg)
     cuda.gather(got, out, 0, tg)
     assert (cuda.download(got) == expect).all(), "scatter_add into 2^32 + 4096 elements"
+
+
+def test_index_value_at_a_position_beyond_any_testable_check(cuda):
+    """The second step of index_check alone: the value at logical position 2^60 + 5 of a view with a zero stride."""
+    import ctypes
+    from homura_b200.ffi import hmc_tensor_desc
+    base = cuda.upload(np.arange(100, 164, dtype=np.int64), I64)
+    d = hmc_tensor_desc()
+    d.data, d.offset, d.dtype, d.ndim = base.storage.ptr, 0, I64, 2
+    d.sizes[0], d.strides[0] = 1 << 56, 0
+    d.sizes[1], d.strides[1] = 64, 1
+    slot = cuda.upload(np.array([(1 << 60) + 5, 0], dtype=np.uint64).view(np.int64), I64)
+    cuda._check(cuda.lib.hmc_test_index_value(cuda.ctx, d, ctypes.cast(slot.storage.ptr, ctypes.POINTER(ctypes.c_uint64))))
+    assert cuda.download(slot).tolist() == [(1 << 60) + 5, 105]
+    # UINT64_MAX: nothing was found, nothing is written
+    slot = cuda.upload(np.array([-1, 42], dtype=np.int64), I64)
+    cuda._check(cuda.lib.hmc_test_index_value(cuda.ctx, d, ctypes.cast(slot.storage.ptr, ctypes.POINTER(ctypes.c_uint64))))
+    assert cuda.download(slot).tolist() == [-1, 42]
