@@ -16,10 +16,12 @@ namespace {
 
 constexpr int kWriteThreads = 256;
 
-__global__ void __launch_bounds__(kWriteThreads) winners_kernel(long long *winner, const int64_t *positions, int64_t m) {
+// (The caller has checked the positions; one outside the dimension names no slice rather than a word beyond the table.)
+__global__ void __launch_bounds__(kWriteThreads) winners_kernel(long long *winner, const int64_t *positions, int64_t m, int64_t size) {
     for (int64_t i = blockIdx.x * static_cast<int64_t>(kWriteThreads) + threadIdx.x; i < m;
          i += static_cast<int64_t>(gridDim.x) * kWriteThreads) {
-        atomicMax(winner + positions[i], static_cast<long long>(i));
+        const int64_t p = positions[i];
+        if (p >= 0 && p < size) atomicMax(winner + p, static_cast<long long>(i));
     }
 }
 
@@ -177,7 +179,7 @@ HMC_API hmc_status hmc_index_overwrite(hmc_context_t ctx, const hmc_tensor_desc 
         long long *winner = static_cast<long long *>(workspace);
         HMC_CUDA(cudaMemsetAsync(winner, 0xFF, static_cast<size_t>(size) * 8, ctx->stream), "cudaMemsetAsync");  // every slot -1
         winners_kernel<<<write_grid(m, kWriteThreads), kWriteThreads, 0, ctx->stream>>>(
-            winner, static_cast<const int64_t *>(positions->data) + positions->offset, m);
+            winner, static_cast<const int64_t *>(positions->data) + positions->offset, m, size);
         s = launch_status("index_overwrite (winners) kernel launch");
         if (s != HMC_OK) return s;
         OverwriteArgs a{*out, *src, winner, dim, n};
