@@ -92,6 +92,63 @@ __global__ void __launch_bounds__(kTriThreads) triangle_kernel(const __grid_cons
     }
 }
 
+// Both tensors contiguous, rows a whole number of 32-byte groups, both 32-byte aligned: a thread takes groups of
+// 32 bytes by their flat number (two in flight), finds (row, first column) with 32-bit divisions, and moves the group
+// with one 256-bit load and store; groups outside the triangle are stored as zeros without the load.
+struct FlatTriangleArgs {
+    char *out;
+    const char *src;
+    uint32_t rows, groups_per_row;   // groups of 32 bytes
+    int32_t upper;
+    int64_t diagonal;
+    int64_t groups;                  // below 2^32
+};
+
+template <class W>
+__global__ void __launch_bounds__(kTriThreads) triangle_flat_kernel(const __grid_constant__ FlatTriangleArgs a) {
+    constexpr int PER = 32 / sizeof(W);
+    constexpr int UNR = 2;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kTriThreads;
+    for (int64_t g0 = blockIdx.x * static_cast<int64_t>(kTriThreads) + threadIdx.x; g0 < a.groups; g0 += UNR * stride) {
+        Bytes32 x[UNR];
+        int64_t c0[UNR], edge[UNR];
+        bool live[UNR], none[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int64_t g = g0 + u * stride;
+            live[u] = g < a.groups;
+            if (!live[u]) continue;
+            const uint32_t line = static_cast<uint32_t>(g) / a.groups_per_row;
+            const uint32_t r = line % a.rows;
+            c0[u] = static_cast<int64_t>(static_cast<uint32_t>(g) - line * a.groups_per_row) * PER;
+            edge[u] = static_cast<int64_t>(r) + a.diagonal;  // upper keeps c >= edge, lower keeps c <= edge
+            none[u] = a.upper ? c0[u] + PER - 1 < edge[u] : c0[u] > edge[u];
+            if (none[u]) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[u].w[e] = 0;
+            } else {
+                x[u] = load_32_bytes(a.src + g * 32);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            if (!live[u]) continue;
+            const bool all = a.upper ? c0[u] >= edge[u] : c0[u] + PER - 1 <= edge[u];
+            if (!none[u] && !all) {
+                W v[PER];
+                memcpy(v, &x[u], 32);
+#pragma unroll
+                for (int e = 0; e < PER; ++e) {
+                    const bool keep = a.upper ? c0[u] + e >= edge[u] : c0[u] + e <= edge[u];
+                    if (!keep) v[e] = W{0};
+                }
+                memcpy(&x[u], v, 32);
+            }
+            store_32_bytes(a.out + (g0 + u * stride) * 32, x[u]);
+        }
+    }
+}
+
 template <class F> hmc_status by_size(int dtype, F &&f) {
     switch (element_size(dtype)) {
         case 1: return f(uint8_t{});
@@ -144,6 +201,27 @@ HMC_API hmc_status hmc_triangle(hmc_context_t ctx, const hmc_tensor_desc *out, c
         const int64_t reach = a.rows + a.cols + 1;
         if (a.diagonal > reach) a.diagonal = reach;
         if (a.diagonal < -reach) a.diagonal = -reach;
+        // the flat kernel where both tensors are contiguous and cut into whole, aligned groups of 32 bytes
+        {
+            bool flat = (a.cols * es) % 32 == 0 && ((reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.src)) & 31) == 0 &&
+                        a.rows < (int64_t{1} << 31);
+            int64_t expect = 1;
+            for (int k = nd - 1; k >= 0 && flat; --k) {
+                flat = (src->sizes[k] == 1 || (src->strides[k] == expect && out->strides[k] == expect));
+                expect *= src->sizes[k];
+            }
+            const int64_t groups = n / (32 / es);
+            if (flat && groups < (int64_t{1} << 32)) {
+                FlatTriangleArgs f{a.out, const_cast<const char *>(a.src), static_cast<uint32_t>(a.rows),
+                                   static_cast<uint32_t>(a.cols * es / 32), a.upper, a.diagonal, groups};
+                const int64_t blocks = ceil_div(groups, static_cast<int64_t>(2 * kTriThreads));
+                const unsigned g = static_cast<unsigned>(blocks < (int64_t{1} << 20) ? blocks : (int64_t{1} << 20));
+                return by_size(src->dtype, [&](auto w) -> hmc_status {
+                    triangle_flat_kernel<decltype(w)><<<g, kTriThreads, 0, ctx->stream>>>(f);
+                    return launch_status("triangle kernel launch");
+                });
+            }
+        }
         // up to four vectors per thread, so that a thread's share of finding its line is spread over 64 bytes
         const int64_t per_line = ceil_div(a.cols, 4 * kTriThreads * (16 / es));
         dim3 grid(static_cast<unsigned>(per_line < 1 ? 1 : (per_line < 65535 ? per_line : 65535)),

@@ -15,7 +15,7 @@ def both(oracle, cuda, raw, dtype, shape):
 
 @pytest.mark.parametrize("dtype", [BOOL, BF16, F32, I64], ids=["bool", "bf16", "f32", "i64"])
 def test_triangle_on_every_layout(oracle, cuda, dtype):
-    shapes = [(5, 7), (64, 64), (1, 9), (9, 1), (130, 70), (3, 2, 33, 260), (2, 257, 300)]
+    shapes = [(5, 7), (64, 64), (1, 9), (9, 1), (130, 70), (3, 2, 33, 260), (2, 257, 300), (2, 3, 40, 96), (1, 3, 1056)]
     for shape in shapes:
         n = int(np.prod(shape))
         (os_, gs) = both(oracle, cuda, values(dtype, n, 400), dtype, shape)
