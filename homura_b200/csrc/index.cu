@@ -79,12 +79,12 @@ __global__ void __launch_bounds__(kIndexThreads) index_select_kernel(const __gri
         for (int u = 0; u < UNR; ++u) {
             if (item + u * stride < a.items) {
                 select_offsets<VEC>(a, item + u * stride, oo[u], so[u]);
-                x[u] = *reinterpret_cast<const Pack<W, VEC> *>(src + so[u]);
+                vector_load<W, VEC>(x[u], src + so[u], true);  // (vectors of 32 bytes are chosen for 32-byte aligned slices only)
             }
         }
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
-            if (item + u * stride < a.items) *reinterpret_cast<Pack<W, VEC> *>(out + oo[u]) = x[u];
+            if (item + u * stride < a.items) vector_store<W, VEC>(out + oo[u], x[u], true);
         }
     }
 }
@@ -262,19 +262,28 @@ HMC_API hmc_status hmc_index_select(hmc_context_t ctx, const hmc_tensor_desc *ou
         a.at = dim;
         a.wrap_negative = wrap_negative != 0;
         a.size = src->sizes[dim];
-        // 16-byte vectors along the innermost dimension when it is not the indexed one, both tensors walk it with unit
-        // stride, its length is whole vectors, and every other stride and both first elements keep the alignment
-        bool vector = dim != last && out->strides[last] == 1 && src->strides[last] == 1 && out->sizes[last] % vec == 0;
-        vector = vector && (reinterpret_cast<uintptr_t>(out->data) + static_cast<uintptr_t>(out->offset) * es) % 16 == 0 &&
-                 (reinterpret_cast<uintptr_t>(src->data) + static_cast<uintptr_t>(src->offset) * es) % 16 == 0;
-        for (int k = 0; k < last && vector; ++k) vector = (out->strides[k] * es) % 16 == 0 && (src->strides[k] * es) % 16 == 0;
+        // Vectors along the innermost dimension when it is not the indexed one, both tensors walk it with unit stride,
+        // its length is whole vectors, and every other stride and both first elements keep the alignment: of 32 bytes
+        // (one 256-bit access each) where all of that holds for 32, else of 16
+        auto aligned_to = [&](int bytes) {
+            const int per = bytes / es;
+            bool ok = dim != last && out->strides[last] == 1 && src->strides[last] == 1 && out->sizes[last] % per == 0;
+            ok = ok && (reinterpret_cast<uintptr_t>(out->data) + static_cast<uintptr_t>(out->offset) * es) % bytes == 0 &&
+                 (reinterpret_cast<uintptr_t>(src->data) + static_cast<uintptr_t>(src->offset) * es) % bytes == 0;
+            for (int k = 0; k < last && ok; ++k) ok = (out->strides[k] * es) % bytes == 0 && (src->strides[k] * es) % bytes == 0;
+            return ok;
+        };
+        const bool wide = aligned_to(32);
+        const bool vector = wide || aligned_to(16);
+        const int per = wide ? 2 * vec : vec;
         a.vector = vector;
-        a.inner = vector ? out->sizes[last] / vec : out->sizes[last];
-        a.items = n / (vector ? vec : 1);
+        a.inner = vector ? out->sizes[last] / per : out->sizes[last];
+        a.items = n / (vector ? per : 1);
         const unsigned grid = index_grid(ceil_div(a.items, 4));  // four items per thread
         return by_size(src->dtype, [&](auto w) -> hmc_status {
             using W = decltype(w);
-            if (vector) index_select_kernel<W, 16 / sizeof(W)><<<grid, kIndexThreads, 0, ctx->stream>>>(a);
+            if (wide) index_select_kernel<W, 32 / sizeof(W)><<<grid, kIndexThreads, 0, ctx->stream>>>(a);
+            else if (vector) index_select_kernel<W, 16 / sizeof(W)><<<grid, kIndexThreads, 0, ctx->stream>>>(a);
             else index_select_kernel<W, 1><<<grid, kIndexThreads, 0, ctx->stream>>>(a);
             return launch_status("index_select kernel launch");
         });
