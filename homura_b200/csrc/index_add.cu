@@ -89,18 +89,19 @@ __global__ void __launch_bounds__(kAddThreads) index_add_kernel(const __grid_con
         }
         oo += static_cast<int64_t>(key) * a.out.strides[a.at];
         const int64_t step = a.src.strides[a.at];
-        Pack<T, VEC> x = *reinterpret_cast<const Pack<T, VEC> *>(out + oo);
+        Pack<T, VEC> x;
+        vector_load<T, VEC>(x, out + oo, true);  // (vectors of 32 bytes are chosen for 32-byte aligned slices only)
         typename S::A acc[VEC];
 #pragma unroll
         for (int e = 0; e < VEC; ++e) acc[e] = S::load(x.v[e]);
         for (int64_t kk = k; kk < a.m && a.keys[kk] == key; ++kk) {
-            x = *reinterpret_cast<const Pack<T, VEC> *>(src + so + static_cast<int64_t>(a.vals[kk]) * step);
+            vector_load<T, VEC>(x, src + so + static_cast<int64_t>(a.vals[kk]) * step, true);
 #pragma unroll
             for (int e = 0; e < VEC; ++e) acc[e] = S::add(acc[e], x.v[e]);
         }
 #pragma unroll
         for (int e = 0; e < VEC; ++e) x.v[e] = S::store(acc[e]);
-        *reinterpret_cast<Pack<T, VEC> *>(out + oo) = x;
+        vector_store<T, VEC>(out + oo, x, true);
     }
 }
 
@@ -263,22 +264,27 @@ HMC_API hmc_status hmc_index_add(hmc_context_t ctx, const hmc_tensor_desc *out, 
             IndexAddArgs<K> a{*out, *src, space.keys[sorted], space.vals[sorted], dim, m, size, rest, work};
             return dispatch_all(out->dtype, [&](auto t) -> hmc_status {
                 using T = decltype(t);
-                constexpr int VEC = 16 / static_cast<int>(sizeof(T));
-                // 16-byte vectors along the innermost dimension where both tensors allow them
+                // vectors of 32 bytes (one 256-bit access), else of 16, along the innermost dimension where both tensors allow them
                 const int last = out->ndim - 1;
-                bool vector = VEC > 1 && dim != last && out->strides[last] == 1 && src->strides[last] == 1 && out->sizes[last] % VEC == 0 &&
-                              ((reinterpret_cast<uintptr_t>(out->data) + out->offset * sizeof(T)) & 15) == 0 &&
-                              ((reinterpret_cast<uintptr_t>(src->data) + src->offset * sizeof(T)) & 15) == 0;
-                for (int k = 0; k < last && vector; ++k) vector = out->strides[k] % VEC == 0 && src->strides[k] % VEC == 0;
-                if (vector) {
+                auto aligned_to = [&](int bytes) {
+                    const int per = bytes / static_cast<int>(sizeof(T));
+                    bool ok = per > 1 && dim != last && out->strides[last] == 1 && src->strides[last] == 1 && out->sizes[last] % per == 0 &&
+                              ((reinterpret_cast<uintptr_t>(out->data) + out->offset * sizeof(T)) % bytes) == 0 &&
+                              ((reinterpret_cast<uintptr_t>(src->data) + src->offset * sizeof(T)) % bytes) == 0;
+                    for (int k = 0; k < last && ok; ++k) ok = out->strides[k] % per == 0 && src->strides[k] % per == 0;
+                    return ok;
+                };
+                auto run_vectors = [&](auto vec_tag) {
+                    constexpr int VEC = decltype(vec_tag)::value;
                     IndexAddArgs<K> v = a;
                     v.out.sizes[last] /= VEC;
                     v.rest /= VEC;
                     v.work /= VEC;
                     index_add_kernel<T, K, VEC><<<add_grid(v.work), kAddThreads, 0, ctx->stream>>>(v);
-                } else {
-                    index_add_kernel<T, K, 1><<<add_grid(work), kAddThreads, 0, ctx->stream>>>(a);
-                }
+                };
+                if (aligned_to(32)) run_vectors(std::integral_constant<int, 32 / static_cast<int>(sizeof(T))>{});
+                else if (aligned_to(16)) run_vectors(std::integral_constant<int, (16 / static_cast<int>(sizeof(T)) > 1 ? 16 / static_cast<int>(sizeof(T)) : 2)>{});
+                else index_add_kernel<T, K, 1><<<add_grid(work), kAddThreads, 0, ctx->stream>>>(a);
                 return launch_status("index_add kernel launch");
             });
         };
