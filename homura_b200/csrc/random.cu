@@ -139,26 +139,44 @@ __device__ __forceinline__ void block_words(uint64_t n, uint64_t seed, uint64_t 
 }
 
 // w % range without the general 64-bit division where the range allows: a mask for a power of two; for a range of
-// at most 2^21, the high half is reduced with a 32-bit division, which leaves x = rest * 2^32 + low half below 2^53,
-// exact as an f64, so that x * (1 / range) truncated is the quotient or one beside it and one correction gives the
-// remainder. The branches are the same for every thread of a launch.
-__device__ __forceinline__ uint64_t word_mod(uint64_t w, uint64_t range) {
-    if ((range & (range - 1)) == 0) return w & (range - 1);
-    if (range <= (1u << 21)) {
-        const uint32_t r = static_cast<uint32_t>(range);
-        const uint64_t x = (static_cast<uint64_t>(static_cast<uint32_t>(w >> 32) % r) << 32) | static_cast<uint32_t>(w);
-        const int64_t q = __double2ll_rz(__ll2double_rn(static_cast<int64_t>(x)) * (1.0 / static_cast<double>(r)));
-        int64_t rem = static_cast<int64_t>(x) - q * static_cast<int64_t>(r);
+// at most 2^21, two steps through inv = 1 / range in f64: the high half h (below 2^32, exact as an f64) gives
+// h * inv truncated, the quotient or one beside it, so one correction leaves h % range; then x = that * 2^32 + the
+// low half is below 2^53, exact again, and the same step gives the remainder. The branches are the same for every
+// thread of a launch.
+struct Modulus {
+    uint64_t range;
+    double inv;     // 1 / range, for kind 1
+    int32_t kind;   // 0: power of two, 1: at most 2^21, 2: any
+};
+
+inline Modulus modulus_of(uint64_t range) {
+    Modulus m;
+    m.range = range;
+    m.inv = 1.0 / static_cast<double>(range);
+    m.kind = (range & (range - 1)) == 0 ? 0 : (range <= (1u << 21) ? 1 : 2);
+    return m;
+}
+
+__device__ __forceinline__ uint64_t word_mod(uint64_t w, const Modulus &m) {
+    if (m.kind == 0) return w & (m.range - 1);
+    if (m.kind == 1) {
+        const int64_t r = static_cast<int64_t>(m.range);
+        const int64_t hi = static_cast<int64_t>(w >> 32);
+        int64_t h = hi - __double2ll_rz(__ll2double_rn(hi) * m.inv) * r;
+        if (h < 0) h += r;
+        if (h >= r) h -= r;
+        const int64_t x = (h << 32) | static_cast<int64_t>(static_cast<uint32_t>(w));
+        int64_t rem = x - __double2ll_rz(__ll2double_rn(x) * m.inv) * r;
         if (rem < 0) rem += r;
-        if (rem >= static_cast<int64_t>(r)) rem -= r;
+        if (rem >= r) rem -= r;
         return static_cast<uint64_t>(rem);
     }
-    return w % range;
+    return w % m.range;
 }
 
 // threshold == 0: word k of the batch is value k.
 __global__ void __launch_bounds__(kSampleThreads) int_all_kernel(int64_t *out, int64_t n, uint64_t seed, uint64_t offset,
-                                                                  uint64_t blocks, int64_t low, uint64_t range) {
+                                                                  uint64_t blocks, int64_t low, const Modulus range) {
     const bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     for (uint64_t b = static_cast<uint64_t>(blockIdx.x) * kSampleThreads + threadIdx.x; b < blocks;
          b += static_cast<uint64_t>(gridDim.x) * kSampleThreads) {
@@ -204,28 +222,55 @@ __device__ __forceinline__ uint32_t block_exclusive_count(uint32_t mine, uint32_
 // A tile is HMC_RANDOM_INT_TILE blocks: one block of threads, one Philox block per thread.
 static_assert(HMC_RANDOM_INT_TILE == kSampleThreads, "a tile is one thread block");
 
+// Counts the accepted words of every tile and, while it has the words, writes them where they belong if no word
+// of an earlier tile was rejected (position of the tile's first word: two per block before it). For the ranges of
+// practice a rejection has a probability near 2^-48, so that is nearly always the final place.
 __global__ void __launch_bounds__(kSampleThreads) int_count_kernel(uint64_t *counts, uint64_t tiles, uint64_t seed, uint64_t offset,
-                                                                    uint64_t blocks, uint64_t threshold) {
+                                                                    uint64_t blocks, uint64_t threshold, int64_t *out, int64_t n,
+                                                                    int64_t low, const Modulus range) {
     for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const uint64_t b = tile * HMC_RANDOM_INT_TILE + threadIdx.x;
-        uint32_t mine = 0;
+        uint64_t w0 = 0, w1 = 0;
+        bool take0 = false, take1 = false;
         if (b < blocks) {
-            uint64_t w0, w1;
             block_words(offset + b, seed, w0, w1);
-            mine = (w0 >= threshold ? 1u : 0u) + (w1 >= threshold ? 1u : 0u);
+            take0 = w0 >= threshold;
+            take1 = w1 >= threshold;
+        }
+        if (__syncthreads_and(take0 && take1)) {  // a whole tile, nothing rejected: no ranks to find
+            if (threadIdx.x == 0) counts[tile] = 2 * HMC_RANDOM_INT_TILE;
+            const uint64_t first = 2 * b;
+            Pack<int64_t, 2> v;
+            v.v[0] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w0, range));
+            v.v[1] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w1, range));
+            if (first + 2 <= static_cast<uint64_t>(n) && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+                *reinterpret_cast<Pack<int64_t, 2> *>(out + first) = v;
+            } else {
+                if (first < static_cast<uint64_t>(n)) out[first] = v.v[0];
+                if (first + 1 < static_cast<uint64_t>(n)) out[first + 1] = v.v[1];
+            }
+            continue;
         }
         uint32_t total;
-        block_exclusive_count(mine, total);
+        uint64_t at = tile * (2 * HMC_RANDOM_INT_TILE) + block_exclusive_count((take0 ? 1u : 0u) + (take1 ? 1u : 0u), total);
         if (threadIdx.x == 0) counts[tile] = total;
+        if (take0) {
+            if (at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w0, range));
+            at += 1;
+        }
+        if (take1 && at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w1, range));
     }
 }
 
+// The tiles after the first rejected word: their words are recomputed and written at their final places. (Positions at
+// and beyond the number of accepted words may hold words of the first attempt; a later batch overwrites them.)
 __global__ void __launch_bounds__(kSampleThreads) int_place_kernel(int64_t *out, int64_t n, const uint64_t *starts, uint64_t tiles,
                                                                     uint64_t seed, uint64_t offset, uint64_t blocks, int64_t low,
-                                                                    uint64_t range, uint64_t threshold) {
+                                                                    const Modulus range, uint64_t threshold) {
     for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const uint64_t start = starts[tile];
-        if (start >= static_cast<uint64_t>(n)) continue;  // (the same for the whole block) everything here is dropped
+        // (both the same for the whole block) everything here is dropped, or already in place
+        if (start >= static_cast<uint64_t>(n) || start == tile * (2 * HMC_RANDOM_INT_TILE)) continue;
         const uint64_t b = tile * HMC_RANDOM_INT_TILE + threadIdx.x;
         uint64_t w0 = 0, w1 = 0;
         bool take0 = false, take1 = false;
@@ -322,7 +367,7 @@ HMC_API hmc_status hmc_random_int(hmc_context_t ctx, const hmc_tensor_desc *out,
         if (threshold == 0) {
             if (n == 0 || blocks == 0) return HMC_OK;
             int_all_kernel<<<sample_grid(static_cast<int64_t>(blocks)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, blocks, low,
-                                                                                                       range);
+                                                                                                       modulus_of(range));
             return launch_status("integer sampling kernel launch");
         }
         if (workspace == nullptr) return fail(HMC_INVALID, "integer sampling with rejection needs its workspace");
@@ -336,14 +381,14 @@ HMC_API hmc_status hmc_random_int(hmc_context_t ctx, const hmc_tensor_desc *out,
             return HMC_OK;
         }
         const unsigned grid = static_cast<unsigned>(tiles < (uint64_t{1} << 22) ? tiles : (uint64_t{1} << 22));
-        int_count_kernel<<<grid, kSampleThreads, 0, ctx->stream>>>(counts, tiles, seed, offset, blocks, threshold);
+        int_count_kernel<<<grid, kSampleThreads, 0, ctx->stream>>>(counts, tiles, seed, offset, blocks, threshold, p, n, low, modulus_of(range));
         s = launch_status("integer sampling (count) kernel launch");
         if (s != HMC_OK) return s;
         launch_tile_starts(ctx->stream, counts, starts, total, tiles);
         s = launch_status("integer sampling (positions) kernel launch");
         if (s != HMC_OK) return s;
         if (n == 0) return HMC_OK;
-        int_place_kernel<<<grid, kSampleThreads, 0, ctx->stream>>>(p, n, starts, tiles, seed, offset, blocks, low, range, threshold);
+        int_place_kernel<<<grid, kSampleThreads, 0, ctx->stream>>>(p, n, starts, tiles, seed, offset, blocks, low, modulus_of(range), threshold);
         return launch_status("integer sampling (placement) kernel launch");
     });
 }

@@ -260,7 +260,8 @@ hmc_status hmc_random_normal(hmc_context_t ctx, const hmc_tensor_desc *out, uint
  * order, become low + word % range (wrapping) and fill the I64 `out` until it is full; the rest are dropped.
  * With threshold 0 every word is taken and `workspace` may be NULL. Otherwise `workspace` holds
  * 2 * tiles + 1 64-bit words of device memory, tiles = ceil(blocks / HMC_RANDOM_INT_TILE), and the number of
- * words >= threshold of the batch (which may exceed out's elements) is left in its last word.
+ * words >= threshold of the batch (which may exceed out's elements) is left in its last word. Elements of out at
+ * and beyond that number are unspecified after the call (a later batch fills them).
  * csrc/homura_rocm.h:283-295 */
 hmc_status hmc_random_int(hmc_context_t ctx, const hmc_tensor_desc *out, uint64_t seed, uint64_t offset,
                           uint64_t blocks, int64_t low, uint64_t range, uint64_t threshold, void *workspace);
