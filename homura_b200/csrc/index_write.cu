@@ -64,6 +64,7 @@ struct MaskArgs {
     uint64_t tiles;
     uint64_t *counts, *starts, *total;
     int64_t *out;      // coordinates (placement only)
+    int64_t columns;   // of out: the number of true elements the caller read back
 };
 
 __device__ __forceinline__ bool mask_at(const MaskArgs &a, int64_t item, int64_t (&coord)[HMC_MAX_DIMS]) {
@@ -87,9 +88,11 @@ __global__ void __launch_bounds__(kScanThreads) mask_kernel(const __grid_constan
         const uint32_t rank = block_rank(set, total);
         if constexpr (PLACE) {
             if (set) {
-                const int64_t count = static_cast<int64_t>(*a.total);  // left there by the counting call
+                // (a caller that passes fewer columns than the count it was given loses the rest, not other memory)
                 const int64_t k = static_cast<int64_t>(a.starts[tile]) + rank;
-                for (int d = 0; d < a.mask.ndim; ++d) a.out[d * count + k] = coord[d];
+                if (k < a.columns) {
+                    for (int d = 0; d < a.mask.ndim; ++d) a.out[d * a.columns + k] = coord[d];
+                }
             }
         } else {
             if (threadIdx.x == 0) a.counts[tile] = total;
@@ -230,6 +233,7 @@ HMC_API hmc_status hmc_mask_coordinates(hmc_context_t ctx, const hmc_tensor_desc
         s = check_desc(out, "the coordinates");
         if (s != HMC_OK) return s;
         if (out->dtype != HMC_I64) return fail(HMC_INVALID, "the coordinates are an I64 tensor");
+        if (out->ndim != 2 || out->sizes[0] != mask->ndim) return fail(HMC_INVALID, "the coordinates are [the mask's rank, the number of true elements]");
         int64_t expect = 1;
         for (int k = out->ndim - 1; k >= 0; --k) {
             if (out->sizes[k] != 1 && out->strides[k] != expect) return fail(HMC_INVALID, "the coordinates are contiguous");
@@ -238,6 +242,7 @@ HMC_API hmc_status hmc_mask_coordinates(hmc_context_t ctx, const hmc_tensor_desc
         if (a.tiles == 0 || expect == 0) return HMC_OK;
         if (out->data == nullptr) return fail(HMC_INVALID, "null data pointer");
         a.out = static_cast<int64_t *>(out->data) + out->offset;
+        a.columns = out->sizes[1];
         const unsigned grid = static_cast<unsigned>(a.tiles < (uint64_t{1} << 20) ? a.tiles : (uint64_t{1} << 20));
         mask_kernel<true><<<grid, kScanThreads, 0, ctx->stream>>>(a);
         return launch_status("mask coordinates kernel launch");

@@ -669,7 +669,10 @@ class CudaBackend:
         count = int(total[0])
         out = self.empty((rank, count), I64)
         if count:
-            self._check(self.lib.hmc_mask_coordinates(self.ctx, d, ws.ptr, nbytes.value, _flat_desc(out)))
+            o = hmc_tensor_desc()
+            o.data, o.offset, o.dtype, o.ndim = out.storage.address, out.offset, I64, 2
+            o.sizes[0], o.strides[0], o.sizes[1], o.strides[1] = rank, count, count, 1
+            self._check(self.lib.hmc_mask_coordinates(self.ctx, d, ws.ptr, nbytes.value, o))
         return [out.select(0, k) for k in range(rank)]
 
     def index_add(self, out: TensorData, dim: int, index: TensorData, src: TensorData) -> None:

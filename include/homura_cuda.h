@@ -351,7 +351,8 @@ hmc_status hmc_index_positions(hmc_context_t ctx, const hmc_tensor_desc *out, co
  * hmc_mask_count queues counting the true elements of the BOOL mask, whose number it leaves at 64-bit word
  * total_word of the workspace (hmc_mask_workspace bytes for the mask's number of elements); hmc_mask_coordinates
  * then writes coordinate d of the k-th true element, in row-major order, to out[d][k] (I64, contiguous, the mask's
- * rank x the number). The mask's description keeps the dimensions whose coordinates are wanted (it is not merged).
+ * rank x the number: a two-dimensional description, whose second size bounds what is written). The mask's
+ * description keeps the dimensions whose coordinates are wanted (it is not merged).
  * csrc/homura_rocm.h:420-429 */
 hmc_status hmc_mask_workspace(int64_t n, int64_t *bytes, int64_t *total_word);
 hmc_status hmc_mask_count(hmc_context_t ctx, const hmc_tensor_desc *mask, void *workspace, int64_t workspace_bytes);
