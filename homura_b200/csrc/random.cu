@@ -264,28 +264,42 @@ __global__ void __launch_bounds__(kSampleThreads) int_count_kernel(uint64_t *cou
 
 // The tiles after the first rejected word: their words are recomputed and written at their final places. (Positions at
 // and beyond the number of accepted words may hold words of the first attempt; a later batch overwrites them.)
+constexpr int kPlaceSpan = 32;
+
 __global__ void __launch_bounds__(kSampleThreads) int_place_kernel(int64_t *out, int64_t n, const uint64_t *starts, uint64_t tiles,
                                                                     uint64_t seed, uint64_t offset, uint64_t blocks, int64_t low,
                                                                     const Modulus range, uint64_t threshold) {
-    for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-        const uint64_t start = starts[tile];
-        // (both the same for the whole block) everything here is dropped, or already in place
-        if (start >= static_cast<uint64_t>(n) || start == tile * (2 * HMC_RANDOM_INT_TILE)) continue;
-        const uint64_t b = tile * HMC_RANDOM_INT_TILE + threadIdx.x;
-        uint64_t w0 = 0, w1 = 0;
-        bool take0 = false, take1 = false;
-        if (b < blocks) {
-            block_words(offset + b, seed, w0, w1);
-            take0 = w0 >= threshold;
-            take1 = w1 >= threshold;
+    // A block takes spans of kPlaceSpan tiles; its first threads look at one tile's start each, and a span without
+    // work (the usual case: every tile already in place) costs one barrier instead of a block per tile.
+    for (uint64_t span = blockIdx.x; span * kPlaceSpan < tiles; span += gridDim.x) {
+        const uint64_t t0 = span * kPlaceSpan;
+        bool work = false;
+        if (threadIdx.x < kPlaceSpan && t0 + threadIdx.x < tiles) {
+            const uint64_t st = starts[t0 + threadIdx.x];
+            work = st < static_cast<uint64_t>(n) && st != (t0 + threadIdx.x) * (2 * HMC_RANDOM_INT_TILE);
         }
-        uint32_t total;
-        uint64_t at = start + block_exclusive_count((take0 ? 1u : 0u) + (take1 ? 1u : 0u), total);
-        if (take0) {
-            if (at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w0, range));
-            at += 1;
+        if (!__syncthreads_or(work)) continue;
+        const uint64_t t1 = t0 + kPlaceSpan < tiles ? t0 + kPlaceSpan : tiles;
+        for (uint64_t tile = t0; tile < t1; ++tile) {
+            const uint64_t start = starts[tile];
+            // (both the same for the whole block) everything here is dropped, or already in place
+            if (start >= static_cast<uint64_t>(n) || start == tile * (2 * HMC_RANDOM_INT_TILE)) continue;
+            const uint64_t b = tile * HMC_RANDOM_INT_TILE + threadIdx.x;
+            uint64_t w0 = 0, w1 = 0;
+            bool take0 = false, take1 = false;
+            if (b < blocks) {
+                block_words(offset + b, seed, w0, w1);
+                take0 = w0 >= threshold;
+                take1 = w1 >= threshold;
+            }
+            uint32_t total;
+            uint64_t at = start + block_exclusive_count((take0 ? 1u : 0u) + (take1 ? 1u : 0u), total);
+            if (take0) {
+                if (at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w0, range));
+                at += 1;
+            }
+            if (take1 && at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w1, range));
         }
-        if (take1 && at < static_cast<uint64_t>(n)) out[at] = static_cast<int64_t>(static_cast<uint64_t>(low) + word_mod(w1, range));
     }
 }
 
@@ -388,7 +402,9 @@ HMC_API hmc_status hmc_random_int(hmc_context_t ctx, const hmc_tensor_desc *out,
         s = launch_status("integer sampling (positions) kernel launch");
         if (s != HMC_OK) return s;
         if (n == 0) return HMC_OK;
-        int_place_kernel<<<grid, kSampleThreads, 0, ctx->stream>>>(p, n, starts, tiles, seed, offset, blocks, low, modulus_of(range), threshold);
+        const uint64_t spans = (tiles + kPlaceSpan - 1) / kPlaceSpan;
+        const unsigned place_grid = static_cast<unsigned>(spans < (uint64_t{1} << 22) ? spans : (uint64_t{1} << 22));
+        int_place_kernel<<<place_grid, kSampleThreads, 0, ctx->stream>>>(p, n, starts, tiles, seed, offset, blocks, low, modulus_of(range), threshold);
         return launch_status("integer sampling (placement) kernel launch");
     });
 }
