@@ -3,12 +3,14 @@
 // (src/backend/cpu/mod.rs:362-403). The library is compiled with -fmad=false, so a*b+c is two
 // roundings unless fma() is spelled out, which is where the CPU calls mul_add.
 //
-// Transcendentals of the float computation type are evaluated in double and rounded once: the
-// result is the correctly rounded f32 value except within ~1e-9 ulp of a tie, hence within one ulp
-// of any libm whose own error is below one ulp (what homura's CPU backend calls).
+// exp, log, log1p, tanh and pow of the float computation type restate the host C library's algorithms and
+// return its bits (libm32.cuh). sin, cos and erf of the float computation type are evaluated in double and
+// rounded once: the correctly rounded f32 value except within ~1e-9 ulp of a tie, hence within one ulp of
+// the C library's sinf / cosf (whose own error is below one ulp) and of the CPU's f64 erf rounded to f32.
 #pragma once
 
 #include "elem.cuh"
+#include "libm32.cuh"
 
 namespace hmc {
 
@@ -71,37 +73,13 @@ __device__ __forceinline__ double reciprocal_short(double s) {
     return r;
 }
 
-// exp of an f32 through f64, without the general-purpose f64 exp: e^x = 2^k * 2^r with t = x * log2(e),
-// k = round(t), r = t - k in [-1/2, 1/2] (exact), 2^r by its Taylor polynomial of degree 10 (relative error
-// below 2^-41), the scaling by 2^k through the exponent field, and one rounding to f32, which also produces
-// subnormal results, 0 and infinity correctly. About 16 f64 operations instead of ~45.
-__device__ __forceinline__ float m_exp(float x) {
-    double t = static_cast<double>(x) * 1.4426950408889634074;
-    t = fmin(fmax(t, -1100.0), 1100.0);
-    const double magic = 6755399441055744.0;  // 1.5 * 2^52: adding it leaves round(t) in the low word
-    const double z = t + magic;
-    const double r = t - (z - magic);
-    int k = __double2loint(z);
-    double p = 0x1.e4cf5158b8ecap-28;
-    p = __fma_rn(p, r, 0x1.b5253d395e7c4p-24);
-    p = __fma_rn(p, r, 0x1.62c0223a5c824p-20);
-    p = __fma_rn(p, r, 0x1.ffcbfc588b0c7p-17);
-    p = __fma_rn(p, r, 0x1.430912f86c787p-13);
-    p = __fma_rn(p, r, 0x1.5d87fe78a6731p-10);
-    p = __fma_rn(p, r, 0x1.3b2ab6fba4e77p-7);
-    p = __fma_rn(p, r, 0x1.c6b08d704a0c0p-5);
-    p = __fma_rn(p, r, 0x1.ebfbdff82c58fp-3);
-    p = __fma_rn(p, r, 0x1.62e42fefa39efp-1);
-    p = __fma_rn(p, r, 1.0);
-    k = max(-1022, min(1023, k));
-    const double scale = __hiloint2double((k + 1023) << 20, 0);
-    const float y = static_cast<float>(p * scale);
-    return x != x ? x + x : y;
-}
+// The f32 exponential, logarithm, log1p, tanh and power return the host C library's bits (libm32.cuh), so
+// that formulas built on them (sigmoid, silu, log_sigmoid, gelu_tanh) are the CPU's bit for bit as well.
+__device__ __forceinline__ float m_exp(float x) { return lm::expf(x); }
 __device__ __forceinline__ double m_exp(double x) { return exp(x); }
-__device__ __forceinline__ float m_log(float x) { return static_cast<float>(log(static_cast<double>(x))); }
+__device__ __forceinline__ float m_log(float x) { return lm::logf(x); }
 __device__ __forceinline__ double m_log(double x) { return log(x); }
-__device__ __forceinline__ float m_log1p(float x) { return static_cast<float>(log1p(static_cast<double>(x))); }
+__device__ __forceinline__ float m_log1p(float x) { return lm::log1pf(x); }
 __device__ __forceinline__ double m_log1p(double x) { return log1p(x); }
 __device__ __forceinline__ float m_sqrt(float x) { return sqrtf(x); }
 __device__ __forceinline__ double m_sqrt(double x) { return sqrt(x); }
@@ -109,13 +87,13 @@ __device__ __forceinline__ float m_sin(float x) { return static_cast<float>(sin(
 __device__ __forceinline__ double m_sin(double x) { return sin(x); }
 __device__ __forceinline__ float m_cos(float x) { return static_cast<float>(cos(static_cast<double>(x))); }
 __device__ __forceinline__ double m_cos(double x) { return cos(x); }
-__device__ __forceinline__ float m_tanh(float x) { return static_cast<float>(tanh(static_cast<double>(x))); }
+__device__ __forceinline__ float m_tanh(float x) { return lm::tanhf(x); }
 __device__ __forceinline__ double m_tanh(double x) { return tanh(x); }
 __device__ __forceinline__ float m_pow(float x, float y) {
-    // x^2 (homura's `x.pow(2)`, e.g. in its rms_norm) is x * x rounded once, which is what a correctly
-    // rounded powf gives; everything else goes through the f64 pow and one rounding.
+    // x^2 (homura's `x.pow(2)`, e.g. in its rms_norm) is x * x rounded once: the C library's powf(x, 2) returns
+    // exactly that for every x (checked over all 2^32 arguments by tests/native/libm32_check.cpp).
     if (y == 2.0f) return x * x;
-    return static_cast<float>(pow(static_cast<double>(x), static_cast<double>(y)));
+    return lm::powf(x, y);
 }
 __device__ __forceinline__ double m_pow(double x, double y) { return pow(x, y); }
 __device__ __forceinline__ float m_abs(float x) { return fabsf(x); }
