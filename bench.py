@@ -1,8 +1,8 @@
-"""Benchmark of the elementwise / broadcast hot path on B200: achieved HBM GB/s by algorithmic bytes.
+"""Benchmark of the elementwise / reduction hot path on B200: achieved HBM GB/s by algorithmic bytes.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2|c3|c4|c5|inputs|all]
 
-Workload (BASELINE.json configs[1], "Elementwise/broadcast at HBM scale"), one step =
+The headline (top-level `value`, `e2e`, `roofline`) is the elementwise / broadcast configuration, one step =
     x bf16 [8192, 8192] ~ N(0, 1), bias f32 [8192, 1], scale bf16 [1, 8192]
     y  = silu(x)     * scale + bias   (bf16 + f32 -> f32)          3 kernels
     yt = silu(x.t()) * scale + bias   (transposed, non-contiguous)  3 kernels
@@ -11,22 +11,32 @@ through the C ABI of include/homura_cuda.h, outputs preallocated from the cachin
 Algorithmic bytes per step (distinct input elements + output elements, temporaries count zero):
 silu 4N, mul 4N, promoting add 6N (twice), cast 6N, with N = 8192^2: 34 N = 2281.7 MB.
 
-Other configurations of BASELINE.json can be timed the same way with `--workload c3|c4|c5` (reductions, softmax,
-sharded-size elementwise + AdamW); the default, and what the headline number is quoted on, is c2.
+The same run adds, under `workloads`, one record per other configuration, each kernel timed alone with L2 flushed
+before it (a "whole step" of reductions over one input would be served from L2 and is not reported):
+    c3  reductions of f32 / i32 [16384, 4096] (sum, mean, var over rows and columns, max + argmax, full sums)
+    c4  softmax / log_softmax of causally masked f32 [8, 32, 2048, 2048], row mean of squares of bf16 [32768, 4096]
+    c5  one GPU's eighth of the sharded configuration: a * b + c on flat f32 2^29, its sum and maximum, and an
+        AdamW step (lr 1e-4, wd 0.01) over the 291 Llama-3-8B-shaped f32 tensors (1/8 of the rows of each,
+        1 003 782 656 parameters, one launch) with the gradient norm
+and, with N > 1 ranks (torchrun), a `sharded` record: the c5 step with its tensors being shards of global ones,
+so that the global sum, maximum and gradient norm gather the ranks' partials over NCCL (all-gather) and fold them
+in rank order inside the timed region, next to the same rank's unsharded timings.
 
-`value` is the whole job's GB/s with inputs resident in HBM; `e2e` is the same metric with the inputs
-coming from pinned host memory and the results going back to it inside the timed region, every step, by the
-blocking copy calls of the C ABI; two threads with a context each take the steps in turn, so that one step's
-results and the next step's inputs cross PCIe at the same time. With N > 1 ranks
-(torchrun) every rank runs the workload on its own GPU (weak scaling, no data-path collective); the time is
-the maximum over ranks. `--impl reference` times the CPU restatement of homura's single-threaded CPU backend
-on a bounded sample of the same workload on the host cores.
+`value` is the whole job's GB/s with inputs resident in HBM: the timed region of K steps is repeated and the
+median repeat is reported (minimum alongside); `e2e` is the same metric with the inputs coming from pinned host
+memory and the results going back to it inside the timed region, every step, by the blocking copy calls of the C
+ABI; two threads with a context each take the steps in turn, so that one step's results and the next step's
+inputs cross PCIe at the same time. With N > 1 ranks every rank runs the headline workload on its own GPU:
+independent replicas, weak scaling, no data-path collective; the time is the maximum over ranks. `--impl
+reference` times the CPU restatement of homura's single-threaded CPU backend on a bounded sample of the same
+workload on the host cores.
 """
 from __future__ import annotations
 
 import argparse
 import ctypes
 import json
+import math
 import os
 import subprocess
 import sys
@@ -45,10 +55,10 @@ STEP_BYTES = 34 * N2
 METRIC = "hbm_gbs_algorithmic"
 UNIT = "GB/s"
 WORKLOAD = "c2_elementwise_broadcast_bf16_8192x8192"
-L2_BYTES = 126 << 20
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel of the c2 step, from one `ncu --set full`
-# capture on B200 (profiles/c2_step_elementwise_kernels.md). Writes are below the algorithmic output where the
-# tail of the output still sits in L2 when the capture ends.
+REPEATS = 7
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel of the headline step, from one
+# `ncu --set full` capture on B200. Writes are below the algorithmic output where the tail of the output still
+# sits in L2 when the capture ends.
 NCU_TRAFFIC_BYTES = {"silu": 219.4e6, "mul_scale": 215.7e6, "add_bias": 345.7e6, "silu_t": 218.6e6, "mul_scale_t": 217.0e6,
                      "add_bias_t": 347.3e6, "cast": 346.2e6}
 
@@ -71,27 +81,31 @@ def peaks() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while running."""
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 50 ms while running."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, index: int, period_ms: int = 50):
+        self.index, self.period_ms, self.proc, self.lines = index, period_ms, None, []
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, text=True)
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
+                                         stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.thread.start()
+            deadline = time.time() + 3.0   # the first sample takes a moment: have one before the timed work starts
+            while not self.lines and time.time() < deadline:
+                time.sleep(0.01)
         except OSError:
             self.proc = None
         return self
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.25)
+            time.sleep(2 * self.period_ms / 1e3)
             self.proc.terminate()
             self.proc.wait()
             self.thread.join(timeout=2)
@@ -112,11 +126,14 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "period_ms": self.period_ms}
 
 
 class Workload:
-    """The C2 step on one backend (device tensors and preallocated outputs)."""
+    """The headline step on one backend (device tensors and preallocated outputs)."""
+
+    name = WORKLOAD
+    dtype = "bf16"
 
     def __init__(self, be, rows: int = ROWS, cols: int = COLS, seed: int = 0):
         from homura_b200.host import BF16, F32
@@ -164,12 +181,16 @@ def _tile_fill(be, big, small):
     n = small.numel
     reps = big.numel // n
     be.copy(big.reshape(reps, n), small.reshape(1, n).expand(reps, n))
+    rest = big.numel - reps * n
+    if rest:
+        be.copy(big.reshape(big.numel).narrow(0, reps * n, rest), small.reshape(n).narrow(0, 0, rest))
 
 
 class C3Workload:
-    """BASELINE configs[2]: reductions of f32 / i32 [16384, 4096]."""
+    """Reductions of f32 / i32 [16384, 4096]."""
 
     name = "c3_reductions_16384x4096"
+    dtype = "f32 / i32, accumulated in f64 / i64"
 
     def __init__(self, be, seed: int = 0):
         from homura_b200.host import F32, I32, I64
@@ -212,10 +233,11 @@ class C3Workload:
 
 
 class C4Workload:
-    """BASELINE configs[3]: softmax / log_softmax of causally masked f32 logits [8, 32, 2048, 2048] and the
-    row mean of squares of bf16 [32768, 4096] as homura's rms_norm composes it (to f32, pow 2, mean)."""
+    """softmax / log_softmax of causally masked f32 logits [8, 32, 2048, 2048] and the row mean of squares of
+    bf16 [32768, 4096] as homura's rms_norm composes it (to f32, pow 2, mean)."""
 
     name = "c4_softmax_8x32x2048x2048"
+    dtype = "f32 / bf16, row maths in f64"
 
     def __init__(self, be, seed: int = 0, batch: int = 256):
         from homura_b200.host import BF16, BOOL, F32
@@ -257,14 +279,29 @@ class C4Workload:
             f()
 
 
+def llama3_8b_shapes() -> list:
+    """The 291 parameter tensors of Llama-3-8B (8 030 261 248 elements): embedding, 32 layers of (q, k, v, o, gate,
+    up, down, two norm weights), the final norm and the output head."""
+    shapes = [(128256, 4096)]
+    for _ in range(32):
+        shapes += [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096), (4096, 14336),
+                   (4096,), (4096,)]
+    shapes += [(4096,), (128256, 4096)]
+    return shapes
+
+
 class C5Workload:
-    """BASELINE configs[4], one GPU's share: a * b + c on flat f32 tensors, their sum and maximum, and an AdamW
-    step (lr 1e-4, wd 0.01) with the gradient norm. `log2n` sets the elements per tensor (2^32 split over 8 GPUs
-    is 2^29 per GPU)."""
+    """One GPU's eighth of the configuration sharded over 8 GPUs: a * b + c on flat f32 tensors of 2^29 elements
+    (2^32 / 8), their sum and maximum, and an AdamW step (lr 1e-4, wd 0.01) over the Llama-3-8B-shaped f32
+    parameters with the gradient norm. Every parameter tensor is split by rows, so a rank holds rows / 8 of each
+    of the 291 tensors. With a `reducer` the tensors are shards of global ones and the reductions that fold the
+    sharded dimension exchange their partials over the communicator."""
 
-    name = "c5_flat_elementwise_adamw"
+    name = "c5_flat_elementwise_adamw_llama3_8b_shard"
+    dtype = "f32, sums in f64"
+    SHARDS = 8
 
-    def __init__(self, be, seed: int = 0, log2n: int = 29, reducer=None):
+    def __init__(self, be, seed: int = 0, log2n: int = 29, reducer=None, param_scale: int = 1):
         from homura_b200.host import F32, F64
         self.be, self.reducer = be, reducer
         n = 1 << log2n
@@ -274,39 +311,58 @@ class C5Workload:
             _tile_fill(be, t, s0)
         self.t = be.empty((n,), F32)
         self.s = be.empty((), F32)
-        # AdamW: params N(0, 0.02), grads N(0, 1e-3), moments start at 0
-        self.p, self.g, self.m, self.v = (be.empty((n,), F32) for _ in range(4))
-        _tile_fill(be, self.p, be.upload(0.02 * philox_normal(1 << 22, 51 + seed), F32))
-        _tile_fill(be, self.g, be.upload(1e-3 * philox_normal(1 << 22, 52 + seed), F32))
-        be.fill(self.m, 0.0)
-        be.fill(self.v, 0.0)
+        # AdamW: params N(0, 0.02), grads N(0, 1e-3), moments start at 0; `param_scale` > 1 shrinks every tensor's
+        # rows further (for short profiler captures)
+        p0 = be.upload(0.02 * philox_normal(1 << 22, 51 + seed), F32)
+        g0 = be.upload(1e-3 * philox_normal(1 << 22, 52 + seed), F32)
+        self.tensors = []
+        for shape in llama3_8b_shapes():
+            local = (max(1, shape[0] // (self.SHARDS * param_scale)),) + tuple(shape[1:])
+            p, g, m, v = (be.empty(local, F32) for _ in range(4))
+            _tile_fill(be, p, p0)
+            _tile_fill(be, g, g0)
+            be.fill(m, 0.0)
+            be.fill(v, 0.0)
+            self.tensors.append((p, g, m, v))
+        self.params = sum(t[0].numel for t in self.tensors)
+        self.group = be.adamw_group(self.tensors, with_grad_sq=True)
+        self.norm_sq = be.empty((), F64)
+        self.norm = be.empty((), F64)
         self.step_no = 0
-        self.op_bytes = {"mul": 12 * n, "add": 12 * n, "sum": 4 * n, "max": 4 * n, "adamw": 28 * n, "grad_sq": 8 * n,
-                         "grad_sum": 4 * n}
-        self.launches_per_step = 7
+        self.op_bytes = {"mul": 12 * n, "add": 12 * n, "sum": 4 * n, "max": 4 * n,
+                         "adamw_291_tensors": 28 * self.params, "grad_norm": 8 * len(self.tensors)}
+        self.launches_per_step = 4 + 2 + 2 + (3 if reducer is not None else 0) * 2
 
     def ops(self):
         from homura_b200 import ffi
+        from homura_b200.host import F64, TensorData
         be = self.be
 
         def adamw():
             self.step_no += 1
-            be.adamw_step(self.p, self.g, self.m, self.v, lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01,
-                          step=float(self.step_no))
-        # with several ranks the tensors are shards of a global one: the three reductions fold the sharded
-        # dimension, so they gather the ranks' partials over NCCL and combine them in rank order
+            self.group.step(lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, step=float(self.step_no))
+
+        # with several ranks the tensors are shards of a global one: the reductions fold the sharded dimension, so
+        # they gather the ranks' partials over NCCL and combine them in rank order
         if self.reducer is not None:
             reduce = lambda op: self.reducer.reduce(op, self.s, self.t, [True])
+            norm_sq = lambda: self.reducer.sum_f64(self.norm_sq, self.group.grad_sq, len(self.tensors))
         else:
             reduce = lambda op: be.reduce(op, self.s, self.t, [True])
+            partials = TensorData(self.group.grad_sq, F64, (len(self.tensors),), (1,))
+            norm_sq = lambda: be.reduce(ffi.HMC_REDUCE_SUM, self.norm_sq, partials, [True])
+
+        def grad_norm():
+            # the per-tensor sums of squares come out of the AdamW launch; fold them (across ranks too) and root
+            norm_sq()
+            be.unary(ffi.HMC_UNARY_SQRT, self.norm, self.norm_sq)
         return [
             ("mul", lambda: be.binary(ffi.HMC_BINARY_MUL, self.t, self.a, self.b)),
             ("add", lambda: be.binary(ffi.HMC_BINARY_ADD, self.t, self.t, self.c)),
             ("sum", lambda: reduce(ffi.HMC_REDUCE_SUM)),
             ("max", lambda: reduce(ffi.HMC_REDUCE_MAX)),
-            ("adamw", adamw),
-            ("grad_sq", lambda: be.binary(ffi.HMC_BINARY_MUL, self.t, self.g, self.g)),
-            ("grad_sum", lambda: reduce(ffi.HMC_REDUCE_SUM)),
+            ("adamw_291_tensors", adamw),
+            ("grad_norm", grad_norm),
         ]
 
     def step(self):
@@ -317,10 +373,11 @@ class C5Workload:
 class InputsWorkload:
     """The step before the path in every config: the samplers that make the inputs (rand bf16 [8192, 8192],
     randn f32 [16384, 4096], randint over a range that rejects words and one that does not) and the causal mask
-    in front of C4's softmax (triu on f32 [64, 2048, 2048], and the Bool mask itself). Bytes are those written,
+    in front of the softmax (triu on f32 [64, 2048, 2048], and the Bool mask itself). Bytes are those written,
     plus the triangle's reads of the kept half."""
 
     name = "inputs_samplers_and_mask"
+    dtype = "bf16 / f32 / i64"
 
     def __init__(self, be, seed: int = 0):
         from homura_b200.host import BF16, BOOL, F32, I64, Generator
@@ -348,7 +405,6 @@ class InputsWorkload:
         # distinct rows are read and written
         self.table_grad = be.empty((vocab, width), BF16)
         be.fill(self.table_grad, 0.0)
-        import math
         touched = int(vocab * (1.0 - math.exp(-tokens / vocab)))
         e = b * m * m
         self.op_bytes = {"embedding_bf16": 4 * tokens * width + 8 * tokens,
@@ -391,12 +447,116 @@ class Events:
         self.be._check(self.be.lib.hmc_event_elapsed_ms(a, b, ctypes.byref(ms)))
         return ms.value
 
+    def destroy(self, ev):
+        self.be.lib.hmc_event_destroy(ev)
+
+
+class Runner:
+    """Timing of one backend's work with events on its stream; with several ranks every region starts at a
+    barrier and its time is the maximum over ranks."""
+
+    def __init__(self, be, dist, local: int, world: int):
+        self.be, self.dist, self.local, self.world = be, dist, local, world
+        self.ev = Events(be)
+        self.scratch = None
+
+    def barrier(self):
+        self.be.synchronize()
+        if self.dist is not None:
+            import torch
+            self.dist.barrier(device_ids=[self.local])
+            torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        if self.dist is None:
+            return list(values)
+        import torch
+        t = torch.tensor(list(values), device="cuda", dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    def timed_steps(self, w, steps: int, warmup: int, repeats: int) -> list:
+        """`repeats` regions of exactly `steps` steps each after `warmup` steps; ms per region, max over ranks."""
+        for _ in range(warmup):
+            w.step()
+        out = []
+        start, stop = self.ev.new(), self.ev.new()
+        for _ in range(repeats):
+            self.barrier()
+            self.ev.record(start)
+            for _ in range(steps):
+                w.step()
+            self.ev.record(stop)
+            self.be.synchronize()
+            out.append(self.ev.elapsed(start, stop))
+        self.barrier()
+        self.ev.destroy(start)
+        self.ev.destroy(stop)
+        return self.max_over_ranks(out)
+
+    def flushed_per_op(self, ops, reps: int = 10, warm: int = 3) -> dict:
+        """Mean ms of each op alone, a 512 MB buffer written before every launch so that nothing is served from L2."""
+        be, ev = self.be, self.ev
+        if self.scratch is None:
+            self.scratch = be.storage(512 << 20)
+        per_op = {}
+        a, b = ev.new(), ev.new()
+        for name, f in ops:
+            times = []
+            for i in range(warm + reps):
+                be._check(be.lib.hmc_memset(be.ctx, self.scratch.ptr, i & 0xFF, self.scratch.nbytes))
+                ev.record(a)
+                f()
+                ev.record(b)
+                t_ms = ev.elapsed(a, b)
+                if i >= warm:
+                    times.append(t_ms)
+            per_op[name] = float(np.mean(times))
+        ev.destroy(a)
+        ev.destroy(b)
+        return per_op
+
+
+def roofline_of(w, per_op: dict, traffic: dict | None = None) -> dict:
+    """The roofline entry of a workload: its kernel furthest below the HBM peak that carries real traffic (ops
+    of a few KB, such as folding 291 partial sums, are launch-bound and not judged against bandwidth)."""
+    peak, peak_kind = peaks()
+    gbs = {k: w.op_bytes[k] / (v * 1e-3) / 1e9 for k, v in per_op.items()}
+    streaming = [k for k in per_op if w.op_bytes[k] >= (64 << 20)] or list(per_op)
+    dominant = max(per_op, key=per_op.get)
+    worst = min(streaming, key=lambda k: gbs[k])
+    total_ms = sum(per_op.values())
+    def entry(k):
+        return {"bound": "hbm", "kernel": k, "achieved": gbs[k], "peak": peak, "peak_kind": peak_kind, "unit": UNIT,
+                "frac": gbs[k] / peak, "traffic": (traffic or {}).get(k), "algorithmic_bytes": w.op_bytes[k],
+                "share_of_step": per_op[k] / total_ms}
+    return {"dominant": entry(dominant), "worst": entry(worst), "per_kernel_gbs": gbs, "per_kernel_ms": per_op}
+
+
+def workload_record(runner: Runner, w, steps: int, warmup: int) -> dict:
+    """One `workloads` entry: every kernel alone with L2 flushed (the honest per-kernel figures, and their sum as
+    the step), plus the same step back to back."""
+    per_op = runner.flushed_per_op(w.ops())
+    per_op = dict(zip(per_op.keys(), runner.max_over_ranks(per_op.values())))
+    regions = runner.timed_steps(w, steps, warmup, 3)
+    step_bytes = sum(w.op_bytes.values())
+    flushed_ms = sum(per_op.values())
+    r = roofline_of(w, per_op)
+    back_ms = float(np.median(regions)) / steps
+    return {"workload": w.name, "dtype": w.dtype, "metric": METRIC, "unit": UNIT,
+            "value": step_bytes / (flushed_ms * 1e-3) / 1e9, "ms_per_step": flushed_ms,
+            "value_basis": "sum of the kernels' times, each alone with L2 flushed before it",
+            "back_to_back": {"value": step_bytes / (back_ms * 1e-3) / 1e9, "ms_per_step": back_ms,
+                             "note": "consecutive kernels over one input are partly served from the 126 MB L2"},
+            "algorithmic_bytes_per_step": step_bytes, "kernels_per_step": w.launches_per_step,
+            "roofline": dict(r["worst"], per_kernel_gbs=r["per_kernel_gbs"], per_kernel_ms=r["per_kernel_ms"]),
+            "frac_of_measured_copy": {k: v / r["worst"]["peak"] for k, v in r["per_kernel_gbs"].items()}}
+
 
 def cpu_sample(seconds_budget: float = 20.0) -> dict:
     """The CPU restatement of homura's CPU backend (single-threaded, as the original is by construction:
     every kernel runs inside one global lock, src/backend/cpu/mod.rs:40-64) on rows of the same workload."""
     sys.path.insert(0, str(ROOT / "tests"))
-    from homura_b200 import ffi
     from oracle_backend import OracleBackend
     be = OracleBackend()
     rows = 256
@@ -420,7 +580,6 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    per_step = []
     sys.path.insert(0, str(ROOT / "tests"))
     from oracle_backend import OracleBackend
     be = OracleBackend()
@@ -430,9 +589,7 @@ def run_reference(args) -> None:
         w.step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        t1 = time.perf_counter()
         w.step()
-        per_step.append(time.perf_counter() - t1)
     dt = time.perf_counter() - t0
     value = 34 * rows * COLS * args.steps / dt / 1e9
     line = {
@@ -449,138 +606,11 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "inputs"])
-    ap.add_argument("--c4-batch", type=int, default=256,
-                    help="matrices of [2048, 2048] logits in the c4 workload (256 = [8, 32, 2048, 2048]); a smaller "
-                         "number keeps a profiler capture short")
-    ap.add_argument("--profile", action="store_true",
-                    help="only the warm-up and the timed steps (no per-kernel loop, end-to-end pass or CPU sample): "
-                         "the short command to run under ncu")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
-    if args.impl == "reference":
-        return run_reference(args)
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
+def end_to_end(be, w, runner: Runner, rank: int, steps: int) -> dict:
+    """The headline step with its inputs coming from pinned host memory and its three results going back to it
+    inside the timed region, every step, through the blocking copies of the C ABI."""
     from homura_b200.host import CudaBackend
-    be = CudaBackend(local)
-    ev = Events(be)
-    if args.workload == "c2":
-        w = Workload(be, seed=rank)
-        workload_name, step_bytes = WORKLOAD, STEP_BYTES
-    elif args.workload == "c5" and world > 1:
-        from homura_b200.shard import NcclComm, ShardedReducer
-        box = [NcclComm.unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        comm = NcclComm(be, world, rank, box[0])
-        n_local = 1 << 29
-        w = C5Workload(be, seed=rank, log2n=29, reducer=ShardedReducer(be, comm, [r * n_local for r in range(world)], world * n_local))
-        workload_name, step_bytes = w.name + "_sharded", sum(w.op_bytes.values())
-    else:
-        if args.workload == "c4":
-            w = C4Workload(be, seed=rank, batch=args.c4_batch)
-        else:
-            w = {"c3": C3Workload, "c5": C5Workload, "inputs": InputsWorkload}[args.workload](be, seed=rank)
-        workload_name, step_bytes = w.name, sum(w.op_bytes.values())
-        if args.workload == "c4" and args.c4_batch != 256:
-            workload_name += f"_batch{args.c4_batch}"
-    ops = w.ops()
 
-    def barrier():
-        be.synchronize()
-        if dist is not None:
-            import torch
-            dist.barrier(device_ids=[local])
-            torch.cuda.synchronize()
-
-    # ---- device-resident throughput: W warm-up steps, then exactly K timed steps ----
-    for _ in range(args.warmup):
-        w.step()
-    barrier()
-    start, stop = ev.new(), ev.new()
-    with ClockSampler(local) as clocks:
-        ev.record(start)
-        for _ in range(args.steps):
-            w.step()
-        ev.record(stop)
-        be.synchronize()
-    ms = ev.elapsed(start, stop)
-    barrier()
-    if dist is not None:
-        import torch
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    value = step_bytes * args.steps * world / (ms * 1e-3) / 1e9
-    if args.profile:
-        if rank == 0:
-            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                              "warmup": args.warmup, "ms_per_step": ms / args.steps, "profile_run": True,
-                              "gpu_launches": w.launches_per_step * args.steps}))
-        be.close()
-        if dist is not None:
-            dist.destroy_process_group()
-        return
-
-    # ---- per-kernel durations, each launch alone with L2 flushed before it ----
-    scratch = be.storage(512 << 20)
-    per_op = {}
-    for name, f in ops:
-        times = []
-        for i in range(3 + 10):
-            be._check(be.lib.hmc_memset(be.ctx, scratch.ptr, i & 0xFF, scratch.nbytes))
-            a, b = ev.new(), ev.new()
-            ev.record(a)
-            f()
-            ev.record(b)
-            t_ms = ev.elapsed(a, b)
-            if i >= 3:
-                times.append(t_ms)
-            be.lib.hmc_event_destroy(a)
-            be.lib.hmc_event_destroy(b)
-        per_op[name] = float(np.mean(times))
-    total_op_ms = sum(per_op.values())
-    dominant = max(per_op, key=per_op.get)
-    peak, peak_kind = peaks()
-    achieved = w.op_bytes[dominant] / (per_op[dominant] * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": UNIT,
-                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(dominant) if args.workload == "c2" else None,
-                "algorithmic_bytes": w.op_bytes[dominant], "share_of_step": per_op[dominant] / total_op_ms,
-                "per_kernel_gbs": {k: w.op_bytes[k] / (v * 1e-3) / 1e9 for k, v in per_op.items()},
-                "per_kernel_ms": per_op}
-
-    if args.workload != "c2":
-        # the other configurations report device-resident throughput and per-kernel rooflines only
-        if rank == 0:
-            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                              "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-                              "scaling": "weak", "vs_baseline": None, "data": "synthetic",
-                              "config": {"workload": workload_name, "kernels_per_step": w.launches_per_step,
-                                         "algorithmic_bytes_per_step": step_bytes},
-                              "clocks": clocks.summary(), "gpu_launches": w.launches_per_step * args.steps,
-                              "roofline": roofline}))
-        be.close()
-        if dist is not None:
-            dist.destroy_process_group()
-        return
-
-    # ---- end to end: inputs from pinned host memory, results back to it, inside the timed region ----
     def pinned(nbytes):
         p = ctypes.c_void_p()
         be._check(be.lib.hmc_host_alloc(nbytes, ctypes.byref(p)))
@@ -597,8 +627,7 @@ def main() -> None:
     # Two lanes, as two threads of a homura program would run them: each has its own context (stream), its own device
     # tensors and result buffers, and makes the same blocking calls; while one lane's results travel to the host the
     # other lane's inputs travel to the device (PCIe carries both directions at once) and its kernels run.
-    import threading
-    be2 = CudaBackend(local)
+    be2 = CudaBackend(be.device)
     w2 = Workload(be2, seed=rank)
     hy2, hyt2, hc2 = pinned(out_bytes), pinned(out_bytes), pinned(out_bytes)
     lanes = [(be, w, (hy, hyt, hc)), (be2, w2, (hy2, hyt2, hc2))]
@@ -631,48 +660,207 @@ def main() -> None:
         if failures:
             raise failures[0]
 
-    e2e_steps = max(4, min(args.steps, 10))
+    e2e_steps = max(4, min(steps, 10))
     run_lanes((2, 2))
-    barrier()
-    ev.record(start)
+    runner.barrier()
+    start, stop = runner.ev.new(), runner.ev.new()
+    runner.ev.record(start)
     run_lanes((e2e_steps - e2e_steps // 2, e2e_steps // 2))
-    ev.record(stop)  # after the other lane's work has completed: the region covers both
+    runner.ev.record(stop)  # after the other lane's work has completed: the region covers both
     be.synchronize()
-    e2e_ms = ev.elapsed(start, stop)
-    if dist is not None:
-        import torch
-        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = STEP_BYTES * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
+    e2e_ms = runner.max_over_ranks([runner.ev.elapsed(start, stop)])[0]
     for p in (hx, hb, hs, hy, hyt, hc, hy2, hyt2, hc2):
         be.lib.hmc_host_free(p)
     be2.close()
+    return {"value": STEP_BYTES * e2e_steps * runner.world / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps, "lanes": 2, "steps": e2e_steps}
 
+
+def sharded_record(be, runner: Runner, rank: int, world: int, steps: int, warmup: int) -> dict:
+    """The c5 step on `world` ranks whose tensors are the shards of global ones: per rank the same work as one GPU's
+    share, plus, inside the timed region, the exchange the global sum, maximum and gradient norm need (an NCCL
+    all-gather of 8 bytes per rank and a rank-ordered combine kernel each)."""
+    from homura_b200 import ffi
+    from homura_b200.shard import NcclComm, ShardedReducer
+    box = [NcclComm.unique_id() if rank == 0 else None]
+    runner.dist.broadcast_object_list(box, src=0)
+    comm = NcclComm(be, world, rank, box[0])
+    n_local = 1 << 29
+    reducer = ShardedReducer(be, comm, [r * n_local for r in range(world)], world * n_local)
+    w = C5Workload(be, seed=rank, log2n=29, reducer=reducer)
+    alone = C5Workload.__new__(C5Workload)      # the same tensors without the exchange, for the per-op comparison
+    alone.__dict__.update(w.__dict__)
+    alone.reducer = None
+    step_bytes = sum(w.op_bytes.values())
+    regions = runner.timed_steps(w, steps, warmup, REPEATS)
+    regions_alone = runner.timed_steps(alone, steps, warmup, 3)
+    per_op = runner.flushed_per_op(w.ops())
+    per_op = dict(zip(per_op.keys(), runner.max_over_ranks(per_op.values())))
+    per_op_alone = runner.flushed_per_op(alone.ops())
+    per_op_alone = dict(zip(per_op_alone.keys(), runner.max_over_ranks(per_op_alone.values())))
+    # the exchange by itself: all-gather of one f64 per rank and the combine kernel, on an 8-byte partial
+    from homura_b200.host import F64, TensorData
+    part = be.storage(8)
+    be.fill(TensorData(part, F64, (1,), (1,)), 1.0)
+    exchange = runner.flushed_per_op([("allgather_8_bytes_per_rank_and_combine",
+                                       lambda: be.shard_combine_float(ffi.HMC_REDUCE_SUM, w.s, reducer._gather(part, 8), world, 1, world))])
+    exchange_ms = runner.max_over_ranks(exchange.values())[0]
+    med = float(np.median(regions))
+    med_alone = float(np.median(regions_alone))
+    rec = {"workload": w.name + "_sharded", "dtype": w.dtype, "metric": METRIC, "unit": UNIT, "ranks": world,
+           "collective": "ncclAllGather of the ranks' 8-byte partials + rank-ordered combine kernel, three per step "
+                         "(global sum, global maximum, gradient norm), on the compute stream",
+           "value": step_bytes * steps * world / (med * 1e-3) / 1e9, "ms_per_step": med / steps,
+           "value_min_time": step_bytes * steps * world / (min(regions) * 1e-3) / 1e9,
+           "repeats": len(regions), "steps_per_repeat": steps,
+           "unsharded_same_ranks": {"value": step_bytes * steps * world / (med_alone * 1e-3) / 1e9, "ms_per_step": med_alone / steps},
+           "algorithmic_bytes_per_step_per_rank": step_bytes,
+           "per_op_ms_sharded": per_op, "per_op_ms_unsharded": per_op_alone,
+           "exchange_ms": exchange_ms, "exchange_share_of_step": 3 * exchange_ms / sum(per_op.values()),
+           "params_per_rank": w.params}
+    comm.close()
+    return rec
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="all", choices=["all", "c2", "c3", "c4", "c5", "inputs"],
+                    help="all (default): the headline with the c3 / c4 / c5 records (and the sharded record with several "
+                         "ranks); c2: the headline alone; another name: that workload's record alone")
+    ap.add_argument("--c4-batch", type=int, default=256,
+                    help="matrices of [2048, 2048] logits in the c4 workload (256 = [8, 32, 2048, 2048]); a smaller "
+                         "number keeps a profiler capture short")
+    ap.add_argument("--c5-param-scale", type=int, default=1,
+                    help="shrinks the rows of every AdamW tensor by this factor (for short profiler captures)")
+    ap.add_argument("--profile", action="store_true",
+                    help="only the warm-up and the timed steps of the chosen workload (no per-kernel loop, end-to-end "
+                         "pass or CPU sample): the short command to run under ncu")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from homura_b200.host import CudaBackend
+    be = CudaBackend(local)
+    runner = Runner(be, dist, local, world)
+
+    def make(name):
+        if name == "c2":
+            return Workload(be, seed=rank)
+        if name == "c3":
+            return C3Workload(be, seed=rank)
+        if name == "c4":
+            return C4Workload(be, seed=rank, batch=args.c4_batch)
+        if name == "c5":
+            return C5Workload(be, seed=rank, param_scale=args.c5_param_scale)
+        return InputsWorkload(be, seed=rank)
+
+    def finish():
+        be.close()
+        if dist is not None:
+            dist.destroy_process_group()
+
+    if args.profile:
+        w = make("c2" if args.workload == "all" else args.workload)
+        regions = runner.timed_steps(w, args.steps, args.warmup, 1)
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                              "value": sum(w.op_bytes.values()) * args.steps * world / (regions[0] * 1e-3) / 1e9,
+                              "ms_per_step": regions[0] / args.steps, "profile_run": True, "workload": w.name,
+                              "gpu_launches": w.launches_per_step * args.steps}))
+        return finish()
+
+    if args.workload not in ("all", "c2"):
+        # one workload's record alone
+        with ClockSampler(local) as clocks:
+            rec = workload_record(runner, make(args.workload), args.steps, args.warmup)
+        if rank == 0:
+            rec.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+                        "vs_baseline": None, "data": "synthetic", "config": {"workload": rec["workload"]},
+                        "clocks": clocks.summary(), "gpu_launches": rec["kernels_per_step"] * (13 + 3 * args.steps + args.warmup)})
+            print(json.dumps(rec))
+        return finish()
+
+    # ---- the headline: device-resident throughput, W warm-up steps, then REPEATS regions of exactly K steps ----
+    w = make("c2")
+    launches = 0
+    with ClockSampler(local) as clocks:
+        regions = runner.timed_steps(w, args.steps, args.warmup, REPEATS)
+        launches += w.launches_per_step * (args.warmup + REPEATS * args.steps)
+        per_op = runner.flushed_per_op(w.ops())
+        per_op = dict(zip(per_op.keys(), runner.max_over_ranks(per_op.values())))
+        launches += w.launches_per_step * 13
+    ms = float(np.median(regions))
+    value = STEP_BYTES * args.steps * world / (ms * 1e-3) / 1e9
+    peak, peak_kind = peaks()
+    r = roofline_of(w, per_op, NCU_TRAFFIC_BYTES)
+    roofline = dict(r["dominant"], per_kernel_gbs=r["per_kernel_gbs"], per_kernel_ms=r["per_kernel_ms"],
+                    worst_kernel=r["worst"]["kernel"], worst_frac=r["worst"]["frac"])
+    e2e = end_to_end(be, w, runner, rank, args.steps)
+    launches += w.launches_per_step * (e2e["steps"] + 4)
+    del w
+
+    workloads, sharded = {}, None
+    if args.workload == "all":
+        with ClockSampler(local) as clocks2:
+            names = ["c3", "c4", "c5"] if world == 1 else ["c5"]   # c3 / c4 do not shard: measured on one GPU only
+            for name in names:
+                wl = make(name)
+                workloads[name] = workload_record(runner, wl, max(3, args.steps // 4), args.warmup)
+                launches += wl.launches_per_step * (13 + 3 * max(3, args.steps // 4) + args.warmup)
+                del wl
+                be.synchronize()
+                be.allocator.empty_cache()
+            if world > 1:
+                sharded = sharded_record(be, runner, rank, world, max(3, args.steps // 4), args.warmup)
+        workloads_clocks = clocks2.summary()
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_sample()
-    barrier()
+    runner.barrier()
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "rows": ROWS, "cols": COLS, "kernels_per_step": w.launches_per_step,
+            "config": {"workload": WORKLOAD, "rows": ROWS, "cols": COLS, "kernels_per_step": 7,
                        "algorithmic_bytes_per_step": STEP_BYTES, "l2": "inputs_larger_than_l2 (x is 134 MB, outputs 268 MB)",
+                       "ranks": "independent replicas of the step, one per GPU, no data-path collective" if world > 1 else "one GPU",
                        "elements_per_s": 7 * N2 * args.steps * world / (ms * 1e-3),
                        "frac_of_nominal_8tbs": value / world / 8000.0, "frac_of_measured_copy": value / world / peak},
+            "repeats": {"n": len(regions), "steps_each": args.steps, "value_is": "median",
+                        "gbs_median": value, "gbs_best": STEP_BYTES * args.steps * world / (min(regions) * 1e-3) / 1e9,
+                        "gbs_worst": STEP_BYTES * args.steps * world / (max(regions) * 1e-3) / 1e9,
+                        "ms_per_step_all": [t / args.steps for t in regions]},
             "clocks": clocks.summary(),
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / e2e_steps, "lanes": 2},
-            "gpu_launches": w.launches_per_step * args.steps,
+            "e2e": e2e,
+            "gpu_launches": 7 * args.steps * len(regions),
+            "gpu_launches_whole_run": launches,
             "roofline": roofline,
             "cpu_baseline": cpu,
         }
+        if workloads:
+            line["workloads"] = workloads
+            line["workloads_clocks"] = workloads_clocks
+        if sharded is not None:
+            line["sharded"] = sharded
         print(json.dumps(line))
-    be.close()
-    if dist is not None:
-        dist.destroy_process_group()
+    finish()
 
 
 if __name__ == "__main__":

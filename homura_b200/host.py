@@ -740,6 +740,61 @@ class CudaBackend:
         self._check(self.lib.hmc_adamw_step(self.ctx, d[0], d[1], d[2], d[3], ctypes.byref(sc)))
 
 
+    def adamw_group(self, tensors: Sequence[Sequence[TensorData]], with_grad_sq: bool = False) -> "AdamWGroup":
+        """The tensors of one parameter group, prepared for :meth:`AdamWGroup.step`."""
+        return AdamWGroup(self, tensors, with_grad_sq)
+
+
+class AdamWGroup:
+    """One parameter group of an optimizer: (param, grad, exp_avg, exp_avg_sq) per parameter, all of one float
+    dtype. Contiguous tensors are updated by one hmc_adamw_step_many launch; views with other strides go
+    through hmc_adamw_step one by one (same bits). With `with_grad_sq` every step also leaves the f64 sums of
+    the squared gradients, one per parameter in the order given (the contiguous ones first), in `grad_sq`."""
+
+    def __init__(self, be: "CudaBackend", tensors: Sequence[Sequence[TensorData]], with_grad_sq: bool = False):
+        self.be = be
+        tensors = [tuple(t) for t in tensors]
+        assert tensors, "an empty parameter group"
+        self.dtype = tensors[0][0].dtype
+        for t in tensors:
+            assert len(t) == 4 and all(x.dtype == self.dtype and x.shape == t[0].shape for x in t)
+        self.flat = [t for t in tensors if all(x.is_contiguous() for x in t)]
+        self.strided = [t for t in tensors if not all(x.is_contiguous() for x in t)]
+        assert not (with_grad_sq and self.strided), "gradient squares are summed for contiguous tensors only"
+        n = len(self.flat)
+        self.table = (ffi.hmc_adamw_tensor * max(n, 1))()
+        es = SIZE[self.dtype]
+        for i, (p, g, m, v) in enumerate(self.flat):
+            e = self.table[i]
+            e.param, e.grad = p.storage.ptr + p.offset * es, g.storage.ptr + g.offset * es
+            e.exp_avg, e.exp_avg_sq = m.storage.ptr + m.offset * es, v.storage.ptr + v.offset * es
+            e.n = p.numel
+        nbytes = ctypes.c_int64()
+        be._check(be.lib.hmc_adamw_step_many_workspace(self.dtype, self.table, n, int(with_grad_sq), ctypes.byref(nbytes)))
+        self.workspace = be.workspace(nbytes.value)
+        self.grad_sq = be.storage(8 * n) if with_grad_sq and n else None
+
+    def step(self, *, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: float) -> None:
+        be = self.be
+        sc = adamw_scalars(self.dtype, lr, beta1, beta2, eps, weight_decay, step)
+        if self.flat:
+            gs = ctypes.cast(self.grad_sq.ptr, ctypes.POINTER(ctypes.c_double)) if self.grad_sq is not None else None
+            be._check(be.lib.hmc_adamw_step_many(be.ctx, self.dtype, self.table, len(self.flat), ctypes.byref(sc), gs,
+                                                 self.workspace.ptr if self.workspace else None,
+                                                 self.workspace.nbytes if self.workspace else 0))
+        for p, g, m, v in self.strided:
+            d = descs("adamw_step", [p, g, m, v])
+            if d is not None:
+                be._check(be.lib.hmc_adamw_step(be.ctx, d[0], d[1], d[2], d[3], ctypes.byref(sc)))
+
+    def grad_squares(self) -> np.ndarray:
+        """The per-parameter f64 sums of the last step (a blocking copy)."""
+        out = np.empty(len(self.flat), dtype=np.float64)
+        if out.size:
+            self.be._check(self.be.lib.hmc_copy_to_host(self.be.ctx, out.ctypes.data, self.grad_sq.ptr, out.nbytes))
+        return out
+
+
 def around(kernel: str, operands: Sequence[TensorData], shape: Sequence[int], dim: int):
     """Descriptions with the dimensions before `dim` and those after it merged, `dim` kept in between, and the position
     of `dim` among them (src/backend/rocm/index.rs:62-84). `shape` has elements."""

@@ -18,7 +18,7 @@ import math
 from typing import Optional, Sequence
 
 from . import ffi
-from .host import I64, SIZE, BackendError, Storage, TensorData, is_float
+from .host import F64, I64, SIZE, BackendError, Storage, TensorData, contiguous_strides, is_float
 
 
 def split_rows(n: int, ranks: int) -> list:
@@ -68,45 +68,90 @@ class NcclComm:
 
 class ShardedReducer:
     """Reductions over the sharded (outermost) dimension. `shard` is this rank's block of the global tensor;
-    `offsets[r]` is the first global index of rank r's block along that dimension; `global_rows` its size."""
+    `offsets[r]` is the first global index of rank r's block along that dimension; `global_rows` its size.
+
+    A rank may hold an empty block (more ranks than rows): it contributes the identity of sums and products.
+    Maxima, minima and their indices need a value from every rank, so they are refused on every rank alike,
+    before any local work or collective, when some block is empty: the block lengths follow from `offsets` and
+    `global_rows`, which all ranks share, so no rank is left waiting in the all-gather.
+
+    The partial and gathered buffers are kept and reused from call to call (all work is ordered on the backend's
+    one stream, so a buffer is free again when the next call's kernels run)."""
 
     def __init__(self, backend, comm, offsets: Sequence[int], global_rows: int):
         self.be, self.comm = backend, comm
         self.offsets, self.global_rows = list(offsets), global_rows
+        assert len(self.offsets) == comm.ranks, "one offset per rank"
+        ends = self.offsets[1:] + [global_rows]
+        self.lengths = [e - o for o, e in zip(self.offsets, ends)]
+        assert all(n >= 0 for n in self.lengths), "offsets must not decrease and must end within global_rows"
+        self._buffers = {}
 
-    def _gather(self, local: Storage, bytes_per_rank: int) -> Storage:
-        gathered = self.be.storage(bytes_per_rank * self.comm.ranks)
+    def _buffer(self, tag: str, nbytes: int) -> Storage:
+        key = (tag, nbytes)
+        if key not in self._buffers:
+            self._buffers[key] = self.be.storage(nbytes)
+        return self._buffers[key]
+
+    def _gather(self, local: Storage, bytes_per_rank: int, tag: str = "gathered") -> Storage:
+        gathered = self._buffer(tag, bytes_per_rank * self.comm.ranks)
         self.comm.allgather(local, gathered, bytes_per_rank)
         return gathered
 
+    def _need_every_block(self, what: str) -> None:
+        empty = [r for r, n in enumerate(self.lengths) if n == 0]
+        if empty:
+            raise BackendError(ffi.HMC_INVALID, f"{what} across shards needs a nonempty block on every rank "
+                                                f"(rank {empty[0]} holds none of the {self.global_rows} rows)")
+
+    def _fill(self, storage: Storage, dtype: int, n: int, value) -> None:
+        self.be.fill(TensorData(storage, dtype, (n,), (1,)), value)
+
     def reduce(self, op: int, out: TensorData, shard: TensorData, mask: Sequence[bool]) -> None:
-        """SUM, PROD, MEAN, MAX or MIN of the global tensor over the dimensions in `mask` (which include
-        dimension 0) into the contiguous `out`, on every rank. Every rank holds at least one row."""
+        """SUM, PROD, MEAN, MAX, MIN, ALL or ANY of the global tensor over the dimensions in `mask` (which
+        include dimension 0) into the contiguous `out`, on every rank."""
         assert len(mask) == len(shard.shape) and mask[0], "the sharded (first) dimension must be reduced"
         be, nout = self.be, out.numel
+        empty = shard.numel == 0
+        if op in (ffi.HMC_REDUCE_MAX, ffi.HMC_REDUCE_MIN):
+            self._need_every_block("max and min")
+        if nout == 0:
+            return
         if op in (ffi.HMC_REDUCE_SUM, ffi.HMC_REDUCE_PROD, ffi.HMC_REDUCE_MEAN) and is_float(shard.dtype):
-            local = be.storage(8 * nout)
-            be.reduce_partial(op, local, shard, mask)
+            local = self._buffer("f64", 8 * nout)
+            if empty:
+                self._fill(local, F64, nout, 1.0 if op == ffi.HMC_REDUCE_PROD else 0.0)
+            else:
+                be.reduce_partial(op, local, shard, mask)
             gathered = self._gather(local, 8 * nout)
             reduced_per_row = math.prod(n for n, m in zip(shard.shape[1:], mask[1:]) if m)
             be.shard_combine_float(op, out, gathered, self.comm.ranks, nout, self.global_rows * reduced_per_row)
         elif op in (ffi.HMC_REDUCE_SUM, ffi.HMC_REDUCE_PROD):
-            local = be.empty(out.shape, I64)
-            be.reduce(op, local, shard, mask)
-            gathered = self._gather(local.storage, 8 * nout)
+            store = self._buffer("i64", 8 * nout)
+            local = TensorData(store, I64, tuple(out.shape), tuple(contiguous_strides(out.shape)))
+            if empty:
+                self._fill(store, I64, nout, 1 if op == ffi.HMC_REDUCE_PROD else 0)
+            else:
+                be.reduce(op, local, shard, mask)
+            gathered = self._gather(store, 8 * nout)
             be.shard_combine_int(op, out, gathered, self.comm.ranks, nout)
         elif op in (ffi.HMC_REDUCE_MAX, ffi.HMC_REDUCE_MIN):
-            local = be.empty(out.shape, shard.dtype)
+            store = self._buffer("extreme", SIZE[shard.dtype] * nout)
+            local = TensorData(store, shard.dtype, tuple(out.shape), tuple(contiguous_strides(out.shape)))
             be.reduce(op, local, shard, mask)
-            gathered = self._gather(local.storage, SIZE[shard.dtype] * nout)
+            gathered = self._gather(store, SIZE[shard.dtype] * nout)
             be.shard_combine_extreme(op == ffi.HMC_REDUCE_MAX, out, None, gathered, shard.dtype, None, None,
                                      self.comm.ranks, nout)
         elif op in (ffi.HMC_REDUCE_ALL, ffi.HMC_REDUCE_ANY):
             # every rank's result is 0 or 1 in out's dtype (Bool, or U8 for U8 tensors): all = the minimum over
-            # the ranks, any = the maximum
-            local = be.empty(out.shape, out.dtype)
-            be.reduce(op, local, shard, mask)
-            gathered = self._gather(local.storage, SIZE[out.dtype] * nout)
+            # the ranks, any = the maximum; an empty block is all-true and any-false
+            store = self._buffer("flags", SIZE[out.dtype] * nout)
+            local = TensorData(store, out.dtype, tuple(out.shape), tuple(contiguous_strides(out.shape)))
+            if empty:
+                self._fill(store, out.dtype, nout, 1 if op == ffi.HMC_REDUCE_ALL else 0)
+            else:
+                be.reduce(op, local, shard, mask)
+            gathered = self._gather(store, SIZE[out.dtype] * nout)
             be.shard_combine_extreme(op == ffi.HMC_REDUCE_ANY, out, None, gathered, out.dtype, None, None,
                                      self.comm.ranks, nout)
         else:
@@ -119,21 +164,47 @@ class ShardedReducer:
         assert len(mask) == len(shard.shape) and mask[0], "the sharded (first) dimension must be reduced"
         assert is_float(shard.dtype)
         be, nout = self.be, out.numel
+        if nout == 0:
+            return
+        empty = shard.numel == 0
         count = self.global_rows * math.prod(n for n, m in zip(shard.shape[1:], mask[1:]) if m)
-        sums = be.storage(8 * nout)
-        be.reduce_partial(ffi.HMC_REDUCE_SUM, sums, shard, mask)
-        means = be.storage(8 * nout)
+        sums = self._buffer("f64", 8 * nout)
+        if empty:
+            self._fill(sums, F64, nout, 0.0)
+        else:
+            be.reduce_partial(ffi.HMC_REDUCE_SUM, sums, shard, mask)
+        means = self._buffer("means", 8 * nout)
         be.shard_combine_means(means, self._gather(sums, 8 * nout), self.comm.ranks, nout, count)
-        squares = be.storage(8 * nout)
-        be.var_partial(squares, shard, mask, means)
+        squares = self._buffer("squares", 8 * nout)
+        if empty:
+            self._fill(squares, F64, nout, 0.0)
+        else:
+            be.var_partial(squares, shard, mask, means)
         be.shard_combine_var(out, self._gather(squares, 8 * nout), self.comm.ranks, nout, count, correction, take_sqrt)
 
     def arg_reduce(self, values: Optional[TensorData], indices: TensorData, shard: TensorData, is_max: bool) -> None:
         """Index (global, along the sharded dimension 0) and optionally value of the maximum or minimum."""
+        self._need_every_block("argmax and argmin")
         be, nout = self.be, indices.numel
-        lv = be.empty(indices.shape, shard.dtype)
-        li = be.empty(indices.shape, I64)
+        if nout == 0:
+            return
+        vs, is_ = self._buffer("extreme", SIZE[shard.dtype] * nout), self._buffer("i64", 8 * nout)
+        lv = TensorData(vs, shard.dtype, tuple(indices.shape), tuple(contiguous_strides(indices.shape)))
+        li = TensorData(is_, I64, tuple(indices.shape), tuple(contiguous_strides(indices.shape)))
         be.arg_reduce(lv, li, shard, 0, is_max)
-        gv = self._gather(lv.storage, SIZE[shard.dtype] * nout)
-        gi = self._gather(li.storage, 8 * nout)
+        gv = self._gather(vs, SIZE[shard.dtype] * nout, "gathered values")
+        gi = self._gather(is_, 8 * nout, "gathered indices")
         be.shard_combine_extreme(is_max, values, indices, gv, shard.dtype, gi, self.offsets, self.comm.ranks, nout)
+
+    def sum_f64(self, out: TensorData, partials: Storage, n: int) -> None:
+        """out (a contiguous F64 scalar) = the sum over all ranks of this rank's `n` f64 `partials`: the partials
+        are folded in their order on each rank, the ranks' sums in rank order. What a gradient norm over sharded
+        parameters needs (hmc_adamw_step_many leaves one partial per tensor): one all-gather of 8 bytes per rank."""
+        assert out.dtype == F64 and out.numel == 1
+        be = self.be
+        local = self._buffer("f64", 8)
+        if n == 0:
+            self._fill(local, F64, 1, 0.0)
+        else:
+            be.reduce_partial(ffi.HMC_REDUCE_SUM, local, TensorData(partials, F64, (n,), (1,)), [True])
+        be.shard_combine_float(ffi.HMC_REDUCE_SUM, out, self._gather(local, 8), self.comm.ranks, 1, n * self.comm.ranks)

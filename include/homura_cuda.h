@@ -402,6 +402,30 @@ hmc_status hmc_adamw_step(hmc_context_t ctx, const hmc_tensor_desc *param,
                           const hmc_tensor_desc *grad, const hmc_tensor_desc *exp_avg,
                           const hmc_tensor_desc *exp_avg_sq, const hmc_adamw_scalars *scalars);
 
+/* The same update for all tensors of a parameter group (one set of scalars) in one launch, for
+ * optimizers that step hundreds of tensors, some of a few hundred elements: homura's loop over the
+ * parameters (src/optim/adam.rs:125-171) issues the per-parameter sequence once per tensor. Each entry
+ * names four contiguous tensors of n elements of `dtype`; tensors that are views with other strides go
+ * through hmc_adamw_step, which gives the same bits (the update must not depend on the layout,
+ * tests/optim.rs:430-480). With grad_sq non-null (device memory, `count` doubles) the call also leaves,
+ * per tensor, the f64 sum of the squares of its gradient, each square rounded to `dtype` first: what
+ * `g.mul(&g).sum()` accumulates before its final rounding, for a gradient norm; the sums are the same on
+ * every run. The table is read during the call only. The workspace (device memory, 256-byte aligned,
+ * hmc_adamw_step_many_workspace bytes) is used by the kernels of this call; a later call on the same
+ * context may reuse it. */
+typedef struct hmc_adamw_tensor {
+    void *param;
+    const void *grad;
+    void *exp_avg;
+    void *exp_avg_sq;
+    int64_t n;
+} hmc_adamw_tensor;
+hmc_status hmc_adamw_step_many_workspace(int32_t dtype, const hmc_adamw_tensor *tensors, int64_t count,
+                                         int32_t with_grad_sq, int64_t *bytes);
+hmc_status hmc_adamw_step_many(hmc_context_t ctx, int32_t dtype, const hmc_adamw_tensor *tensors,
+                               int64_t count, const hmc_adamw_scalars *scalars, double *grad_sq,
+                               void *workspace, int64_t workspace_bytes);
+
 /* Pinned host memory for transfers that should run at link speed. */
 hmc_status hmc_host_alloc(uint64_t nbytes, void **out);
 hmc_status hmc_host_free(void *ptr);

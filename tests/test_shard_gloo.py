@@ -89,6 +89,45 @@ def _worker(rank, world, port, results):
                 wv, wi = whole.max_dim(0) if is_max else whole.min_dim(0)
                 assert_bitwise(be.download(i), wi.raw(), I64, "global indices")
                 assert_bitwise(be.download(v), wv.raw(), dt, "values")
+        # more ranks than rows: rank 1 holds an empty block. Sums, products, means, variances, all / any take the
+        # identity from it; max / min / argmax are refused on every rank before anything is exchanged.
+        from homura_b200.host import BackendError, F64, TensorData
+        one_row = rng.standard_normal((1, cols)).astype(np.float32)
+        blocks = split_rows(1, world)
+        assert blocks[1] == (1, 0)
+        start, length = blocks[rank]
+        red = ShardedReducer(be, GlooComm(world, rank), [b[0] for b in blocks], 1)
+        whole, shard = T(be, be.upload(one_row, F32)), be.upload(one_row[start:start + length], F32)
+        for name, op in (("sum", ffi.HMC_REDUCE_SUM), ("prod", ffi.HMC_REDUCE_PROD), ("mean", ffi.HMC_REDUCE_MEAN)):
+            out = be.empty((cols,), F32)
+            red.reduce(op, out, shard, [True, False])
+            assert_bitwise(be.download(out), whole._red(name, [0]).raw(), F32, f"{name} with an empty block")
+        for name, op in (("all", ffi.HMC_REDUCE_ALL), ("any", ffi.HMC_REDUCE_ANY)):
+            out = be.empty((cols,), BOOL)
+            red.reduce(op, out, shard, [True, False])
+            assert_bitwise(be.download(out), whole._red(name, [0]).raw(), BOOL, f"{name} with an empty block")
+        ishard = be.upload(np.arange(cols, dtype=np.int32).reshape(1, cols)[start:start + length], I32)
+        out = be.empty((), I64)
+        red.reduce(ffi.HMC_REDUCE_SUM, out, ishard, [True, True])
+        assert int(be.download(out)) == cols * (cols - 1) // 2
+        out = be.empty((cols,), F32)
+        red.var(out, shard, [True, False], 0, False)
+        assert (be.download(out) == 0).all()
+        for refused in (lambda: red.reduce(ffi.HMC_REDUCE_MAX, be.empty((cols,), F32), shard, [True, False]),
+                        lambda: red.reduce(ffi.HMC_REDUCE_MIN, be.empty((), F32), shard, [True, True]),
+                        lambda: red.arg_reduce(be.empty((cols,), F32), be.empty((cols,), I64), shard, True)):
+            try:
+                refused()
+                raise AssertionError("an empty block was accepted")
+            except BackendError as e:
+                assert e.status == ffi.HMC_INVALID and "nonempty block on every rank" in str(e)
+        # the ranks' f64 partials (one per tensor of an optimizer step) folded in order, then in rank order
+        parts = np.array([0.5, 1e-30, 3.0, -1.25][: 4 - rank], dtype=np.float64)  # 4 partials on rank 0, 3 on rank 1
+        store = be.upload(parts, F64).storage
+        total = be.empty((), F64)
+        red.sum_f64(total, store, parts.size)
+        want = (0.5 + 1e-30 + 3.0 - 1.25) + (0.5 + 1e-30 + 3.0)
+        assert float(be.download(total)) == want
         results[rank] = "ok"
     except BaseException as e:  # report to the parent instead of dying silently
         import traceback
