@@ -12,7 +12,10 @@ Algorithmic bytes per step (distinct input elements + output elements, temporari
 silu 4N, mul 4N, promoting add 6N (twice), cast 6N, with N = 8192^2: 34 N = 2281.7 MB.
 
 The same run adds, under `workloads`, one record per other configuration, each kernel timed alone with L2 flushed
-before it (a "whole step" of reductions over one input would be served from L2 and is not reported):
+before it (a "whole step" of reductions over one input would be served from L2 and is not reported). The flush
+writes a 512 MB buffer and reads it back, so that the L2 holds unmodified lines when the timed kernel starts (after
+a write-only flush a read-only kernel is charged the write-back of the flush buffer; each record's `flush` entry
+shows the difference on its first kernel):
     c3  reductions of f32 / i32 [16384, 4096] (sum, mean, var over rows and columns, max + argmax, full sums)
     c4  softmax / log_softmax of causally masked f32 [8, 32, 2048, 2048], row mean of squares of bf16 [32768, 4096]
     c5  one GPU's eighth of the sharded configuration: a * b + c on flat f32 2^29, its sum and maximum, and an
@@ -179,11 +182,13 @@ class Workload:
 def _tile_fill(be, big, small):
     """Fills the contiguous `big` with repetitions of the contiguous `small` (a device-side broadcast copy)."""
     n = small.numel
-    reps = big.numel // n
-    be.copy(big.reshape(reps, n), small.reshape(1, n).expand(reps, n))
-    rest = big.numel - reps * n
+    flat = big.reshape(big.numel)
+    reps = flat.numel // n
+    if reps:
+        be.copy(flat.narrow(0, 0, reps * n).reshape(reps, n), small.reshape(1, n).expand(reps, n))
+    rest = flat.numel - reps * n
     if rest:
-        be.copy(big.reshape(big.numel).narrow(0, reps * n, rest), small.reshape(n).narrow(0, 0, rest))
+        be.copy(flat.narrow(0, reps * n, rest), small.reshape(n).narrow(0, 0, rest))
 
 
 class C3Workload:
@@ -459,6 +464,7 @@ class Runner:
         self.be, self.dist, self.local, self.world = be, dist, local, world
         self.ev = Events(be)
         self.scratch = None
+        self.scratch_sum = None
 
     def barrier(self):
         self.be.synchronize()
@@ -494,17 +500,31 @@ class Runner:
         self.ev.destroy(stop)
         return self.max_over_ranks(out)
 
-    def flushed_per_op(self, ops, reps: int = 10, warm: int = 3) -> dict:
-        """Mean ms of each op alone, a 512 MB buffer written before every launch so that nothing is served from L2."""
-        be, ev = self.be, self.ev
+    def flush(self, i: int = 0, read_back: bool = True) -> None:
+        """Empties the L2 of anything the next kernel could hit: 512 MB (four times the L2) are written, then read
+        back. The read matters for what is timed next: after a write alone the L2 is full of modified lines, and a
+        kernel that only reads then pays, in its own time, for writing up to 126 MB of the flush buffer back to HBM
+        (measured here: +13 us on a 268 MB read, which caps it near 4.8 TB/s). After the read the L2 holds the same
+        lines unmodified, and evicting them costs nothing."""
+        from homura_b200 import ffi
+        from homura_b200.host import I64, U8, TensorData
+        be = self.be
         if self.scratch is None:
             self.scratch = be.storage(512 << 20)
+            self.scratch_sum = be.empty((), I64)
+        be._check(be.lib.hmc_memset(be.ctx, self.scratch.ptr, i & 0xFF, self.scratch.nbytes))
+        if read_back:
+            be.reduce(ffi.HMC_REDUCE_SUM, self.scratch_sum, TensorData(self.scratch, U8, (self.scratch.nbytes,), (1,)), [True])
+
+    def flushed_per_op(self, ops, reps: int = 10, warm: int = 3, read_back: bool = True) -> dict:
+        """Mean ms of each op alone, the L2 emptied before every launch (see flush)."""
+        ev = self.ev
         per_op = {}
         a, b = ev.new(), ev.new()
         for name, f in ops:
             times = []
             for i in range(warm + reps):
-                be._check(be.lib.hmc_memset(be.ctx, self.scratch.ptr, i & 0xFF, self.scratch.nbytes))
+                self.flush(i, read_back)
                 ev.record(a)
                 f()
                 ev.record(b)
@@ -543,7 +563,13 @@ def workload_record(runner: Runner, w, steps: int, warmup: int) -> dict:
     flushed_ms = sum(per_op.values())
     r = roofline_of(w, per_op)
     back_ms = float(np.median(regions)) / steps
-    return {"workload": w.name, "dtype": w.dtype, "metric": METRIC, "unit": UNIT,
+    # what the flush's read-back is worth: the first op again after a flush that only writes
+    first = w.ops()[:1]
+    write_only = runner.max_over_ranks(runner.flushed_per_op(first, read_back=False).values())[0]
+    flush_note = {"op": first[0][0], "ms_after_write_then_read_flush": per_op[first[0][0]], "ms_after_write_only_flush": write_only,
+                  "note": "a flush that only writes leaves the L2 full of modified lines whose write-back is then charged to the "
+                          "timed kernel; the figures of this record are taken after a flush that writes and reads back"}
+    return {"workload": w.name, "dtype": w.dtype, "metric": METRIC, "unit": UNIT, "flush": flush_note,
             "value": step_bytes / (flushed_ms * 1e-3) / 1e9, "ms_per_step": flushed_ms,
             "value_basis": "sum of the kernels' times, each alone with L2 flushed before it",
             "back_to_back": {"value": step_bytes / (back_ms * 1e-3) / 1e9, "ms_per_step": back_ms,

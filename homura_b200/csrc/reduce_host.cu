@@ -65,15 +65,6 @@ ReducePlan make_reduce_plan(const hmc_tensor_desc &kept, const hmc_tensor_desc &
     return p;
 }
 
-namespace {
-
-// The 16-byte aligned size of the f64 means var keeps between its two passes when it cannot do
-// both in one kernel.
-int64_t means_bytes(const ReducePlan &p, bool var) {
-    const bool one_kernel = p.kind == 0 && p.splits == 1;
-    return var && !one_kernel ? (p.nout * 8 + 15) / 16 * 16 : 0;
-}
-
 hmc_status check_reduction(const hmc_tensor_desc *kept, const hmc_tensor_desc *red) {
     hmc_status s = check_desc(kept, "the kept dimensions");
     if (s != HMC_OK) return s;
@@ -103,6 +94,15 @@ hmc_status check_output(const hmc_tensor_desc *out, const hmc_tensor_desc *kept,
     }
     if (nout > 0 && out->data == nullptr) return fail(HMC_INVALID, "null data pointer");
     return HMC_OK;
+}
+
+namespace {
+
+// The 16-byte aligned size of the f64 means var keeps between its two passes when it cannot do
+// both in one kernel.
+int64_t means_bytes(const ReducePlan &p, bool var) {
+    const bool one_kernel = p.kind == 0 && p.splits == 1;
+    return var && !one_kernel ? (p.nout * 8 + 15) / 16 * 16 : 0;
 }
 
 hmc_status take_workspace(ReduceArgs &a, bool var, void *workspace, int64_t bytes, double **means) {

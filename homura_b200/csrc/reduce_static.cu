@@ -20,9 +20,13 @@
 //    is written by the same call's first kernel before the second kernel reads it, so nothing has to
 //    start at zero and nothing is cleared.
 //
-// The device address of the array is looked up the first time the entry point runs on a device, with that
-// device current; so the first call per device does a little more work than later ones and should be
-// made before a stream capture is begun on that device.
+// The device address of the array is looked up once per device, with that device current: when a context is
+// created on the device (hmc_context_create does it, so that the runtime loads the module holding the array
+// while memory is still plentiful), or else by the first call of this entry point there, which should then be
+// made before a stream capture is begun on that device. "Allocates nothing" describes a call whose code is
+// already resident: unless the process runs with CUDA_MODULE_LOADING=EAGER the runtime loads each kernel the
+// first time it is launched, which takes device memory, so a caller that must not allocate later makes one
+// call per (op, dtype, layout class) it will need at start-up.
 #include <mutex>
 
 #include "map.cuh"
@@ -39,37 +43,27 @@ static __device__ __align__(256) unsigned char noalloc_scratch[kScratchBytes];
 std::mutex address_mutex;
 void *scratch_address[kMaxDevices] = {};
 
-// The device address of the scratch array on `device`, which is the calling thread's current device.
-hmc_status scratch_on(int device, void **out) {
-    if (device < 0 || device >= kMaxDevices) return hmc::fail(HMC_INVALID, "device index beyond the scratch table");
+}  // namespace
+
+namespace hmc {
+
+hmc_status noalloc_scratch_on(int device, void **out) {
+    if (device < 0 || device >= kMaxDevices) return fail(HMC_INVALID, "device index beyond the scratch table");
     std::lock_guard<std::mutex> lock(address_mutex);
     if (scratch_address[device] == nullptr) {
         void *ptr = nullptr;
         cudaError_t err = cudaGetSymbolAddress(&ptr, noalloc_scratch);
-        if (err != cudaSuccess) return hmc::cuda_fail(err, "cudaGetSymbolAddress");
+        if (err != cudaSuccess) return cuda_fail(err, "cudaGetSymbolAddress");
         if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255) != 0) {
-            return hmc::fail(HMC_INTERNAL_ERROR, "the scratch array has no usable device address");
+            return fail(HMC_INTERNAL_ERROR, "the scratch array has no usable device address");
         }
         scratch_address[device] = ptr;
     }
-    *out = scratch_address[device];
+    if (out != nullptr) *out = scratch_address[device];
     return HMC_OK;
 }
 
-hmc_status check_contiguous_output(const hmc_tensor_desc *out, int64_t nout) {
-    hmc_status s = hmc::check_desc(out, "the output");
-    if (s != HMC_OK) return s;
-    if (hmc::desc_count(*out) != nout) return hmc::fail(HMC_INVALID, "the output does not have one element per kept position");
-    int64_t expect = 1;
-    for (int k = out->ndim - 1; k >= 0; --k) {
-        if (out->sizes[k] != 1 && out->strides[k] != expect) return hmc::fail(HMC_INVALID, "the output is not contiguous");
-        expect *= out->sizes[k];
-    }
-    if (nout > 0 && out->data == nullptr) return hmc::fail(HMC_INVALID, "null data pointer");
-    return HMC_OK;
-}
-
-}  // namespace
+}  // namespace hmc
 
 using namespace hmc;
 
@@ -77,14 +71,11 @@ HMC_API hmc_status hmc_reduce_noalloc(hmc_context_t ctx, int32_t op, const hmc_t
                                       const hmc_tensor_desc *kept, const hmc_tensor_desc *red) {
     return guarded([&]() -> hmc_status {
         HMC_ENTER(ctx);
-        hmc_status s = check_desc(kept, "the kept dimensions");
+        hmc_status s = check_reduction(kept, red);
         if (s != HMC_OK) return s;
-        s = check_desc(red, "the reduced dimensions");
-        if (s != HMC_OK) return s;
-        if (red->dtype != kept->dtype) return fail(HMC_INVALID, "kept and reduced descriptions differ in dtype");
         if (op < HMC_REDUCE_SUM || op > HMC_REDUCE_ANY) return fail(HMC_INVALID, "unknown reduction");
         ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr};
-        s = check_contiguous_output(out, a.plan.nout);
+        s = check_output(out, kept, "the output", a.plan.nout);
         if (s != HMC_OK) return s;
         const int dt = kept->dtype;
         const bool is_float = dtype_is_float(dt);
@@ -106,7 +97,7 @@ HMC_API hmc_status hmc_reduce_noalloc(hmc_context_t ctx, int32_t op, const hmc_t
         }
         if (need > 0) {
             void *scratch = nullptr;
-            s = scratch_on(ctx->device, &scratch);
+            s = noalloc_scratch_on(ctx->device, &scratch);
             if (s != HMC_OK) return s;
             a.partials = scratch;
         }

@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "reduce.cuh"
 
 namespace hmc {
 
@@ -189,6 +190,10 @@ HMC_API hmc_status hmc_context_create(int32_t device, hmc_context_t *out) {
         if (err != cudaSuccess) return abandon(cuda_fail(err, "probe kernel"));
         if (free_err != cudaSuccess) return abandon(cuda_fail(free_err, "probe: cudaFree"));
         if (answer != kProbeWord) return abandon(fail(HMC_CUDA_ERROR, "probe kernel wrote the wrong value"));
+        // The scratch array of hmc_reduce_noalloc: looking up its address now makes the runtime load the module
+        // that holds it while this call is allocating anyway. A failure here is not the context's: the entry point
+        // looks the address up again when it is first used.
+        if (noalloc_scratch_on(device, nullptr) != HMC_OK) t.message.clear();
         hmc_context *ctx = nullptr;
         if (t.fail_after_probe > 0) {
             t.fail_after_probe -= 1;

@@ -11,6 +11,9 @@
 // exp is skipped for x - max = -inf (a masked logit), whose result is exactly +0.
 #include <math_constants.h>
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "map.cuh"
 #include "math.cuh"
 #include "reduce.cuh"
@@ -145,6 +148,13 @@ __device__ __forceinline__ double exp_shifted(double d) {
     if constexpr (std::is_same_v<T, double>) return exp(d);
     else return exp_lite(d);
 }
+
+// f64 -> T with the hardware's round-to-nearest conversion (through f32 for the half types, as the CPU does);
+// a NaN comes out as the hardware's canonical NaN, which no softmax result is compared on.
+template <class T> __device__ __forceinline__ T round_f64(double v);
+template <> __device__ __forceinline__ float round_f64<float>(double v) { return __double2float_rn(v); }
+template <> __device__ __forceinline__ F16 round_f64<F16>(double v) { return down<F16>(__double2float_rn(v)); }
+template <> __device__ __forceinline__ BF16 round_f64<BF16>(double v) { return down<BF16>(__double2float_rn(v)); }
 
 // Rows are handled one after the other inside a block (load, max, exp, sum, store are dependent phases), so
 // throughput is rows in flight per SM: the register budget keeps three blocks resident while a lane caches up
@@ -376,6 +386,218 @@ __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_ker
     }
 }
 
+
+// ---- rows staged in shared memory, a warp per row ----
+//
+// For F16, BF16 and F32 rows of whole, aligned vectors (the attention-logit case). The kernel above keeps a row
+// in registers, so the bytes a block has in flight are bounded by its registers and the phases of a row (load,
+// maximum, exponentials, sum, store) leave the memory system idle in between. Here a warp owns a row and a ring
+// of two row buffers in shared memory: while it computes one row from its buffer, the next row is on its way
+// from HBM into the other one by asynchronous copies (cp.async, 16 bytes per lane and copy), which need no
+// registers. Vector v of a row belongs to lane v mod 32, for the copy and for every pass, so a lane only ever
+// reads what it copied itself: cp.async.wait_group is all the synchronisation there is, no barrier. A row is
+// read from HBM once and written once.
+//
+// The maths is the CPU's in f64 (src/backend/cpu/misc.rs:15-51): the maximum is exact in f32; exp(x - max) is
+// 2^(k/32) from a table times a cubic in the remainder (relative error below 2^-35, for results that are rounded
+// to 24 bits or fewer), nine f64 operations; the sum is added per lane in vector order and folded over the lanes
+// by a butterfly. For softmax the exponentials are evaluated a second time for the output instead of being kept
+// (64 of them per lane for a row of 2048 would cost 128 registers); a second evaluation gives the same bits. An
+// element more than 200 below the maximum is moved up to there (its exponential, below 1e-86, rounds to 0 in the
+// output and vanishes in the sum), which keeps 2^k a normal number; a vector that lies entirely below, such as the
+// masked half of causal logits, is skipped and stored as zeros.
+struct RowExp {
+    double c, mc;  // t = x * c + mc = (x - max) * 32 / ln 2
+    __device__ __forceinline__ double operator()(float x, const uint64_t *table) const {
+        const double t = __fma_rn(static_cast<double>(x), c, mc);
+        const double shift = 0x1.8p+52;
+        double kd = t + shift;
+        const uint32_t ki = static_cast<uint32_t>(__double2loint(kd));
+        kd -= shift;
+        const double r = t - kd;
+        const uint64_t entry = table[ki & 31u];
+        const double s = __hiloint2double(static_cast<int>(static_cast<uint32_t>(entry >> 32) + (ki << 15)),
+                                          static_cast<int>(static_cast<uint32_t>(entry)));
+        const double q = __fma_rn(0x1.c6af84b912394p-5 / 32768.0, r, 0x1.ebfce50fac4f3p-3 / 1024.0);
+        const double r2 = r * r;
+        double y = __fma_rn(0x1.62e42ff0c52d6p-1 / 32.0, r, 1.0);
+        y = __fma_rn(q, r2, y);
+        return y * s;
+    }
+};
+
+// CU vectors of a lane (vectors lane + 32 * (c0 + u), u = 0..CU-1: sixteen elements) as f32 values; vectors beyond
+// the row read as -inf. Returns the largest value, NaN if one of them is a NaN.
+template <class T, int VEC, int CU>
+__device__ __forceinline__ float load_chunk(const RVec<T, VEC> *row, int lane, int c0, int nvec, float (&xf)[CU][VEC]) {
+    float top = -CUDART_INF_F;
+#pragma unroll
+    for (int u = 0; u < CU; ++u) {
+        const int v = lane + 32 * (c0 + u);
+        if (v < nvec) {
+            const RVec<T, VEC> x = row[v];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                xf[u][e] = up(x.v[e]);
+                top = max_keep_nan(top, xf[u][e]);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) xf[u][e] = -CUDART_INF_F;
+        }
+    }
+    return top;
+}
+
+template <class T, bool LOG>
+__global__ void __launch_bounds__(kRThreads, 1) softmax_staged_kernel(const __grid_constant__ SoftmaxArgs a, const int row_bytes) {
+    constexpr int VEC = 16 / sizeof(T);
+    constexpr int CU = 16 / VEC;  // vectors per chunk: sixteen elements
+    extern __shared__ __align__(16) unsigned char staged[];
+    __shared__ uint64_t table[32];
+    if (threadIdx.x < 32) table[threadIdx.x] = lm::kExp2Table[threadIdx.x];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    unsigned char *ring = staged + static_cast<size_t>(warp) * 2 * row_bytes;
+    const int nvec = static_cast<int>(a.n / VEC);
+    const int per_lane = (nvec + 31) / 32;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * warps;
+    const T *src = static_cast<const T *>(a.src_rows.data) + a.src_rows.offset;
+    T *dst = static_cast<T *>(a.out_rows.data) + a.out_rows.offset;
+    auto fetch = [&](int64_t r, int stage) {
+        const T *ps = src + decompose(a.src_rows, r, a.src_rows.ndim);
+        unsigned char *buf = ring + static_cast<size_t>(stage) * row_bytes;
+        for (int v = lane; v < nvec; v += 32) async_copy_16(buf + 16 * v, ps + static_cast<size_t>(v) * VEC);
+    };
+    int64_t r = static_cast<int64_t>(blockIdx.x) * warps + warp;
+    if (r < a.nrows) fetch(r, 0);
+    async_copy_commit();
+    int stage = 0;
+    for (; r < a.nrows; r += stride, stage ^= 1) {
+        if (r + stride < a.nrows) fetch(r + stride, stage ^ 1);
+        async_copy_commit();
+        async_copy_wait(1);  // everything but the copies just issued has landed: this row is in its buffer
+        const RVec<T, VEC> *row = reinterpret_cast<const RVec<T, VEC> *>(ring + static_cast<size_t>(stage) * row_bytes);
+        T *po = dst + decompose(a.out_rows, r, a.out_rows.ndim);
+        // pass 1: the maximum (a NaN never wins; it reaches the sum below)
+        float mxf = -CUDART_INF_F;
+#pragma unroll 4
+        for (int v = lane; v < nvec; v += 32) {
+            const RVec<T, VEC> x = row[v];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) mxf = fmaxf(mxf, up(x.v[e]));
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) mxf = fmaxf(mxf, __shfl_xor_sync(0xFFFFFFFFu, mxf, d));
+        const float floor_x = mxf - 200.0f;
+        const double mx = static_cast<double>(mxf);
+        RowExp ex;
+        ex.c = 0x1.71547652b82fep+0 * 32.0;
+        ex.mc = -mx * ex.c;
+        // pass 2: the sum of the exponentials, sixteen independent evaluations at a time; a chunk that lies below
+        // the floor altogether adds nothing, an element below it inside a live chunk adds less than 1e-86
+        double sum = 0.0;
+        for (int c0 = 0; c0 < per_lane; c0 += CU) {
+            float xf[CU][VEC];
+            const float top = load_chunk<T, VEC, CU>(row, lane, c0, nvec, xf);
+            if (top < floor_x) continue;  // (false for a NaN)
+            double ev[CU][VEC];
+#pragma unroll
+            for (int u = 0; u < CU; ++u)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) ev[u][e] = ex(max_keep_nan(xf[u][e], floor_x), table);
+#pragma unroll
+            for (int u = 0; u < CU; ++u) {
+                // (a vector beyond the row holds -inf, whose clamped exponential is as good as zero; when the whole
+                // row is -inf the floor is -inf too and every exponential a NaN, as on the CPU)
+                double part = ev[u][0];
+#pragma unroll
+                for (int e = 1; e < VEC; ++e) part += ev[u][e];
+                sum += part;
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+        // pass 3: the outputs
+        if constexpr (LOG) {
+            const double log_sum = log(sum);
+#pragma unroll 4
+            for (int v = lane; v < nvec; v += 32) {
+                const RVec<T, VEC> x = row[v];
+                RVec<T, VEC> y;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) y.v[e] = round_f64<T>((static_cast<double>(up(x.v[e])) - mx) - log_sum);
+                *reinterpret_cast<RVec<T, VEC> *>(po + static_cast<size_t>(v) * VEC) = y;
+            }
+        } else {
+            const double inv = reciprocal_short(sum);
+            // what a skipped element gets: +0, or NaN when the row's sum is one
+            const T nothing = round_f64<T>(0.0 * inv);
+            for (int c0 = 0; c0 < per_lane; c0 += CU) {
+                float xf[CU][VEC];
+                const float top = load_chunk<T, VEC, CU>(row, lane, c0, nvec, xf);
+                RVec<T, VEC> y[CU];
+                if (top < floor_x) {
+#pragma unroll
+                    for (int u = 0; u < CU; ++u)
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) y[u].v[e] = nothing;
+                } else {
+#pragma unroll
+                    for (int u = 0; u < CU; ++u)
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) y[u].v[e] = round_f64<T>(ex(max_keep_nan(xf[u][e], floor_x), table) * inv);
+                }
+#pragma unroll
+                for (int u = 0; u < CU; ++u) {
+                    const int v = lane + 32 * (c0 + u);
+                    if (v < nvec) *reinterpret_cast<RVec<T, VEC> *>(po + static_cast<size_t>(v) * VEC) = y[u];
+                }
+            }
+        }
+    }
+    async_copy_wait(0);
+}
+
+// Whether the staged kernel takes these rows: unit stride inside a row, whole vectors, every row of source and
+// output starting on a 16-byte boundary, rows of 256 bytes to 48 KB.
+template <class T>
+bool staged_rows(const SoftmaxArgs &a) {
+    constexpr int VEC = 16 / sizeof(T);
+    if (a.si != 1 || a.so != 1 || a.n % VEC != 0) return false;
+    const int64_t bytes = a.n * static_cast<int64_t>(sizeof(T));
+    if (bytes < 256 || bytes > 48 * 1024) return false;
+    for (const hmc_tensor_desc *d : {&a.src_rows, &a.out_rows}) {
+        if ((reinterpret_cast<uintptr_t>(d->data) + static_cast<uintptr_t>(d->offset) * sizeof(T)) % 16 != 0) return false;
+        for (int k = 0; k < d->ndim; ++k)
+            if (d->sizes[k] > 1 && d->strides[k] % VEC != 0) return false;
+    }
+    return true;
+}
+
+template <class T>
+hmc_status launch_softmax_staged(hmc_context_t ctx, const SoftmaxArgs &a, bool log) {
+    const int row_bytes = static_cast<int>(a.n * sizeof(T));
+    // as many warps per block as two row buffers each allow within ~96 KB, so that two blocks share an SM
+    int warps = 8;
+    int budget = 96 * 1024;
+    if (const char *e = std::getenv("HMC_TUNE_SOFTMAX_BUDGET")) budget = std::atoi(e);
+    while (warps > 1 && static_cast<int64_t>(warps) * 2 * row_bytes > budget) warps >>= 1;
+    if (const char *e = std::getenv("HMC_TUNE_SOFTMAX_WARPS")) warps = std::atoi(e);
+    const size_t shared = static_cast<size_t>(warps) * 2 * row_bytes;
+    int per_sm = std::max<int>(1, std::min<int>(8, static_cast<int>((220 * 1024) / (shared + 1024))));
+    if (const char *e = std::getenv("HMC_TUNE_SOFTMAX_PER_SM")) per_sm = std::atoi(e);
+    const int64_t blocks_needed = ceil_div(a.nrows, warps);
+    const unsigned grid = clamp_grid(blocks_needed, static_cast<int64_t>(ctx->sm_count) * per_sm);
+    auto kernel = log ? softmax_staged_kernel<T, true> : softmax_staged_kernel<T, false>;
+    if (shared > 48 * 1024) {
+        HMC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)),
+                 "shared memory size of the softmax kernel");
+    }
+    kernel<<<grid, warps * 32, shared, ctx->stream>>>(a, row_bytes);
+    return launch_status("softmax kernel launch");
+}
+
 template <class T, int G, int CV>
 hmc_status launch_softmax_cv(hmc_context_t ctx, const SoftmaxArgs &a, bool log) {
     constexpr int P = kRThreads / G;
@@ -442,6 +664,20 @@ HMC_API hmc_status hmc_test_softmax_plan(const hmc_tensor_desc *src_rows, int64_
         *kind = p.kind;
         *group = p.group;
         *cache = p.cache;
+        if (src_rows->dtype != HMC_F64) {
+            // the plan for rows like these when the output has the same layout: a warp per row, staged in shared memory
+            SoftmaxArgs a{*src_rows, *src_rows, 1, n, src_stride, src_stride};
+            const bool staged = dispatch_float(src_rows->dtype, [&](auto t) -> hmc_status {
+                using T = decltype(t);
+                if constexpr (std::is_same_v<T, double>) return HMC_INVALID;
+                else return staged_rows<T>(a) ? HMC_OK : HMC_INVALID;
+            }) == HMC_OK;
+            if (staged) {
+                *kind = 2;
+                *group = 32;
+                *cache = 0;
+            }
+        }
         return HMC_OK;
     });
 }
@@ -465,6 +701,9 @@ HMC_API hmc_status hmc_softmax(hmc_context_t ctx, const hmc_tensor_desc *out_row
         const SoftmaxPlan p = softmax_plan(src_rows->dtype, n);
         return dispatch_float(src_rows->dtype, [&](auto t) -> hmc_status {
             using T = decltype(t);
+            if constexpr (!std::is_same_v<T, double>) {
+                if (staged_rows<T>(a)) return launch_softmax_staged<T>(ctx, a, log != 0);
+            }
             if (p.group == 32) return launch_softmax_g<T, 32>(ctx, a, p, log != 0);
             if (p.group == 128) return launch_softmax_g<T, 128>(ctx, a, p, log != 0);
             return launch_softmax_g<T, 256>(ctx, a, p, log != 0);

@@ -368,8 +368,13 @@ hmc_status hmc_mask_coordinates(hmc_context_t ctx, const hmc_tensor_desc *mask, 
  * HMC_NOALLOC_SCRATCH_BYTES built into the library's device image (held on every GPU that loads the
  * library until the process exits); a reduction whose plan needs more is refused with HMC_INVALID.
  * Same results, bit for bit, as hmc_reduce. The entry point allocates nothing. All calls share the one
- * array: calls that overlap on a GPU race, calls on one context are ordered by its stream. The first
- * call on a device also looks up the array's device address; make it before any stream capture. */
+ * array: calls that overlap on a GPU race, calls on one context are ordered by its stream. The array's
+ * device address is looked up when a context is created on the device (which makes the runtime load the
+ * module that holds the array then, not under memory pressure later), else by the first call on that
+ * device, which should then come before any stream capture. The runtime loads a kernel's code the first
+ * time it is launched unless the process runs with CUDA_MODULE_LOADING=EAGER, and that takes device
+ * memory: a caller that must not allocate later makes one call per (op, dtype, layout class) it will
+ * need while starting up; from then on a call leaves the device's free memory unchanged. */
 #define HMC_NOALLOC_SCRATCH_BYTES 1048576
 hmc_status hmc_reduce_noalloc(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
                               const hmc_tensor_desc *kept, const hmc_tensor_desc *red);
@@ -470,7 +475,8 @@ void hmc_abi_check(hmc_abi_info *out);
  * fail_data(n, oom): the next n data operations fail before queueing anything.
  * reduce_plan / softmax_plan: which plan the library picks, so tests can reach every path.
  *   reduce: kind (0 rows, 1 columns, 2 generic), splits of the reduced range, elements per split.
- *   softmax: kind (0 row in registers, 1 streaming), lanes per row, elements a lane keeps.
+ *   softmax: kind (0 row in registers, 1 streaming, 2 row staged in shared memory by a warp), lanes per
+ *   row, vectors a lane keeps.
  * live_streams: streams the thread created and has not destroyed. */
 void hmc_test_fail_stream_create(int32_t n);
 void hmc_test_fail_after_probe(int32_t n);

@@ -1,18 +1,21 @@
 """Builds the CPU checker: ``oracle/oracle.cpp`` -> ``oracle/_build/liboracle.so`` (g++ -O2, no fast-math,
 no contraction of a*b+c, so the arithmetic is that of homura's Rust CPU backend on x86-64), and, where
-homura's sources are mounted at ``/root/reference``, ``oracle/_ref/libref_casts.so``: homura's own C++
+homura's sources are present (the directory named by the environment variable ``HOMURA_SRC``),
+``oracle/_ref/libref_casts.so``: homura's own C++
 restatement of its casts (``csrc/elem.hpp``) compiled for the host from where it lies, used to cross-check
 the oracle's conversions. TEST INFRASTRUCTURE: nothing that ships may load these libraries.
 """
 from __future__ import annotations
 
+import os
 import subprocess
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 LIB = HERE / "_build" / "liboracle.so"
 REF_LIB = HERE / "_ref" / "libref_casts.so"
-REFERENCE = Path("/root/reference")
+# A checkout of homura, if there is one: HOMURA_SRC names it (README.md gives the default of the build machine).
+REFERENCE = Path(os.environ.get("HOMURA_SRC") or Path.home() / "reference")
 CXXFLAGS = ["-O2", "-std=c++17", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared", "-Wall", "-Wno-sign-compare",
             "-Wno-type-limits"]
 

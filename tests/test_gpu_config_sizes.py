@@ -103,9 +103,10 @@ def test_softmax_of_masked_logits_8x32x2048x2048_on_sampled_rows(oracle, cuda):
     soft, logsoft = cuda.empty((b, n, n), F32), cuda.empty((b, n, n), F32)
     cuda.softmax(soft, x, 2, False)
     cuda.softmax(logsoft, x, 2, True)
-    # 8192 rows: row k * 64 + (37 k mod 64), so every position of a row inside its causal matrix turns up
+    # 8192 rows, one in every 64: within its group of 64 the k-th row sits at (k div 32) mod 64, so every position of
+    # a row inside its causal matrix of 2048 rows turns up (four times)
     k = np.arange(8192, dtype=np.int64)
-    rows = k * 64 + (37 * k) % 64
+    rows = k * 64 + (k // 32) % 64
     assert len(set((rows % n).tolist())) == n
     index = cuda.upload(rows, I64)
     def sample(t):

@@ -179,6 +179,9 @@ def test_float_pow_and_scalars(oracle, cuda, dtype):
         fw = storage_to_f64(w, dtype)
         if dtype == F64:
             check_within(g, w, dtype, np.where(np.isfinite(fw), 4.0 * u * np.abs(fw), 0.0), f"pow {s}")
+        elif s == 2.0:
+            # the square is one multiplication on the GPU; the C library's powf(x, 2) is not always the nearest value
+            assert_ulp(g, w, dtype, 1, f"pow {s}")
         else:
             assert_bitwise(g, w, dtype, f"pow {s}")
     for name, o, g in pairs(oracle, cuda, dtype, 34):

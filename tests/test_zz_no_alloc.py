@@ -73,3 +73,46 @@ def test_a_reduction_beyond_the_built_in_scratch_is_refused(cuda):
     assert status == ffi.HMC_INVALID
     message = cuda.lib.hmc_last_error().decode()
     assert str(need.value) in message and str(ffi.HMC_NOALLOC_SCRATCH_BYTES) in message
+
+
+def test_a_warmed_call_leaves_the_free_device_memory_unchanged(cuda):
+    """Once the kernels of a reduction have run (the runtime loads a kernel's code at its first launch), further
+    calls of the entry point take nothing from the device: free memory as the driver reports it is the same
+    before and after, on the plans with and without partials."""
+    a = cuda.upload(normal(1 << 22, 303), F32)
+    r_full, r_rows = describe("reduce", a, [True]), describe("reduce", a.reshape(1 << 10, 1 << 12), [False, True])
+    out_full, out_rows = cuda.empty((), F32), cuda.empty((1 << 10,), F32)
+
+    def call():
+        cuda._check(cuda.lib.hmc_reduce_noalloc(cuda.ctx, ffi.HMC_REDUCE_SUM, output_desc("reduce", r_full, out_full), r_full.kept, r_full.red))
+        cuda._check(cuda.lib.hmc_reduce_noalloc(cuda.ctx, ffi.HMC_REDUCE_SUM, output_desc("reduce", r_rows, out_rows), r_rows.kept, r_rows.red))
+        cuda.synchronize()
+
+    def free_bytes():
+        free, total = ctypes.c_uint64(), ctypes.c_uint64()
+        cuda._check(cuda.lib.hmc_mem_get_info(cuda.device, ctypes.byref(free), ctypes.byref(total)))
+        return free.value
+
+    call()  # warm: module and kernels resident
+    before = free_bytes()
+    for _ in range(3):
+        call()
+    assert free_bytes() == before, "hmc_reduce_noalloc changed the device's free memory"
+
+
+def test_sizes_whose_product_overflows_are_refused(cuda):
+    k, r, o = ffi.hmc_tensor_desc(), ffi.hmc_tensor_desc(), ffi.hmc_tensor_desc()
+    dummy = cuda.empty((16,), U8)
+    for d, dt in ((k, U8), (r, U8), (o, I64)):
+        d.data, d.dtype, d.ndim = dummy.storage.ptr, dt, 1
+    k.ndim = 2
+    k.sizes[0], k.strides[0], k.sizes[1], k.strides[1] = 1 << 40, 0, 1 << 40, 0
+    r.sizes[0], r.strides[0] = 4, 1
+    o.sizes[0], o.strides[0] = 4, 1
+    assert cuda.lib.hmc_reduce_noalloc(cuda.ctx, ffi.HMC_REDUCE_SUM, ctypes.byref(o), ctypes.byref(k), ctypes.byref(r)) == ffi.HMC_INVALID
+    assert b"too many outputs" in cuda.lib.hmc_last_error()
+    k.ndim, k.sizes[0], k.strides[0] = 1, 4, 1
+    r.ndim = 2
+    r.sizes[0], r.strides[0], r.sizes[1], r.strides[1] = 1 << 40, 0, 1 << 40, 0
+    assert cuda.lib.hmc_reduce_noalloc(cuda.ctx, ffi.HMC_REDUCE_SUM, ctypes.byref(o), ctypes.byref(k), ctypes.byref(r)) == ffi.HMC_INVALID
+    assert b"too many reduced elements" in cuda.lib.hmc_last_error()
