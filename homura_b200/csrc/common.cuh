@@ -28,9 +28,21 @@ struct hmc_event {
 
 namespace hmc {
 
+// The calling thread's last error text, in storage that exists from the thread's first call: recording a
+// message never allocates, so it also works when the host heap is exhausted (texts beyond the capacity are cut).
+class Message {
+  public:
+    void assign(const char *text) noexcept { std::snprintf(text_, sizeof text_, "%s", text != nullptr ? text : ""); }
+    void clear() noexcept { text_[0] = '\0'; }
+    const char *c_str() const noexcept { return text_; }
+
+  private:
+    char text_[1024] = {};
+};
+
 // ---- per-thread state ----
 struct ThreadState {
-    std::string message;
+    Message message;
     int fail_stream_create = 0;
     int fail_after_probe = 0;
     int fail_properties = 0;
@@ -40,8 +52,9 @@ struct ThreadState {
 };
 ThreadState &thread_state();
 
-// Records `message` for the calling thread and returns `status`.
-hmc_status fail(hmc_status status, const std::string &message);
+// Records `message` for the calling thread and returns `status`. The form taking a C string allocates nothing.
+hmc_status fail(hmc_status status, const char *message) noexcept;
+hmc_status fail(hmc_status status, const std::string &message) noexcept;
 
 // Turns a CUDA error into a status (out of memory is its own status), records "<what>: <text>" and
 // clears the runtime's sticky last-error so that the failure does not resurface in a later,
@@ -54,25 +67,20 @@ hmc_status cuda_fail(cudaError_t err, const char *what);
         if (hmc_err_ != cudaSuccess) return ::hmc::cuda_fail(hmc_err_, what); \
     } while (0)
 
-// Runs `body` (returning hmc_status) so that no C++ exception reaches the caller.
+// Runs `body` (returning hmc_status) so that no C++ exception reaches the caller. The handlers allocate nothing
+// (the message store is fixed storage), so they cannot throw in turn when the host heap is exhausted.
 template <class Body>
 hmc_status guarded(Body &&body) noexcept {
     try {
         return body();
     } catch (const std::bad_alloc &) {
-        try {
-            return fail(HMC_OUT_OF_MEMORY, "out of host memory");
-        } catch (...) {
-            return HMC_OUT_OF_MEMORY;
-        }
+        return fail(HMC_OUT_OF_MEMORY, "out of host memory");
     } catch (const std::exception &e) {
-        try {
-            return fail(HMC_INTERNAL_ERROR, std::string("internal error: ") + e.what());
-        } catch (...) {
-            return HMC_INTERNAL_ERROR;
-        }
+        char text[512];
+        std::snprintf(text, sizeof text, "internal error: %s", e.what());
+        return fail(HMC_INTERNAL_ERROR, text);
     } catch (...) {
-        return HMC_INTERNAL_ERROR;
+        return fail(HMC_INTERNAL_ERROR, "internal error");
     }
 }
 
@@ -104,7 +112,24 @@ bool injected_data_failure(hmc_status &status);
         if (::hmc::injected_data_failure(hmc_inj_)) return hmc_inj_;               \
     }                                                                               \
     ::hmc::DeviceGuard hmc_guard_((ctx)->device);                                   \
-    if (hmc_guard_.status() != HMC_OK) return hmc_guard_.status()
+    if (hmc_guard_.status() != HMC_OK) return hmc_guard_.status();                  \
+    ::hmc::forget_earlier_error()
+
+// An error that the caller's own CUDA calls left as the thread's last error must not be taken for a failure of
+// the launch this entry is about to check: reading it clears it.
+inline void forget_earlier_error() { (void)cudaGetLastError(); }
+
+// A kernel launch. Host-only builds of the runtime files (the failure harness, which compiles them with g++
+// against a stand-in CUDA runtime) route it through that runtime instead of the <<<>>> syntax.
+#if defined(HMC_FAKE_CUDA)
+#define HMC_LAUNCH(kernel, grid, block, shared, stream, ...) ::fake::launch([&] { kernel(__VA_ARGS__); })
+#else
+#define HMC_LAUNCH(kernel, grid, block, shared, stream, ...) kernel<<<(grid), (block), (shared), (stream)>>>(__VA_ARGS__)
+#endif
+
+// Looks up, once per device, the device address of the scratch array hmc_reduce_noalloc uses, which also makes the
+// runtime load the module that holds it. `device` is the calling thread's current device.
+hmc_status noalloc_scratch_on(int device, void **out);
 
 // After a kernel launch: picks up a launch failure (and clears it).
 hmc_status launch_status(const char *what);

@@ -73,9 +73,7 @@ ReducePlan make_reduce_plan(const hmc_tensor_desc &kept, const hmc_tensor_desc &
 hmc_status check_reduction(const hmc_tensor_desc *kept, const hmc_tensor_desc *red);
 // `out` is a contiguous description of `nout` elements with a data pointer.
 hmc_status check_output(const hmc_tensor_desc *out, const hmc_tensor_desc *kept, const char *what, int64_t nout);
-// Looks up, once per device, the device address of the scratch array hmc_reduce_noalloc uses, which also makes the
-// runtime load the module that holds it. `device` is the calling thread's current device.
-hmc_status noalloc_scratch_on(int device, void **out);
+
 inline int64_t plan_partial_bytes(const ReducePlan &p) { return p.splits > 1 ? p.splits * p.nout * kPartialBytes : 0; }
 
 // ---- device helpers ----

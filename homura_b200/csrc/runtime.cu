@@ -4,7 +4,6 @@
 #include <cstring>
 
 #include "common.cuh"
-#include "reduce.cuh"
 
 namespace hmc {
 
@@ -13,15 +12,17 @@ ThreadState &thread_state() {
     return state;
 }
 
-hmc_status fail(hmc_status status, const std::string &message) {
-    thread_state().message = message;
+hmc_status fail(hmc_status status, const char *message) noexcept {
+    thread_state().message.assign(message);
     return status;
 }
+hmc_status fail(hmc_status status, const std::string &message) noexcept { return fail(status, message.c_str()); }
 
 hmc_status cuda_fail(cudaError_t err, const char *what) {
     // Reading the error clears the runtime's per-thread record of it.
     cudaGetLastError();
-    std::string text = std::string(what) + ": " + cudaGetErrorString(err);
+    char text[512];
+    std::snprintf(text, sizeof text, "%s: %s", what, cudaGetErrorString(err));
     bool oom = err == cudaErrorMemoryAllocation;
     return fail(oom ? HMC_OUT_OF_MEMORY : HMC_CUDA_ERROR, text);
 }
@@ -171,18 +172,19 @@ HMC_API hmc_status hmc_context_create(int32_t device, hmc_context_t *out) {
         HMC_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreateWithFlags");
         t.live_streams += 1;
         // Everything below must destroy the stream before failing.
+        // (the failure's message is already recorded and survives: the clean-up records nothing. A stream the
+        // runtime refuses to destroy stays counted.)
         auto abandon = [&](hmc_status status) {
-            std::string keep = t.message;
-            if (cudaStreamDestroy(stream) != cudaSuccess) cudaGetLastError();
-            t.live_streams -= 1;
-            t.message = keep;
+            if (cudaStreamDestroy(stream) == cudaSuccess) t.live_streams -= 1;
+            else cudaGetLastError();
             return status;
         };
         uint32_t *slot = nullptr;
         cudaError_t err = cudaMalloc(&slot, sizeof(uint32_t));
         if (err != cudaSuccess) return abandon(cuda_fail(err, "probe: cudaMalloc"));
         uint32_t answer = 0;
-        probe_kernel<<<1, 1, 0, stream>>>(slot);
+        forget_earlier_error();
+        HMC_LAUNCH(probe_kernel, 1, 1, 0, stream, slot);
         err = cudaGetLastError();
         if (err == cudaSuccess) err = cudaMemcpyAsync(&answer, slot, sizeof answer, cudaMemcpyDeviceToHost, stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
@@ -212,7 +214,7 @@ HMC_API hmc_status hmc_context_destroy(hmc_context_t ctx) {
         DeviceGuard guard(ctx->device);
         if (guard.status() != HMC_OK) return guard.status();
         cudaError_t err = cudaStreamDestroy(ctx->stream);
-        thread_state().live_streams -= 1;
+        if (err == cudaSuccess) thread_state().live_streams -= 1;
         delete ctx;
         if (err != cudaSuccess) return cuda_fail(err, "cudaStreamDestroy");
         return HMC_OK;

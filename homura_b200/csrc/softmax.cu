@@ -400,16 +400,18 @@ __global__ void __launch_bounds__(kRThreads, softmax_min_blocks(CV)) softmax_ker
 //
 // The maths is the CPU's in f64 (src/backend/cpu/misc.rs:15-51): the maximum is exact in f32; exp(x - max) is
 // 2^(k/32) from a table times a cubic in the remainder (relative error below 2^-35, for results that are rounded
-// to 24 bits or fewer), nine f64 operations; the sum is added per lane in vector order and folded over the lanes
+// to 24 bits or fewer), ten f64 operations; the sum is added per lane in vector order and folded over the lanes
 // by a butterfly. For softmax the exponentials are evaluated a second time for the output instead of being kept
 // (64 of them per lane for a row of 2048 would cost 128 registers); a second evaluation gives the same bits. An
 // element more than 200 below the maximum is moved up to there (its exponential, below 1e-86, rounds to 0 in the
 // output and vanishes in the sum), which keeps 2^k a normal number; a vector that lies entirely below, such as the
 // masked half of causal logits, is skipped and stored as zeros.
 struct RowExp {
-    double c, mc;  // t = x * c + mc = (x - max) * 32 / ln 2
+    double mx;  // the row's maximum
+    // exp(x - mx). The difference is taken first, in f64 (exact whenever it matters: the maximum itself gives 0 and
+    // its exponential exactly 1, as on the CPU, which a row with a single live element shows in log_softmax).
     __device__ __forceinline__ double operator()(float x, const uint64_t *table) const {
-        const double t = __fma_rn(static_cast<double>(x), c, mc);
+        const double t = (static_cast<double>(x) - mx) * (0x1.71547652b82fep+0 * 32.0);
         const double shift = 0x1.8p+52;
         double kd = t + shift;
         const uint32_t ki = static_cast<uint32_t>(__double2loint(kd));
@@ -491,9 +493,7 @@ __global__ void __launch_bounds__(kRThreads, 1) softmax_staged_kernel(const __gr
         for (int d = 16; d > 0; d >>= 1) mxf = fmaxf(mxf, __shfl_xor_sync(0xFFFFFFFFu, mxf, d));
         const float floor_x = mxf - 200.0f;
         const double mx = static_cast<double>(mxf);
-        RowExp ex;
-        ex.c = 0x1.71547652b82fep+0 * 32.0;
-        ex.mc = -mx * ex.c;
+        const RowExp ex{mx};
         // pass 2: the sum of the exponentials, sixteen independent evaluations at a time; a chunk that lies below
         // the floor altogether adds nothing, an element below it inside a live chunk adds less than 1e-86
         double sum = 0.0;

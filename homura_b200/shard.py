@@ -60,10 +60,46 @@ class NcclComm:
     def allgather(self, send: Storage, recv: Storage, nbytes: int) -> None:
         self._check(self.lib.hmc_comm_allgather(self.handle, send.ptr, recv.ptr, nbytes))
 
+    def set_timeout(self, seconds: float) -> None:
+        """How long a call may wait for progress before the communicator is aborted (60 s by default)."""
+        self._check(self.lib.hmc_comm_set_timeout(self.handle, max(1, int(seconds * 1000))))
+
+    def wait(self) -> None:
+        """Waits until the stream has run everything queued so far, collectives included, for at most the timeout;
+        raises (and the communicator is aborted) when a peer never joined."""
+        self._check(self.lib.hmc_comm_wait(self.handle))
+
+    def abort(self) -> None:
+        """Tears the communicator down without its peers (after one of them is known to be gone)."""
+        self._check(self.lib.hmc_comm_abort(self.handle))
+
     def close(self) -> None:
         if self.handle is not None:
             handle, self.handle = self.handle, None
             self._check(self.lib.hmc_comm_destroy(handle))
+
+
+class RankWatch:
+    """Who is still there, kept in a key-value store all ranks reach (a torch.distributed store, or anything with
+    ``set(key, value)`` and ``check([keys])``): a rank that stops between steps says so first, and its peers look
+    before they queue the next collective, so nobody launches a kernel that would wait for a rank that is gone.
+    Failure detection on the host: no kernel waits, nothing has to time out."""
+
+    def __init__(self, store, rank: int, ranks: int, job: str = "hmc"):
+        self.store, self.rank, self.ranks, self.job = store, rank, ranks, job
+
+    def _key(self, r: int) -> str:
+        return f"{self.job}/left/{r}"
+
+    def leave(self, reason: str = "") -> None:
+        """Announces that this rank takes part in no further collective."""
+        self.store.set(self._key(self.rank), reason or "left")
+
+    def check(self) -> None:
+        """Raises when a peer has announced that it left."""
+        for r in range(self.ranks):
+            if r != self.rank and self.store.check([self._key(r)]):
+                raise BackendError(ffi.HMC_CUDA_ERROR, f"rank {r} has left the job: no collective is queued")
 
 
 class ShardedReducer:
@@ -75,11 +111,14 @@ class ShardedReducer:
     before any local work or collective, when some block is empty: the block lengths follow from `offsets` and
     `global_rows`, which all ranks share, so no rank is left waiting in the all-gather.
 
+    With a `watch` (RankWatch) every collective first looks whether a peer has announced that it left, and raises
+    instead of queuing a kernel that would wait for it.
+
     The partial and gathered buffers are kept and reused from call to call (all work is ordered on the backend's
     one stream, so a buffer is free again when the next call's kernels run)."""
 
-    def __init__(self, backend, comm, offsets: Sequence[int], global_rows: int):
-        self.be, self.comm = backend, comm
+    def __init__(self, backend, comm, offsets: Sequence[int], global_rows: int, watch: Optional[RankWatch] = None):
+        self.be, self.comm, self.watch = backend, comm, watch
         self.offsets, self.global_rows = list(offsets), global_rows
         assert len(self.offsets) == comm.ranks, "one offset per rank"
         ends = self.offsets[1:] + [global_rows]
@@ -94,6 +133,8 @@ class ShardedReducer:
         return self._buffers[key]
 
     def _gather(self, local: Storage, bytes_per_rank: int, tag: str = "gathered") -> Storage:
+        if self.watch is not None:
+            self.watch.check()  # before the collective is queued: a peer that is gone would never answer it
         gathered = self._buffer(tag, bytes_per_rank * self.comm.ranks)
         self.comm.allgather(local, gathered, bytes_per_rank)
         return gathered

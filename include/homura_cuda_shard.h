@@ -78,12 +78,24 @@ typedef struct hmc_comm *hmc_comm_t;
 /* A fresh identifier for a communicator; rank 0 makes it and hands it to the others by any channel. */
 hmc_status hmc_comm_unique_id(uint8_t *id);
 /* Joins the communicator `id` as `rank` of `ranks` with the context's device and stream (collective:
- * every rank calls it). */
+ * every rank calls it). The communicator never blocks a caller for ever: every call gives the library at most
+ * the communicator's timeout (60 s unless the environment variable HMC_COMM_TIMEOUT_MS or hmc_comm_set_timeout
+ * says otherwise) to make progress. When the time runs out, or the library reports an error of an earlier
+ * collective, the communicator is aborted (kernels of it that still wait for a peer stop; the context and its
+ * stream stay usable), the call returns HMC_CUDA_ERROR and every later call on the communicator HMC_INVALID. */
 hmc_status hmc_comm_create(hmc_context_t ctx, int32_t ranks, int32_t rank, const uint8_t *id, hmc_comm_t *out);
+hmc_status hmc_comm_set_timeout(hmc_comm_t comm, int64_t milliseconds);
 hmc_status hmc_comm_destroy(hmc_comm_t comm);
 /* Queues an all-gather on the context's stream: rank r's `bytes` bytes at `send` land at
  * recv + r * bytes on every rank. send and recv are device memory of the context's device. */
 hmc_status hmc_comm_allgather(hmc_comm_t comm, const void *send, void *recv, uint64_t bytes);
+/* Waits, for at most the timeout, until everything queued on the context's stream has run (the collectives
+ * included). Where hmc_context_synchronize would wait for ever on a collective whose peer never joined, this
+ * aborts the communicator and returns HMC_CUDA_ERROR. */
+hmc_status hmc_comm_wait(hmc_comm_t comm);
+/* Tears the communicator down without the peers (which hmc_comm_destroy's orderly shutdown expects to be there):
+ * for a rank that has learnt that a peer is gone. hmc_comm_destroy still frees the handle afterwards. */
+hmc_status hmc_comm_abort(hmc_comm_t comm);
 
 #ifdef __cplusplus
 }

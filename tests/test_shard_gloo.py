@@ -146,6 +146,65 @@ def test_two_gloo_ranks_reproduce_the_single_rank_results():
     assert dict(results) == {0: "ok", 1: "ok"}, "\n".join(str(v) for v in results.values())
 
 
+def _leaving_worker(rank, world, port, store_path, results):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import time
+        from homura_b200 import ffi
+        from homura_b200.host import BackendError, F32
+        from homura_b200.shard import RankWatch, ShardedReducer, split_rows
+        from oracle_backend import OracleBackend
+
+        be = OracleBackend()
+        rows, cols = 10, 7
+        blocks = split_rows(rows, world)
+        start, length = blocks[rank]
+        watch = RankWatch(dist.FileStore(store_path, world), rank, world)
+        red = ShardedReducer(be, GlooComm(world, rank), [b[0] for b in blocks], rows, watch=watch)
+        full = np.arange(rows * cols, dtype=np.float32).reshape(rows, cols)
+        shard = be.upload(full[start:start + length], F32)
+        out = be.empty((cols,), F32)
+        red.reduce(ffi.HMC_REDUCE_SUM, out, shard, [True, False])       # a step with everybody there
+        assert (be.download(out) == full.sum(axis=0)).all()
+        dist.barrier()
+        if rank == 1:
+            watch.leave("finished early")                                # between steps, nothing in flight
+            results[rank] = "left"
+            return
+        deadline = time.time() + 20
+        while True:                                                      # the peers learn of it on the host ...
+            try:
+                watch.check()
+            except BackendError:
+                break
+            assert time.time() < deadline, "the departure never showed in the store"
+            time.sleep(0.05)
+        try:                                                             # ... and queue no collective that would wait for it
+            red.reduce(ffi.HMC_REDUCE_SUM, out, shard, [True, False])
+            results[rank] = "the collective was queued although a rank had left"
+        except BackendError as e:
+            assert e.status == ffi.HMC_CUDA_ERROR and "rank 1 has left" in str(e)
+            results[rank] = "ok"
+    except BaseException as e:
+        import traceback
+        results[rank] = "".join(traceback.format_exception(e))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_rank_that_leaves_between_steps_is_noticed_before_the_next_collective(tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_leaving_worker, args=(2, port, str(tmp_path / "ranks"), results), nprocs=2, join=True)
+    assert dict(results) == {0: "ok", 1: "left"}, "\n".join(str(v) for v in results.values())
+
+
 def test_split_rows():
     from homura_b200.shard import split_rows
     assert split_rows(10, 4) == [(0, 3), (3, 3), (6, 3), (9, 1)]
