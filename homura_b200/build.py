@@ -31,7 +31,8 @@ ARCH = os.environ.get("HOMURA_CUDA_ARCH", "sm_100a")
 NVCC_FLAGS = [
     "-gencode", f"arch=compute_{ARCH[3:]},code={ARCH}",
     "-O3", "-std=c++17", "-lineinfo", "-fmad=false",
-    "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Werror",
+    "-Werror", "all-warnings",
     "--expt-relaxed-constexpr",
     "-Xcudafe", "--diag_suppress=unsigned_compare_with_zero",
 ]

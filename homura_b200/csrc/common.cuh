@@ -15,10 +15,14 @@
 
 #define HMC_API extern "C" __attribute__((visibility("default")))
 
+namespace hmc {
+struct TraceState;
+}
 struct hmc_context {
     int32_t device;
     cudaStream_t stream;
     int32_t sm_count;
+    hmc::TraceState *trace;  // per-call timing records, when the timing log is on (else null)
 };
 
 struct hmc_event {
@@ -113,7 +117,37 @@ bool injected_data_failure(hmc_status &status);
     }                                                                               \
     ::hmc::DeviceGuard hmc_guard_((ctx)->device);                                   \
     if (hmc_guard_.status() != HMC_OK) return hmc_guard_.status();                  \
-    ::hmc::forget_earlier_error()
+    ::hmc::forget_earlier_error();                                                  \
+    ::hmc::EntryTrace hmc_trace_((ctx), __PRETTY_FUNCTION__)
+
+// Opt-in tracing of the entry points that queue work, read from the environment once per process:
+//   HMC_TIMING_LOG=<file>  every such call is bracketed by two events on the context's stream; the elapsed device
+//                          times are appended to the file as "<entry>\t<ms>" lines when the context is next
+//                          synchronised or destroyed (nothing waits inside the calls themselves);
+//   HMC_NVTX=1             every such call is an NVTX range named after the entry, for timeline tools.
+// With neither set an entry pays one predictable branch.
+class EntryTrace {
+  public:
+    EntryTrace(hmc_context *ctx, const char *pretty_function) {
+        if (enabled()) begin(ctx, pretty_function);
+    }
+    ~EntryTrace() {
+        if (active_) end();
+    }
+    EntryTrace(const EntryTrace &) = delete;
+    EntryTrace &operator=(const EntryTrace &) = delete;
+    static bool enabled();
+
+  private:
+    void begin(hmc_context *ctx, const char *pretty_function);
+    void end();
+    hmc_context *ctx_ = nullptr;
+    bool active_ = false, range_ = false;
+    int record_ = -1;
+};
+// Writes out what the timing log holds for `ctx` (the stream must have been synchronised).
+void flush_trace(hmc_context *ctx);
+void destroy_trace(hmc_context *ctx);
 
 // An error that the caller's own CUDA calls left as the thread's last error must not be taken for a failure of
 // the launch this entry is about to check: reading it clears it.

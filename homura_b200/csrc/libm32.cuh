@@ -16,17 +16,18 @@
 //                      (sysdeps/ieee754/flt-32/s_{expm1f,tanhf,log1pf}.c), plain f32 arithmetic without
 //                      fused operations.
 //
-// The header compiles for the host too (g++), where tests/native/libm32_check.cpp compares every function with the
-// host's own library over all 2^32 arguments (expf, logf, expm1f, tanhf, log1pf) and over random pairs and
-// every special pair (powf). The 2^(i/32) table is 2^(i/32) rounded to nearest with the index folded into
-// the exponent field; the other constants are the algorithms' published ones.
+// The header compiles for the host too (with g++; under nvcc the functions are device functions), where
+// tests/native/libm32_check.cpp compares every function with the host's own library over all 2^32 arguments
+// (expf, logf, expm1f, tanhf, log1pf, powf with the exponent 2) and over random pairs and every special pair
+// (powf). The 2^(i/32) table is 2^(i/32) rounded to nearest with the index folded into the exponent field; the
+// other constants are the algorithms' published ones.
 #pragma once
 
 #include <cstdint>
 #include <cstring>
 
 #if defined(__CUDACC__)
-#define LM_HD __host__ __device__ __forceinline__
+#define LM_HD __device__ __forceinline__
 #define LM_TABLE __device__ const
 #else
 #define LM_HD static inline

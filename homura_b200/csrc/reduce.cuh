@@ -8,12 +8,15 @@
 // Two kernels cover every layout, chosen from sizes and strides alone (never from the device or
 // the data's address), so a given reduction always folds in the same order:
 //
-//  * group (kind 0): an output is folded by G = 1, 32 or 256 lanes. The last reduced dimension is
-//    the "row"; it is cut into vectors of VEC elements (16 bytes), vector v of a row goes to lane
-//    v mod G, and a lane folds its vectors in order. Rows with unit stride whose start is 16-byte
-//    aligned are read with 128-bit loads, four in flight per lane; any other row is read element
-//    by element with the same assignment, hence the same result bits. Lanes are combined by warp
-//    shuffles and, for G = 256, through shared memory in warp order.
+//  * rows (kind 0): the reduced elements of an output are a sequence of runs along the last reduced
+//    dimension. An output (or one chunk of its reduced range) belongs to a team of G = 1, 32 or 256
+//    lanes; a run is cut into pieces of 32 bytes, piece w goes to lane w mod G, and a lane folds its
+//    pieces in order, run after run. Unit-stride runs that start on a 32-byte boundary are read with
+//    256-bit loads, four in flight per lane; any other run is read element by element under the same
+//    assignment, hence with the same result bits. The lanes of a team are folded by shuffles in lane
+//    order and, for 256 lanes, the warps through shared memory in warp order. The grid is one block
+//    per 256 / G outputs and chunk, all launched at once: on B200 a read-only sweep by many short
+//    blocks measured 5 % faster than the same sweep by a resident grid that loops.
 //  * columns (kind 1): the outputs are adjacent in memory (the last kept dimension has stride 1)
 //    and the reduced elements are strided. A block is 32 x 8 threads; a thread owns VC adjacent
 //    outputs (one 16-byte load per reduced index), the 8 warps take reduced indices j, j+8, ...,
@@ -34,23 +37,26 @@ namespace hmc {
 
 constexpr int kRThreads = 256;
 constexpr int64_t kTargetLanes = 148 * 2048;  // fixed, so that plans do not depend on the device
-constexpr int64_t kTargetColumnBlocks = 148 * 3;  // one wave of the column kernel's blocks (three are resident per SM)
+// The column kernel's blocks: enough of them for every SM several times over (blocks that read a few hundred KB
+// each and all start at once measured a third faster than one resident wave), each reading at least this much.
+constexpr int64_t kTargetColumnBlocks = 148 * 8;
+constexpr int64_t kColumnBlockBytes = 256 * 1024;
 constexpr int64_t kMaxSplits = 4096;
 constexpr int64_t kWarpRowOutputs = 148 * 32;  // outputs from which a long row is folded by a warp
 constexpr int64_t kWarpRowLength = 1 << 16;    // and the longest such row
 constexpr int64_t kPartialBytes = 16;
 
 struct ReducePlan {
-    int32_t kind;    // 0 group, 1 columns
-    int32_t group;   // lanes per output (kind 0)
-    int32_t vec;     // elements per 16-byte vector of the source dtype
+    int32_t kind;    // 0 rows, 1 columns
+    int32_t group;   // lanes per team (kind 0)
+    int32_t vec;     // elements per 32-byte piece of the source dtype (kind 0)
     int32_t vc;      // outputs per thread (kind 1)
     int64_t nout, nred;
     int64_t row, step;  // last reduced dimension: size and source stride
     int64_t splits, chunk;
     int64_t ncols, kouter, xtiles;  // kind 1: last kept size, product of the others, column tiles
-    // kind 0, no chunks, and every output folds one unit-stride row of whole vectors (nred < 2^31): rows that
-    // start on a 16-byte boundary take a loop without the bookkeeping of ranges, dimensions and ragged ends.
+    // kind 0, no chunks, and every output folds one unit-stride run of whole 16-byte vectors (nred < 2^31): what the
+    // one-pass variance kernel for rows requires.
     int32_t simple;
 };
 
@@ -112,25 +118,29 @@ __device__ __forceinline__ Acc shuffle_down(Acc v, int delta) {
     return v;
 }
 
-// The result of the G lanes of a group, valid in its lane 0. All threads of the block call it.
+// ---- teams ----
+// The accumulators of a team's G lanes folded in lane order; the result is valid in the team's lane 0. Every
+// thread of the block calls it (256-lane teams meet at block barriers).
 template <int G, class Op>
-__device__ __forceinline__ typename Op::Acc group_combine(const Op &op, typename Op::Acc acc) {
+__device__ __forceinline__ typename Op::Acc fold_team(const Op &op, typename Op::Acc acc) {
     using Acc = typename Op::Acc;
     if constexpr (G == 1) {
         return acc;
     } else {
+        // lane l takes lane l + d: after the last step lane 0 holds lanes 0..31 in order
 #pragma unroll
-        for (int d = 16; d > 0; d >>= 1) {
-            Acc other = shuffle_down(acc, d);
-            acc = op.combine(acc, other);
+        for (int d = 1; d < 32; d <<= 1) {
+            const Acc later = shuffle_down(acc, d);
+            acc = op.combine(acc, later);
         }
         if constexpr (G == 256) {
-            __shared__ Acc warp_acc[kRThreads / 32];
-            const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-            if (lane == 0) warp_acc[warp] = acc;
+            __shared__ Acc of_warp[kRThreads / 32];
+            const int warp = threadIdx.x >> 5;
+            if ((threadIdx.x & 31) == 0) of_warp[warp] = acc;
             __syncthreads();
             if (threadIdx.x == 0) {
-                for (int w = 1; w < kRThreads / 32; ++w) acc = op.combine(acc, warp_acc[w]);
+#pragma unroll
+                for (int w = 1; w < kRThreads / 32; ++w) acc = op.combine(acc, of_warp[w]);
             }
             __syncthreads();
         }
@@ -181,314 +191,264 @@ struct alignas(sizeof(T) * VEC >= 16 ? 16 : sizeof(T) * VEC) RVec {
     T v[VEC];
 };
 
-// Folds the reduced elements [j0, j1) of output o, whose kept offset is `base`, for one lane.
-template <int G, class Op>
-__device__ __forceinline__ typename Op::Acc fold_range(const Op &op, const ReduceArgs &a, int64_t o, int64_t base,
-                                                       int64_t j0, int64_t j1, int lane) {
-    using T = typename Op::T;
-    using Acc = typename Op::Acc;
-    constexpr int VEC = 16 / sizeof(T);
-    constexpr int UNR = 4;
-    const T *src = static_cast<const T *>(a.kept.data);
-    const int64_t row = a.plan.row, step = a.plan.step;
-    Acc acc = op.init();
-    if (j1 <= j0) return acc;
-    for (int64_t q = j0 / row; q * row < j1; ++q) {
-        const int64_t first = q * row;
-        const int64_t lo = j0 > first ? j0 - first : 0;
-        const int64_t hi = j1 - first < row ? j1 - first : row;
-        const int64_t r = base + (a.red.ndim > 1 ? decompose(a.red, q, a.red.ndim - 1) : 0);
-        const T *p = src + r;
-        const int64_t v_end = (hi + VEC - 1) / VEC;
-        int64_t v = lo / VEC + lane;
-        const bool fast = step == 1 && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
-        if (fast) {
-            // A range that starts inside a vector: its lane takes the leading elements one by one.
-            if (v < v_end && v * VEC < lo) {
-                for (int e = 0; e < VEC; ++e) {
-                    const int64_t i = v * VEC + e;
-                    if (i >= lo && i < hi) acc = fold_step(op, acc, p[i], o, first + i);
-                }
-                v += G;
-            }
-            // Whole, aligned vectors, UNR of them in flight.
-            while (v + (UNR - 1) * G < v_end && (v + (UNR - 1) * G) * VEC + VEC <= hi) {
-                RVec<T, VEC> x[UNR];
-#pragma unroll
-                for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VEC> *>(p + (v + u * G) * VEC);
-                bool general = true;
-                if constexpr (is_extreme<Op>::value) {
-                    // The best of the batch by plain comparisons (a later element wins only if strictly better), then
-                    // one general combination with what came before; a NaN in the batch (seen in the sum of the
-                    // keys) sends the batch through the general step instead.
-                    constexpr bool kMax = extreme_is_max<Op>::value;
-                    auto best_key = order_key(x[0].v[0]);
-                    T best = x[0].v[0];
-                    int code = 0;
-                    float alarm = 0.0f;
-#pragma unroll
-                    for (int u = 0; u < UNR; ++u) {
-#pragma unroll
-                        for (int e = 0; e < VEC; ++e) {
-                            const auto k = order_key(x[u].v[e]);
-                            if constexpr (Tr<T>::kind == kFloat) alarm += static_cast<float>(k);
-                            const bool better = kMax ? k > best_key : k < best_key;
-                            best_key = better ? k : best_key;
-                            best = better ? x[u].v[e] : best;
-                            code = better ? u * VEC + e : code;
-                        }
-                    }
-                    if (alarm == alarm) {
-                        const int64_t at = first + (v + (code / VEC) * G) * VEC + code % VEC;
-                        acc = op.combine(acc, Acc{best, at});
-                        general = false;
-                    }
-                }
-                if (general) {
-#pragma unroll
-                    for (int u = 0; u < UNR; ++u) {
-#pragma unroll
-                        for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x[u].v[e], o, first + (v + u * G) * VEC + e);
-                    }
-                }
-                v += UNR * G;
-            }
-            for (; v < v_end; v += G) {
-                const int64_t i0 = v * VEC;
-                if (i0 + VEC <= hi) {
-                    RVec<T, VEC> x = *reinterpret_cast<const RVec<T, VEC> *>(p + i0);
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x.v[e], o, first + i0 + e);
-                } else {
-                    for (int e = 0; e < VEC; ++e) {
-                        const int64_t i = i0 + e;
-                        if (i < hi) acc = fold_step(op, acc, p[i], o, first + i);
-                    }
-                }
-            }
-        } else {
-            for (; v < v_end; v += G) {
-                const int64_t i0 = v * VEC;
-#pragma unroll
-                for (int e = 0; e < VEC; ++e) {
-                    const int64_t i = i0 + e;
-                    if (i >= lo && i < hi) acc = fold_step(op, acc, p[i * step], o, first + i);
-                }
-            }
-        }
-    }
-    return acc;
+// ---- rows ----
+// A piece: 32 bytes of a run, read with one 256-bit load.
+template <class T>
+struct alignas(32) Piece {
+    static constexpr int N = 32 / static_cast<int>(sizeof(T));
+    T v[N];
+};
+template <class T>
+__device__ __forceinline__ Piece<T> load_piece(const T *p) {
+    uint32_t w[8];
+    // (not volatile: the compiler may schedule it like any other load)
+    asm("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+        : "l"(p));
+    Piece<T> out;
+    memcpy(&out, w, 32);
+    return out;
 }
 
-// One lane's share of a simple row (plan.simple): vectors lane, lane + G, ... of the nvec vectors at p, in
-// the order and with the element indices fold_range gives them, hence the same bits.
-template <int G, class Op>
-__device__ __forceinline__ typename Op::Acc fold_simple_row(const Op &op, const typename Op::T *p, uint32_t nvec, int lane,
-                                                            int64_t o) {
-    using T = typename Op::T;
-    using Acc = typename Op::Acc;
-    constexpr int VEC = 16 / sizeof(T);
-    constexpr int UNR = 4;
-    Acc acc = op.init();
-    uint32_t v = lane;
-    for (; v + (UNR - 1) * G < nvec; v += UNR * G) {
-        RVec<T, VEC> x[UNR];
+// A batch of pieces folded into `acc`; `at[u]` is the reduced index of piece u's first element.
+template <int U, class Op>
+__device__ __forceinline__ void fold_batch(const Op &op, typename Op::Acc &acc, const Piece<typename Op::T> (&x)[U],
+                                           const int64_t (&at)[U], int64_t o) {
+    constexpr int N = Piece<typename Op::T>::N;
 #pragma unroll
-        for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VEC> *>(p + static_cast<size_t>(v + u * G) * VEC);
+    for (int u = 0; u < U; ++u) {
 #pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x[u].v[e], o, static_cast<int64_t>(v + u * G) * VEC + e);
-        }
+        for (int e = 0; e < N; ++e) acc = fold_step(op, acc, x[u].v[e], o, at[u] + e);
     }
-    for (; v < nvec; v += G) {
-        const RVec<T, VEC> x = *reinterpret_cast<const RVec<T, VEC> *>(p + static_cast<size_t>(v) * VEC);
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) acc = fold_step(op, acc, x.v[e], o, static_cast<int64_t>(v) * VEC + e);
-    }
-    return acc;
 }
 
-
-// The same for max / min / argmax / argmin, where the general step (first NaN, then first of equals, a 64-bit
-// index) costs about forty instructions per element. Here a lane keeps the best key, its raw value and a
-// 32-bit index, and takes a later element only if it is strictly better: "first of equals" as in the general
-// step. NaNs are not handled but detected (the sum of a vector's keys is NaN if one of them is; an
-// infinity minus infinity there raises a false alarm, which is harmless): `redo` tells the caller to fold the
-// row again with the general step.
-template <int G, class TT, bool MAX>
-__device__ __forceinline__ typename Extreme<TT, MAX>::Acc fold_simple_row_extreme(const TT *p, uint32_t nvec, int lane, bool &redo) {
-    using Acc = typename Extreme<TT, MAX>::Acc;
-    constexpr int VEC = 16 / sizeof(TT);
-    constexpr int UNR = 4;
-    constexpr bool kFloating = Tr<TT>::kind == kFloat;
-    redo = false;
-    if (static_cast<uint32_t>(lane) >= nvec) return Acc{TT{}, -1};
-    TT best = p[static_cast<size_t>(lane) * VEC];
-    auto best_key = order_key(best);
-    uint32_t best_at = lane * VEC;
-    float alarm = 0.0f;
-    auto take_vector = [&](const RVec<TT, VEC> &x, uint32_t at) {
-        if constexpr (kFloating) {
-            float s = static_cast<float>(order_key(x.v[0]));
-#pragma unroll
-            for (int e = 1; e < VEC; ++e) s += static_cast<float>(order_key(x.v[e]));
-            alarm += s;
-        }
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-            const auto k = order_key(x.v[e]);
-            const bool better = MAX ? k > best_key : k < best_key;
-            best_key = better ? k : best_key;
-            best = better ? x.v[e] : best;
-            best_at = better ? at + e : best_at;
+// One lane's share of the elements [lo, hi) of a run: the run's element i lies at p[i * step] and has the reduced
+// index first + i; piece w = elements [w N, (w + 1) N) belongs to lane w mod G.
+template <int G, class Op>
+__device__ __forceinline__ void fold_run(const Op &op, typename Op::Acc &acc, const typename Op::T *p, int64_t step, int64_t lo,
+                                         int64_t hi, int64_t first, int lane, int64_t o) {
+    using T = typename Op::T;
+    constexpr int N = Piece<T>::N;
+    constexpr int U = 4;
+    const int64_t w_lo = lo / N, w_whole = hi / N, w_end = (hi + N - 1) / N;
+    // the lane's first piece at or after w_lo
+    int64_t w = w_lo + ((lane - w_lo % G) + G) % G;
+    auto ragged = [&](int64_t piece) {
+        for (int e = 0; e < N; ++e) {
+            const int64_t i = piece * N + e;
+            if (i >= lo && i < hi) acc = fold_step(op, acc, p[i * step], o, first + i);
         }
     };
-    uint32_t v = lane;
-    for (; v + (UNR - 1) * G < nvec; v += UNR * G) {
-        RVec<TT, VEC> x[UNR];
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<TT, VEC> *>(p + static_cast<size_t>(v + u * G) * VEC);
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) take_vector(x[u], (v + u * G) * VEC);
+    if (w == w_lo && w * N < lo && w < w_end) {  // the range starts inside this piece
+        ragged(w);
+        w += G;
     }
-    for (; v < nvec; v += G) take_vector(*reinterpret_cast<const RVec<TT, VEC> *>(p + static_cast<size_t>(v) * VEC), v * VEC);
-    if constexpr (kFloating) redo = alarm != alarm;
-    return Acc{best, static_cast<int64_t>(best_at)};
-}
-
-// kind 0. Grid: (tiles of 256 / G outputs, splits).
-template <int G, class Op, class Sink>
-__global__ void __launch_bounds__(kRThreads) reduce_group_kernel(const __grid_constant__ ReduceArgs a, const Op op,
-                                                                 const Sink sink) {
-    using Acc = typename Op::Acc;
-    constexpr int P = kRThreads / G;
-    const ReducePlan &p = a.plan;
-    const int lane = threadIdx.x % G;
-    const int slot = threadIdx.x / G;
-    const int64_t c = blockIdx.y;
-    const int64_t j0 = c * p.chunk;
-    const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
-    const int64_t tiles = (p.nout + P - 1) / P;
-    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-        const int64_t o = tile * P + slot;
-        Acc acc = op.init();
-        if (o < p.nout) {
-            using T = typename Op::T;
-            const int64_t base = a.kept.offset + decompose(a.kept, o, a.kept.ndim);
-            const T *row = static_cast<const T *>(a.kept.data) + base;
-            bool general = true;
-            if constexpr (G > 1) {
-                if (p.simple && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
-                    const uint32_t nvec = static_cast<uint32_t>(p.nred) / (16 / sizeof(T));
-                    if constexpr (is_extreme<Op>::value) {
-                        bool redo;
-                        acc = fold_simple_row_extreme<G, T, std::is_same_v<Op, Extreme<T, true>>>(row, nvec, lane, redo);
-                        // the lanes of an output agree on folding again (an output's lanes are a warp, or the block)
-                        if constexpr (G == 32) general = __any_sync(0xFFFFFFFFu, redo);
-                        else general = __syncthreads_or(redo);
-                    } else {
-                        acc = fold_simple_row<G>(op, row, nvec, lane, o);
-                        general = false;
+    if (step == 1 && (reinterpret_cast<uintptr_t>(p) & 31) == 0) {
+        if constexpr (is_extreme<Op>::value) {
+            // max / min: the general step (first NaN, then first of equals, a 64-bit index) costs about forty
+            // instructions an element. Here the lane keeps the best key, its value and place by plain comparisons over
+            // all its whole pieces of the run (a later element wins only if strictly better, so the first of equals
+            // stays) and folds that once. NaNs are not handled but detected (the sum of the keys is NaN if one of
+            // them is; an infinity minus infinity raises a false alarm, which is harmless): the lane then folds the
+            // same pieces again with the general step.
+            if (w < w_whole) {
+                constexpr bool kMax = extreme_is_max<Op>::value;
+                const typename Op::Acc before = acc;
+                const int64_t w_first = w;
+                T best = p[w * N];
+                auto best_key = order_key(best);
+                int64_t best_at = w * N;
+                float alarm = 0.0f;
+                auto take = [&](const Piece<T> &x, int64_t at) {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) {
+                        const auto k = order_key(x.v[e]);
+                        if constexpr (Tr<T>::kind == kFloat) alarm += static_cast<float>(k);
+                        const bool better = kMax ? k > best_key : k < best_key;
+                        best_key = better ? k : best_key;
+                        best = better ? x.v[e] : best;
+                        best_at = better ? at + e : best_at;
+                    }
+                };
+                for (; w + (U - 1) * G < w_whole; w += U * G) {
+                    Piece<T> x[U];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) x[u] = load_piece(p + (w + u * G) * N);
+#pragma unroll
+                    for (int u = 0; u < U; ++u) take(x[u], (w + u * G) * N);
+                }
+                for (; w < w_whole; w += G) take(load_piece(p + w * N), w * N);
+                if (alarm == alarm) {
+                    acc = op.combine(acc, typename Op::Acc{best, first + best_at});
+                } else {
+                    acc = before;
+                    for (int64_t v = w_first; v < w_whole; v += G) {
+                        const Piece<T> x = load_piece(p + v * N);
+#pragma unroll
+                        for (int e = 0; e < N; ++e) acc = fold_step(op, acc, x.v[e], o, first + v * N + e);
                     }
                 }
             }
-            if (general) acc = fold_range<G>(op, a, o, base, j0, j1, lane);
         }
-        acc = group_combine<G>(op, acc);
-        if (lane == 0 && o < p.nout) {
-            if (p.splits == 1) sink.put(o, acc, p.nred);
-            else static_cast<Acc *>(a.partials)[c * p.nout + o] = acc;
+        for (; w + (U - 1) * G < w_whole; w += U * G) {
+            Piece<T> x[U];
+            int64_t at[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                at[u] = first + (w + u * G) * N;
+                x[u] = load_piece(p + (w + u * G) * N);
+            }
+            fold_batch<U>(op, acc, x, at, o);
         }
+        for (; w < w_whole; w += G) {
+            const Piece<T> x[1] = {load_piece(p + w * N)};
+            const int64_t at[1] = {first + w * N};
+            fold_batch<1>(op, acc, x, at, o);
+        }
+    } else {
+        for (; w < w_whole; w += G) {
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc = fold_step(op, acc, p[(w * N + e) * step], o, first + w * N + e);
+        }
+    }
+    if (w < w_end) ragged(w);  // the range ends inside this piece (w == w_whole)
+}
+
+// One lane's share of the reduced elements [j0, j1) of output o, whose first element lies at `base`: the runs
+// that the range touches, in order.
+template <int G, class Op>
+__device__ __forceinline__ typename Op::Acc fold_span(const Op &op, const ReduceArgs &a, int64_t o, int64_t base, int64_t j0,
+                                                      int64_t j1, int lane) {
+    using T = typename Op::T;
+    typename Op::Acc acc = op.init();
+    if (j1 <= j0) return acc;
+    const T *src = static_cast<const T *>(a.kept.data) + base;
+    const int64_t row = a.plan.row, step = a.plan.step;
+    if (a.red.ndim <= 1) {
+        fold_run<G>(op, acc, src, step, j0, j1, 0, lane, o);
+        return acc;
+    }
+    const int64_t q_first = j0 / row, q_last = (j1 - 1) / row;
+    for (int64_t q = q_first; q <= q_last; ++q) {
+        const int64_t first = q * row;
+        const int64_t lo = q == q_first ? j0 - first : 0;
+        const int64_t hi = q == q_last ? j1 - first : row;
+        fold_run<G>(op, acc, src + decompose(a.red, q, a.red.ndim - 1), step, lo, hi, first, lane, o);
+    }
+    return acc;
+}
+
+// kind 0. Grid: (teams of outputs, chunks), every block launched at once: block (x, y) folds chunk y of the
+// 256 / G outputs x * (256 / G) ...
+template <int G, class Op, class Sink>
+__global__ void __launch_bounds__(kRThreads) reduce_rows_kernel(const __grid_constant__ ReduceArgs a, const Op op, const Sink sink) {
+    using Acc = typename Op::Acc;
+    constexpr int kTeams = kRThreads / G;
+    const ReducePlan &p = a.plan;
+    const int lane = threadIdx.x % G;
+    const int64_t o = static_cast<int64_t>(blockIdx.x) * kTeams + threadIdx.x / G;
+    const int64_t chunk = blockIdx.y;
+    const bool live = o < p.nout;
+    Acc acc = op.init();
+    if (live) {
+        const int64_t j0 = chunk * p.chunk;
+        const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
+        acc = fold_span<G>(op, a, o, a.kept.offset + decompose(a.kept, o, a.kept.ndim), j0, j1, lane);
+    }
+    acc = fold_team<G>(op, acc);
+    if (lane == 0 && live) {
+        if (p.splits == 1) sink.put(o, acc, p.nred);
+        else static_cast<Acc *>(a.partials)[chunk * p.nout + o] = acc;
     }
 }
 
-// kind 1. Grid: (kouter * xtiles, splits); block 32 x 8.
+// kind 1. Grid: (kouter * xtiles, splits), every block launched at once; block 32 x 8: thread (tx, ty) owns the VC
+// adjacent outputs tx * VC .. of its strip of 32 * VC outputs and folds the reduced indices j0 + ty, j0 + ty + 8, ...
+// of its chunk; the eight warps are then folded in warp order through shared memory.
 template <class Op, class Sink>
 __global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_constant__ ReduceArgs a, const Op op,
                                                                    const Sink sink) {
     using T = typename Op::T;
     using Acc = typename Op::Acc;
     constexpr int VC = (16 / sizeof(T)) > 8 ? 8 : (16 / sizeof(T));
-    constexpr int UNR = 8;  // loads in flight per thread: 8 measured 6 % faster than 4 on B200 (three blocks per SM)
+    constexpr int UNR = 8;  // loads in flight per thread
     const ReducePlan &p = a.plan;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int64_t chunk = blockIdx.y;
     const int64_t j0 = chunk * p.chunk;
     const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
     const int last = a.kept.ndim - 1;
-    const bool single = a.red.ndim == 1;
-    auto red_off = [&](int64_t j) { return single ? j * a.red.strides[0] : decompose(a.red, j, a.red.ndim); };
     __shared__ Acc stage[7][32 * VC];
-    const int64_t xblocks = p.kouter * p.xtiles;
-    for (int64_t bx = blockIdx.x; bx < xblocks; bx += gridDim.x) {
-        const int64_t outer = bx / p.xtiles;
-        const int64_t tile = bx - outer * p.xtiles;
-        const int64_t c0 = tile * (32 * VC) + static_cast<int64_t>(tx) * VC;
-        // Offset of the outer kept index; the column index adds c (stride 1).
-        const int64_t base = a.kept.offset + (last > 0 ? decompose(a.kept, outer, last) : 0);
-        const int64_t o0 = outer * p.ncols + c0;
-        const T *src = static_cast<const T *>(a.kept.data) + base + c0;
-        Acc acc[VC];
+    const int64_t outer = blockIdx.x / p.xtiles;
+    const int64_t tile = blockIdx.x - outer * p.xtiles;
+    const int64_t c0 = tile * (32 * VC) + static_cast<int64_t>(tx) * VC;
+    // Offset of the outer kept index; the column index adds c (stride 1).
+    const int64_t base = a.kept.offset + (last > 0 ? decompose(a.kept, outer, last) : 0);
+    const int64_t o0 = outer * p.ncols + c0;
+    const T *src = static_cast<const T *>(a.kept.data) + base + c0;
+    Acc acc[VC];
 #pragma unroll
-        for (int e = 0; e < VC; ++e) acc[e] = op.init();
-        // what the op needs to know about an output (its mean, for the squared deviations) is fetched once
-        Op ops[VC];
+    for (int e = 0; e < VC; ++e) acc[e] = op.init();
+    // what the op needs to know about an output (its mean, for the squared deviations) is fetched once
+    Op ops[VC];
 #pragma unroll
-        for (int e = 0; e < VC; ++e) ops[e] = bind_output(op, c0 + e < p.ncols ? o0 + e : 0);
-        const bool in_range = c0 < p.ncols;
-        const bool whole = c0 + VC <= p.ncols;
-        if (in_range) {
+    for (int e = 0; e < VC; ++e) ops[e] = bind_output(op, c0 + e < p.ncols ? o0 + e : 0);
+    const bool in_range = c0 < p.ncols;
+    const bool whole = c0 + VC <= p.ncols;
+    if (in_range) {
+        const int64_t stride = a.red.strides[0];
+        const bool walk = a.red.ndim == 1 && whole && (reinterpret_cast<uintptr_t>(src) & (alignof(RVec<T, VC>) - 1)) == 0 &&
+                          (stride * static_cast<int64_t>(sizeof(T))) % static_cast<int64_t>(alignof(RVec<T, VC>)) == 0;
+        if (walk) {
+            // one reduced dimension, whole aligned vectors: a pointer that steps by eight rows
+            const T *q = src + (j0 + ty) * stride;
+            const int64_t step = 8 * stride;
             int64_t j = j0 + ty;
-            for (; j + (UNR - 1) * 8 < j1; j += UNR * 8) {
+            for (; j + (UNR - 1) * 8 < j1; j += UNR * 8, q += UNR * step) {
                 RVec<T, VC> x[UNR];
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) {
-                    const T *q = src + red_off(j + u * 8);
-                    if (whole && (reinterpret_cast<uintptr_t>(q) & (alignof(RVec<T, VC>) - 1)) == 0) {
-                        x[u] = *reinterpret_cast<const RVec<T, VC> *>(q);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < VC; ++e) x[u].v[e] = c0 + e < p.ncols ? q[e] : T{};
-                    }
-                }
+                for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VC> *>(q + u * step);
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
 #pragma unroll
-                    for (int e = 0; e < VC; ++e) {
-                        if (whole || c0 + e < p.ncols) acc[e] = fold_step(ops[e], acc[e], x[u].v[e], o0 + e, j + u * 8);
-                    }
+                    for (int e = 0; e < VC; ++e) acc[e] = fold_step(ops[e], acc[e], x[u].v[e], o0 + e, j + u * 8);
                 }
             }
-            for (; j < j1; j += 8) {
-                const T *q = src + red_off(j);
+            for (; j < j1; j += 8, q += step) {
+                const RVec<T, VC> x = *reinterpret_cast<const RVec<T, VC> *>(q);
+#pragma unroll
+                for (int e = 0; e < VC; ++e) acc[e] = fold_step(ops[e], acc[e], x.v[e], o0 + e, j);
+            }
+        } else {
+            const bool single = a.red.ndim == 1;
+            for (int64_t j = j0 + ty; j < j1; j += 8) {
+                const T *q = src + (single ? j * stride : decompose(a.red, j, a.red.ndim));
 #pragma unroll
                 for (int e = 0; e < VC; ++e) {
                     if (c0 + e < p.ncols) acc[e] = fold_step(ops[e], acc[e], q[e], o0 + e, j);
                 }
             }
         }
-        if (ty > 0) {
+    }
+    if (ty > 0) {
 #pragma unroll
-            for (int e = 0; e < VC; ++e) stage[ty - 1][tx * VC + e] = acc[e];
-        }
-        __syncthreads();
-        if (ty == 0 && in_range) {
+        for (int e = 0; e < VC; ++e) stage[ty - 1][tx * VC + e] = acc[e];
+    }
+    __syncthreads();
+    if (ty == 0 && in_range) {
 #pragma unroll
-            for (int e = 0; e < VC; ++e) {
-                if (c0 + e >= p.ncols) continue;
-                Acc r = acc[e];
-                for (int w = 0; w < 7; ++w) r = op.combine(r, stage[w][tx * VC + e]);
-                if (p.splits == 1) sink.put(o0 + e, r, p.nred);
-                else static_cast<Acc *>(a.partials)[chunk * p.nout + o0 + e] = r;
-            }
+        for (int e = 0; e < VC; ++e) {
+            if (c0 + e >= p.ncols) continue;
+            Acc r = acc[e];
+            for (int w = 0; w < 7; ++w) r = op.combine(r, stage[w][tx * VC + e]);
+            if (p.splits == 1) sink.put(o0 + e, r, p.nred);
+            else static_cast<Acc *>(a.partials)[chunk * p.nout + o0 + e] = r;
         }
-        __syncthreads();
     }
 }
 
-// Folds the partials of each output in chunk order. L lanes per output (1, 32 or 256): lane l folds chunks
-// l, l + L, ... and the lanes are combined in lane order (shuffles, and shared memory for 256).
+// The partials of an output folded in chunk order by a team of L lanes (1, 32 or 256): lane l takes chunks
+// l, l + L, ... and the team folds in lane order. Grid: one block per 256 / L outputs.
 template <int L, class Op, class Sink>
 __global__ void __launch_bounds__(kRThreads) reduce_combine_kernel(const __grid_constant__ ReduceArgs a, const Op op,
                                                                    const Sink sink) {
@@ -496,23 +456,14 @@ __global__ void __launch_bounds__(kRThreads) reduce_combine_kernel(const __grid_
     const ReducePlan &p = a.plan;
     const Acc *partials = static_cast<const Acc *>(a.partials);
     const int lane = threadIdx.x % L;
-    const int64_t per_block = kRThreads / L;
-    const int64_t rounds = (p.nout + per_block - 1) / per_block;
-    for (int64_t t = blockIdx.x; t < rounds; t += gridDim.x) {
-        const int64_t o = t * per_block + threadIdx.x / L;
-        Acc acc = op.init();
-        if (o < p.nout) {
+    const int64_t o = static_cast<int64_t>(blockIdx.x) * (kRThreads / L) + threadIdx.x / L;
+    Acc acc = op.init();
+    if (o < p.nout) {
 #pragma unroll 4
-            for (int64_t c = lane; c < p.splits; c += L) acc = op.combine(acc, partials[c * p.nout + o]);
-        }
-        if constexpr (L == 32) {
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) acc = op.combine(acc, shuffle_down(acc, d));
-        } else if constexpr (L == 256) {
-            acc = group_combine<256>(op, acc);
-        }
-        if (lane == 0 && o < p.nout) sink.put(o, acc, p.nred);
+        for (int64_t c = lane; c < p.splits; c += L) acc = op.combine(acc, partials[c * p.nout + o]);
     }
+    acc = fold_team<L>(op, acc);
+    if (lane == 0 && o < p.nout) sink.put(o, acc, p.nred);
 }
 
 inline unsigned clamp_grid(int64_t n, int64_t cap) { return static_cast<unsigned>(n < cap ? (n < 1 ? 1 : n) : cap); }
@@ -524,29 +475,29 @@ hmc_status launch_reduce(const ReduceArgs &a, const Op &op, const Sink &sink, cu
     const ReducePlan &p = a.plan;
     if (p.nout == 0) return HMC_OK;
     if (p.kind == 1) {
-        dim3 grid(clamp_grid(p.kouter * p.xtiles, 1 << 20), static_cast<unsigned>(p.splits));
+        if (p.kouter * p.xtiles > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 strips of outputs");
+        dim3 grid(static_cast<unsigned>(p.kouter * p.xtiles), static_cast<unsigned>(p.splits));
         reduce_columns_kernel<Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
     } else {
-        const int64_t per_block = kRThreads / p.group;
-        const int64_t tiles = (p.nout + per_block - 1) / per_block;
-        dim3 grid(clamp_grid(tiles, 1 << 20), static_cast<unsigned>(p.splits));
-        if (p.group == 256) reduce_group_kernel<256, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
-        else if (p.group == 32) reduce_group_kernel<32, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
-        else reduce_group_kernel<1, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        const int64_t teams = kRThreads / p.group;
+        const int64_t blocks = (p.nout + teams - 1) / teams;
+        if (blocks > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
+        dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(p.splits));
+        if (p.group == 256) reduce_rows_kernel<256, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        else if (p.group == 32) reduce_rows_kernel<32, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        else reduce_rows_kernel<1, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
     }
     hmc_status s = launch_status("reduction kernel launch");
     if (s != HMC_OK) return s;
     if (p.splits > 1) {
-        if (p.splits >= 512 && p.nout <= 64) {
-            // a few outputs with very many partials each (a full reduction): a block per output
-            reduce_combine_kernel<256, Op, Sink><<<clamp_grid(p.nout, 1 << 16), kRThreads, 0, stream>>>(a, op, sink);
-        } else if (p.splits >= 64) {
-            const int64_t rounds = (p.nout + 7) / 8;
-            reduce_combine_kernel<32, Op, Sink><<<clamp_grid(rounds, 1 << 16), kRThreads, 0, stream>>>(a, op, sink);
-        } else {
-            const int64_t rounds = (p.nout + kRThreads - 1) / kRThreads;
-            reduce_combine_kernel<1, Op, Sink><<<clamp_grid(rounds, 1 << 16), kRThreads, 0, stream>>>(a, op, sink);
-        }
+        // a few outputs with very many partials each (a full reduction): a block per output; many partials: a warp
+        const int lanes = (p.splits >= 512 && p.nout <= 64) ? 256 : (p.splits >= 64 ? 32 : 1);
+        const int64_t blocks = (p.nout + kRThreads / lanes - 1) / (kRThreads / lanes);
+        if (blocks > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
+        const unsigned grid = static_cast<unsigned>(blocks);
+        if (lanes == 256) reduce_combine_kernel<256, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        else if (lanes == 32) reduce_combine_kernel<32, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        else reduce_combine_kernel<1, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
         s = launch_status("reduction combine kernel launch");
     }
     return s;

@@ -32,36 +32,28 @@ hmc_status reduce_var_partial(hmc_context_t ctx, double *partial, ReduceArgs &a,
 namespace {
 
 // Sum, mean and squared deviations of each output in one kernel, for plans without chunks: the
-// second walk over the row finds it in cache. The folds and the lane tree are those of the two
-// separate reductions, so both routes give the same bits.
+// second walk over the row finds it in cache. The folds and the team's order are those of the two
+// separate reductions, so both routes give the same bits. Grid: one block per 256 / G outputs.
 template <int G, class T>
 __global__ void __launch_bounds__(kRThreads) deviations_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
-    constexpr int P = kRThreads / G;
+    constexpr int kTeams = kRThreads / G;
     const ReducePlan &p = a.plan;
     const int lane = threadIdx.x % G;
-    const int slot = threadIdx.x / G;
-    __shared__ double mean_of[P];
-    FloatFold<T, false> fold;
-    const int64_t tiles = (p.nout + P - 1) / P;
-    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-        const int64_t o = tile * P + slot;
-        const bool valid = o < p.nout;
-        const int64_t base = valid ? a.kept.offset + decompose(a.kept, o, a.kept.ndim) : 0;
-        const T *row = static_cast<const T *>(a.kept.data) + base;
-        const bool simple = G > 1 && p.simple && (reinterpret_cast<uintptr_t>(row) & 15) == 0;
-        const uint32_t nvec = static_cast<uint32_t>(p.nred) / (16 / sizeof(T));
-        double sum = !valid ? 0.0 : (simple ? fold_simple_row<G>(fold, row, nvec, lane, o) : fold_range<G>(fold, a, o, base, 0, p.nred, lane));
-        sum = group_combine<G>(fold, sum);
-        if (lane == 0) mean_of[slot] = sum / static_cast<double>(p.nred);
-        if constexpr (G > 1) {
-            if constexpr (G == 32) __syncwarp(); else __syncthreads();
-        }
-        SquaredDeviation<T> dev{nullptr, mean_of[slot]};
-        double sq = !valid ? 0.0 : (simple ? fold_simple_row<G>(dev, row, nvec, lane, o) : fold_range<G>(dev, a, o, base, 0, p.nred, lane));
-        sq = group_combine<G>(dev, sq);
-        if (lane == 0 && valid) sink.put(o, sq, p.nred);
-        if constexpr (G == 256) __syncthreads();
-    }
+    const int team = threadIdx.x / G;
+    __shared__ double mean_of[kTeams];
+    const FloatFold<T, false> fold;
+    const int64_t o = static_cast<int64_t>(blockIdx.x) * kTeams + team;
+    const bool live = o < p.nout;
+    const int64_t base = live ? a.kept.offset + decompose(a.kept, o, a.kept.ndim) : 0;
+    double sum = live ? fold_span<G>(fold, a, o, base, 0, p.nred, lane) : 0.0;
+    sum = fold_team<G>(fold, sum);
+    if (lane == 0) mean_of[team] = sum / static_cast<double>(p.nred);
+    if constexpr (G == 32) __syncwarp();
+    else __syncthreads();
+    const SquaredDeviation<T> dev{nullptr, mean_of[team]};
+    double sq = live ? fold_span<G>(dev, a, o, base, 0, p.nred, lane) : 0.0;
+    sq = fold_team<G>(dev, sq);
+    if (lane == 0 && live) sink.put(o, sq, p.nred);
 }
 
 
@@ -98,38 +90,36 @@ __global__ void __launch_bounds__(kRThreads) var_columns_kernel(const __grid_con
     const int64_t j0 = chunk * p.chunk;
     const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
     const int last = a.kept.ndim - 1;
-    const bool single = a.red.ndim == 1;
-    auto red_off = [&](int64_t j) { return single ? j * a.red.strides[0] : decompose(a.red, j, a.red.ndim); };
     __shared__ double stage_mean[7][32 * VC];
     __shared__ double stage_m2[7][32 * VC];
     __shared__ double stage_n[8];
-    const int64_t xblocks = p.kouter * p.xtiles;
-    for (int64_t bx = blockIdx.x; bx < xblocks; bx += gridDim.x) {
-        const int64_t outer = bx / p.xtiles;
-        const int64_t tile = bx - outer * p.xtiles;
-        const int64_t c0 = tile * (32 * VC) + static_cast<int64_t>(tx) * VC;
-        const int64_t base = a.kept.offset + (last > 0 ? decompose(a.kept, outer, last) : 0);
-        const int64_t o0 = outer * p.ncols + c0;
-        const T *src = static_cast<const T *>(a.kept.data) + base + c0;
-        double n = 0.0, mean[VC], m2[VC];
+    // Grid: (kouter * xtiles, splits), one block per strip of 32 * VC outputs and chunk.
+    const int64_t outer = blockIdx.x / p.xtiles;
+    const int64_t tile = blockIdx.x - outer * p.xtiles;
+    const int64_t c0 = tile * (32 * VC) + static_cast<int64_t>(tx) * VC;
+    const int64_t base = a.kept.offset + (last > 0 ? decompose(a.kept, outer, last) : 0);
+    const int64_t o0 = outer * p.ncols + c0;
+    const T *src = static_cast<const T *>(a.kept.data) + base + c0;
+    double n = 0.0, mean[VC], m2[VC];
 #pragma unroll
-        for (int e = 0; e < VC; ++e) mean[e] = m2[e] = 0.0;
-        const bool in_range = c0 < p.ncols;
-        const bool whole = c0 + VC <= p.ncols;
-        if (in_range) {
-            int64_t j = j0 + ty;
-            for (; j + (UNR - 1) * 8 < j1; j += UNR * 8) {
+    for (int e = 0; e < VC; ++e) mean[e] = m2[e] = 0.0;
+    const bool in_range = c0 < p.ncols;
+    const bool whole = c0 + VC <= p.ncols;
+    if (in_range) {
+        const int64_t stride = a.red.strides[0];
+        const bool single = a.red.ndim == 1;
+        const bool walk = single && whole && (reinterpret_cast<uintptr_t>(src) & (alignof(RVec<T, VC>) - 1)) == 0 &&
+                          (stride * static_cast<int64_t>(sizeof(T))) % static_cast<int64_t>(alignof(RVec<T, VC>)) == 0;
+        auto red_off = [&](int64_t j) { return single ? j * stride : decompose(a.red, j, a.red.ndim); };
+        int64_t j = j0 + ty;
+        if (walk) {
+            // whole aligned vectors along one reduced dimension: batches of four rows, a pointer that steps by eight
+            const T *q = src + j * stride;
+            const int64_t step = 8 * stride;
+            for (; j + (UNR - 1) * 8 < j1; j += UNR * 8, q += UNR * step) {
                 RVec<T, VC> x[UNR];
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) {
-                    const T *q = src + red_off(j + u * 8);
-                    if (whole && (reinterpret_cast<uintptr_t>(q) & (alignof(RVec<T, VC>) - 1)) == 0) {
-                        x[u] = *reinterpret_cast<const RVec<T, VC> *>(q);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < VC; ++e) x[u].v[e] = c0 + e < p.ncols ? q[e] : T{};
-                    }
-                }
+                for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VC> *>(q + u * step);
                 const double total = n + UNR;
                 const double w = UNR / total;
 #pragma unroll
@@ -150,42 +140,41 @@ __global__ void __launch_bounds__(kRThreads) var_columns_kernel(const __grid_con
                 }
                 n = total;
             }
-            for (; j < j1; j += 8) {
-                const T *q = src + red_off(j);
-                const double total = n + 1.0;
-                const double w = 1.0 / total;
+        }
+        for (; j < j1; j += 8) {
+            const T *q = src + red_off(j);
+            const double total = n + 1.0;
+            const double w = 1.0 / total;
 #pragma unroll
-                for (int e = 0; e < VC; ++e) {
-                    if (c0 + e < p.ncols) {
-                        const double v = to_f64(q[e]);
-                        const double d = v - mean[e];
-                        mean[e] = n == 0.0 ? v : mean[e] + d * w;
-                        m2[e] = n == 0.0 ? 0.0 : m2[e] + d * d * n * w;
-                    }
+            for (int e = 0; e < VC; ++e) {
+                if (c0 + e < p.ncols) {
+                    const double v = to_f64(q[e]);
+                    const double d = v - mean[e];
+                    mean[e] = n == 0.0 ? v : mean[e] + d * w;
+                    m2[e] = n == 0.0 ? 0.0 : m2[e] + d * d * n * w;
                 }
-                n = total;
             }
+            n = total;
         }
-        if (ty > 0) {
+    }
+    if (ty > 0) {
 #pragma unroll
-            for (int e = 0; e < VC; ++e) {
-                stage_mean[ty - 1][tx * VC + e] = mean[e];
-                stage_m2[ty - 1][tx * VC + e] = m2[e];
-            }
+        for (int e = 0; e < VC; ++e) {
+            stage_mean[ty - 1][tx * VC + e] = mean[e];
+            stage_m2[ty - 1][tx * VC + e] = m2[e];
         }
-        if (tx == 0) stage_n[ty] = n;
-        __syncthreads();
-        if (ty == 0 && in_range) {
+    }
+    if (tx == 0) stage_n[ty] = n;
+    __syncthreads();
+    if (ty == 0 && in_range) {
 #pragma unroll
-            for (int e = 0; e < VC; ++e) {
-                if (c0 + e >= p.ncols) continue;
-                double cn = n, cm = mean[e], c2 = m2[e];
-                for (int w = 0; w < 7; ++w) merge_moments(cn, cm, c2, stage_n[w + 1], stage_mean[w][tx * VC + e], stage_m2[w][tx * VC + e]);
-                if (p.splits == 1) sink.put(o0 + e, c2, p.nred);
-                else static_cast<Moments *>(a.partials)[chunk * p.nout + o0 + e] = Moments{cm, c2};
-            }
+        for (int e = 0; e < VC; ++e) {
+            if (c0 + e >= p.ncols) continue;
+            double cn = n, cm = mean[e], c2 = m2[e];
+            for (int w = 0; w < 7; ++w) merge_moments(cn, cm, c2, stage_n[w + 1], stage_mean[w][tx * VC + e], stage_m2[w][tx * VC + e]);
+            if (p.splits == 1) sink.put(o0 + e, c2, p.nred);
+            else static_cast<Moments *>(a.partials)[chunk * p.nout + o0 + e] = Moments{cm, c2};
         }
-        __syncthreads();
     }
 }
 
@@ -319,8 +308,9 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
                 }
             }
             const int64_t per_block = kRThreads / p.group;
-            const int64_t tiles = (p.nout + per_block - 1) / per_block;
-            unsigned grid = clamp_grid(tiles, 1 << 20);
+            const int64_t blocks = (p.nout + per_block - 1) / per_block;
+            if (blocks > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
+            const unsigned grid = static_cast<unsigned>(blocks);
             if (p.group == 256) deviations_kernel<256, T><<<grid, kRThreads, 0, ctx->stream>>>(a, sink);
             else if (p.group == 32) deviations_kernel<32, T><<<grid, kRThreads, 0, ctx->stream>>>(a, sink);
             else deviations_kernel<1, T><<<grid, kRThreads, 0, ctx->stream>>>(a, sink);
@@ -328,7 +318,8 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
         }
         if constexpr (!std::is_same_v<T, double>) {
             if (p.kind == 1) {
-                dim3 grid(clamp_grid(p.kouter * p.xtiles, 1 << 20), static_cast<unsigned>(p.splits));
+                if (p.kouter * p.xtiles > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 strips of outputs");
+                dim3 grid(static_cast<unsigned>(p.kouter * p.xtiles), static_cast<unsigned>(p.splits));
                 var_columns_kernel<T><<<grid, kRThreads, 0, ctx->stream>>>(a, sink);
                 hmc_status s1 = launch_status("var kernel launch");
                 if (s1 != HMC_OK || p.splits == 1) return s1;

@@ -10,8 +10,8 @@ namespace hmc {
 ReducePlan make_reduce_plan(const hmc_tensor_desc &kept, const hmc_tensor_desc &red) {
     ReducePlan p{};
     const int es = element_size(kept.dtype);
-    p.vec = 16 / es;
-    p.vc = p.vec > 8 ? 8 : p.vec;
+    p.vec = 32 / es;
+    p.vc = 16 / es > 8 ? 8 : 16 / es;
     p.nout = desc_count(kept);
     p.nred = desc_count(red);
     p.row = red.ndim > 0 ? red.sizes[red.ndim - 1] : 1;
@@ -35,9 +35,10 @@ ReducePlan make_reduce_plan(const hmc_tensor_desc &kept, const hmc_tensor_desc &
         p.xtiles = ceil_div(p.ncols, 32 * p.vc);
         const int64_t blocks = p.kouter * p.xtiles;
         if (blocks < kTargetColumnBlocks) {
-            // as many chunks as still fit into one wave of blocks: equal blocks, no tail
-            const int64_t want = kTargetColumnBlocks / blocks;
-            const int64_t worth = p.nred / 64;
+            // chunks until there are enough blocks, as long as a block still reads a worthwhile amount
+            const int64_t want = ceil_div(kTargetColumnBlocks, blocks);
+            const int64_t strip_bytes = 32 * static_cast<int64_t>(p.vc) * es;
+            const int64_t worth = std::min(p.nred / 64, p.nred * strip_bytes / kColumnBlockBytes);
             p.splits = std::max<int64_t>(1, std::min({want, worth, kMaxSplits}));
         }
         p.chunk = ceil_div(p.nred, p.splits);
@@ -55,9 +56,9 @@ ReducePlan make_reduce_plan(const hmc_tensor_desc &kept, const hmc_tensor_desc &
         const int64_t worth = p.nred / (static_cast<int64_t>(p.group) * p.vec * 16);
         p.splits = std::max<int64_t>(1, std::min({want, worth, kMaxSplits}));
     }
-    p.simple = p.splits == 1 && p.group > 1 && red.ndim == 1 && p.step == 1 && p.nred % p.vec == 0 && p.nred < (int64_t{1} << 31);
+    p.simple = p.splits == 1 && p.group > 1 && red.ndim == 1 && p.step == 1 && p.nred % (16 / es) == 0 && p.nred < (int64_t{1} << 31);
     if (p.splits > 1) {
-        // Whole vectors per lane and chunk, so that only a range's two ends can be partial.
+        // Whole pieces per lane and chunk, so that only a range's two ends can be ragged.
         const int64_t unit = static_cast<int64_t>(p.group) * p.vec;
         p.chunk = ceil_div(ceil_div(p.nred, p.splits), unit) * unit;
         p.splits = ceil_div(p.nred, p.chunk);

@@ -1,7 +1,15 @@
 // Device discovery, contexts, error state and the ABI self-description.
 // Stands in for homura's csrc/runtime.hip on NVIDIA hardware.
+#include <cctype>
 #include <cstddef>
+#include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <vector>
+
+#if !defined(HMC_FAKE_CUDA)
+#include <nvtx3/nvToolsExt.h>
+#endif
 
 #include "common.cuh"
 
@@ -53,6 +61,136 @@ DeviceGuard::~DeviceGuard() {
     if (switched_) {
         if (cudaSetDevice(previous_) != cudaSuccess) cudaGetLastError();
     }
+}
+
+// ---- tracing ----
+struct TraceRecord {
+    char name[48];
+    cudaEvent_t start, stop;
+};
+struct TraceState {
+    std::vector<TraceRecord> records;
+    std::vector<cudaEvent_t> spare;
+};
+
+namespace {
+struct TraceConfig {
+    bool nvtx = false;
+    std::string log_path;
+    std::mutex log_mutex;
+};
+TraceConfig &trace_config() {
+    static TraceConfig config;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        if (const char *p = std::getenv("HMC_TIMING_LOG")) config.log_path = p;
+        if (const char *n = std::getenv("HMC_NVTX")) config.nvtx = n[0] != '\0' && n[0] != '0';
+    });
+    return config;
+}
+// "hmc_status hmc_unary(...)::<lambda()>" -> "hmc_unary"
+void entry_name(const char *pretty, char (&out)[48]) {
+    const char *p = std::strstr(pretty, "hmc_");
+    while (p != nullptr && std::strncmp(p, "hmc_status", 10) == 0) p = std::strstr(p + 10, "hmc_");
+    size_t n = 0;
+    if (p != nullptr) {
+        while (n + 1 < sizeof out && (std::isalnum(static_cast<unsigned char>(p[n])) || p[n] == '_')) {
+            out[n] = p[n];
+            ++n;
+        }
+    }
+    out[n] = '\0';
+}
+cudaEvent_t trace_event(TraceState *t) {
+    if (!t->spare.empty()) {
+        cudaEvent_t e = t->spare.back();
+        t->spare.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return e;
+}
+}  // namespace
+
+bool EntryTrace::enabled() {
+    static const bool on = trace_config().nvtx || !trace_config().log_path.empty();
+    return on;
+}
+
+void EntryTrace::begin(hmc_context *ctx, const char *pretty_function) {
+    // (tracing is an aid: a failure inside it switches the record off and never fails the entry)
+    try {
+        ctx_ = ctx;
+        active_ = true;
+        TraceRecord r{};
+        entry_name(pretty_function, r.name);
+#if !defined(HMC_FAKE_CUDA)
+        if (trace_config().nvtx) {
+            nvtxRangePushA(r.name);
+            range_ = true;
+        }
+#endif
+        if (!trace_config().log_path.empty()) {
+            if (ctx->trace == nullptr) ctx->trace = new TraceState();
+            r.start = trace_event(ctx->trace);
+            r.stop = trace_event(ctx->trace);
+            if (r.start != nullptr && r.stop != nullptr && cudaEventRecord(r.start, ctx->stream) == cudaSuccess) {
+                ctx->trace->records.push_back(r);
+                record_ = static_cast<int>(ctx->trace->records.size()) - 1;
+            } else {
+                cudaGetLastError();
+            }
+        }
+    } catch (...) {
+        record_ = -1;
+    }
+}
+
+void EntryTrace::end() {
+    if (record_ >= 0) {
+        if (cudaEventRecord(ctx_->trace->records[static_cast<size_t>(record_)].stop, ctx_->stream) != cudaSuccess) cudaGetLastError();
+    }
+#if !defined(HMC_FAKE_CUDA)
+    if (range_) nvtxRangePop();
+#endif
+}
+
+void flush_trace(hmc_context *ctx) {
+    if (ctx == nullptr || ctx->trace == nullptr || ctx->trace->records.empty()) return;
+    try {
+        TraceConfig &config = trace_config();
+        std::lock_guard<std::mutex> lock(config.log_mutex);
+        std::FILE *f = std::fopen(config.log_path.c_str(), "a");
+        for (TraceRecord &r : ctx->trace->records) {
+            float ms = 0.0f;
+            if (cudaEventElapsedTime(&ms, r.start, r.stop) != cudaSuccess) {
+                cudaGetLastError();
+                ms = -1.0f;  // (an entry that failed before its closing event was recorded)
+            }
+            if (f != nullptr) std::fprintf(f, "%s\t%.6f\n", r.name, static_cast<double>(ms));
+            ctx->trace->spare.push_back(r.start);
+            ctx->trace->spare.push_back(r.stop);
+        }
+        if (f != nullptr) std::fclose(f);
+        ctx->trace->records.clear();
+    } catch (...) {
+    }
+}
+
+void destroy_trace(hmc_context *ctx) {
+    if (ctx == nullptr || ctx->trace == nullptr) return;
+    for (TraceRecord &r : ctx->trace->records) {
+        cudaEventDestroy(r.start);
+        cudaEventDestroy(r.stop);
+    }
+    for (cudaEvent_t e : ctx->trace->spare) cudaEventDestroy(e);
+    cudaGetLastError();
+    delete ctx->trace;
+    ctx->trace = nullptr;
 }
 
 bool injected_data_failure(hmc_status &status) {
@@ -201,7 +339,7 @@ HMC_API hmc_status hmc_context_create(int32_t device, hmc_context_t *out) {
             t.fail_after_probe -= 1;
             return abandon(fail(HMC_OUT_OF_MEMORY, "out of host memory"));
         }
-        ctx = new (std::nothrow) hmc_context{device, stream, prop.multiProcessorCount};
+        ctx = new (std::nothrow) hmc_context{device, stream, prop.multiProcessorCount, nullptr};
         if (ctx == nullptr) return abandon(fail(HMC_OUT_OF_MEMORY, "out of host memory"));
         *out = ctx;
         return HMC_OK;
@@ -213,6 +351,11 @@ HMC_API hmc_status hmc_context_destroy(hmc_context_t ctx) {
         if (ctx == nullptr) return HMC_OK;
         DeviceGuard guard(ctx->device);
         if (guard.status() != HMC_OK) return guard.status();
+        if (ctx->trace != nullptr) {
+            if (cudaStreamSynchronize(ctx->stream) == cudaSuccess) flush_trace(ctx);
+            else cudaGetLastError();
+            destroy_trace(ctx);
+        }
         cudaError_t err = cudaStreamDestroy(ctx->stream);
         if (err == cudaSuccess) thread_state().live_streams -= 1;
         delete ctx;
@@ -227,6 +370,7 @@ HMC_API hmc_status hmc_context_synchronize(hmc_context_t ctx) {
         DeviceGuard guard(ctx->device);
         if (guard.status() != HMC_OK) return guard.status();
         HMC_CUDA(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+        flush_trace(ctx);
         return HMC_OK;
     });
 }

@@ -13,6 +13,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <string>
 
 #include "map.cuh"
 #include "math.cuh"
@@ -598,6 +599,124 @@ hmc_status launch_softmax_staged(hmc_context_t ctx, const SoftmaxArgs &a, bool l
     return launch_status("softmax kernel launch");
 }
 
+// ---- a few very long rows: three launches ----
+//
+// A row per block leaves most of the GPU idle when there are only a handful of rows, however long. Such
+// reductions are split like any other: (1) the rows' maxima by the reduction engine, whose plan cuts each row
+// into chunks until the GPU is full, (2) the rows' sums of exp(x - max) the same way, both kept in f64 in the
+// caller's workspace, (3) an elementwise pass over all elements that writes exp(x - max) / sum or
+// (x - max) - ln(sum). Three reads of the source instead of one, on every SM instead of on four.
+// (homura's ROCm layer splits the same way: csrc/reduce.hip:283-300, 348-361.)
+template <class TT>
+struct MaxSkippingNaN {
+    using T = TT;
+    using Acc = double;
+    __device__ __forceinline__ Acc init() const { return -CUDART_INF; }
+    __device__ __forceinline__ Acc load(T x, int64_t, int64_t) const { return to_f64(x); }
+    // (a NaN never wins the comparison: src/backend/cpu/misc.rs:25-30)
+    __device__ __forceinline__ Acc combine(Acc a, Acc b) const { return b > a ? b : a; }
+};
+template <class TT>
+struct ExpSum {
+    using T = TT;
+    using Acc = double;
+    const double *maxima;
+    double mx;
+    __device__ __forceinline__ Acc init() const { return 0.0; }
+    __device__ __forceinline__ Acc load(T x, int64_t o, int64_t) const {
+        return exp_shifted<T>(to_f64(x) - (maxima != nullptr ? maxima[o] : mx));
+    }
+    __device__ __forceinline__ ExpSum bound(int64_t o) const { return ExpSum{nullptr, maxima != nullptr ? maxima[o] : mx}; }
+    __device__ __forceinline__ Acc combine(Acc a, Acc b) const { return a + b; }
+};
+struct KeepF64 {
+    double *out;
+    __device__ __forceinline__ void put(int64_t o, double a, int64_t) const { out[o] = a; }
+};
+
+// Grid: (segments of a row, rows). A thread takes 16-byte vectors of its row when both sides allow.
+template <class T, bool LOG>
+__global__ void __launch_bounds__(kRThreads) softmax_normalize_kernel(const __grid_constant__ SoftmaxArgs a, const double *maxima,
+                                                                      const double *sums) {
+    constexpr int VEC = 16 / sizeof(T);
+    const T *src = static_cast<const T *>(a.src_rows.data);
+    T *dst = static_cast<T *>(a.out_rows.data);
+    for (int64_t r = blockIdx.y; r < a.nrows; r += gridDim.y) {
+        const T *ps = src + a.src_rows.offset + decompose(a.src_rows, r, a.src_rows.ndim);
+        T *po = dst + a.out_rows.offset + decompose(a.out_rows, r, a.out_rows.ndim);
+        const double mx = maxima[r], sum = sums[r];
+        const double log_sum = LOG ? log(sum) : 0.0;
+        constexpr bool kReciprocal = !std::is_same_v<T, double>;
+        const double inv = (!LOG && kReciprocal) ? 1.0 / sum : 0.0;
+        auto one = [&](T x) {
+            const double d = to_f64(x) - mx;
+            if constexpr (LOG) return from_f64<T>(d - log_sum);
+            else return from_f64<T>(kReciprocal ? exp_shifted<T>(d) * inv : exp_shifted<T>(d) / sum);
+        };
+        const bool vectors = a.si == 1 && a.so == 1 && (reinterpret_cast<uintptr_t>(ps) & 15) == 0 && (reinterpret_cast<uintptr_t>(po) & 15) == 0;
+        const int64_t nvec = vectors ? a.n / VEC : 0;
+        const int64_t stride = static_cast<int64_t>(gridDim.x) * kRThreads;
+        for (int64_t v = static_cast<int64_t>(blockIdx.x) * kRThreads + threadIdx.x; v < nvec; v += stride) {
+            const RVec<T, VEC> x = *reinterpret_cast<const RVec<T, VEC> *>(ps + v * VEC);
+            RVec<T, VEC> y;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) y.v[e] = one(x.v[e]);
+            *reinterpret_cast<RVec<T, VEC> *>(po + v * VEC) = y;
+        }
+        for (int64_t i = nvec * VEC + static_cast<int64_t>(blockIdx.x) * kRThreads + threadIdx.x; i < a.n; i += stride) {
+            po[i * a.so] = one(ps[i * a.si]);
+        }
+    }
+}
+
+// The rows as a reduction: kept = the rows' dimensions, reduced = the n elements of a row.
+void rows_as_reduction(const SoftmaxArgs &a, ReduceArgs &r) {
+    r.kept = a.src_rows;
+    r.red = hmc_tensor_desc{};
+    r.red.dtype = a.src_rows.dtype;
+    r.red.ndim = 1;
+    r.red.sizes[0] = a.n;
+    r.red.strides[0] = a.si;
+    r.plan = make_reduce_plan(r.kept, r.red);
+    r.partials = nullptr;
+}
+
+// Few rows, each long enough that cutting it fills the GPU better than a block per row does.
+bool split_rows_plan(int64_t nrows, int64_t n) { return nrows <= 128 && n >= (int64_t{1} << 16); }
+
+// Workspace of the split plan: the f64 maxima and sums (256-byte aligned blocks), then the reductions' partials.
+int64_t split_bytes(const SoftmaxArgs &a) {
+    ReduceArgs r;
+    rows_as_reduction(a, r);
+    const int64_t block = (a.nrows * 8 + 255) / 256 * 256;
+    return 2 * block + plan_partial_bytes(r.plan);
+}
+
+template <class T>
+hmc_status launch_softmax_split(hmc_context_t ctx, const SoftmaxArgs &a, bool log, void *workspace, int64_t workspace_bytes) {
+    const int64_t need = split_bytes(a);
+    if (workspace == nullptr || workspace_bytes < need) {
+        return fail(HMC_INVALID, "the workspace of softmax is too small: " + std::to_string(need) + " bytes needed");
+    }
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return fail(HMC_INVALID, "the workspace of softmax must be 16-byte aligned");
+    ReduceArgs r;
+    rows_as_reduction(a, r);
+    const int64_t block = (a.nrows * 8 + 255) / 256 * 256;
+    double *maxima = static_cast<double *>(workspace);
+    double *sums = reinterpret_cast<double *>(static_cast<char *>(workspace) + block);
+    r.partials = static_cast<char *>(workspace) + 2 * block;
+    hmc_status s = launch_reduce(r, MaxSkippingNaN<T>{}, KeepF64{maxima}, ctx->stream);
+    if (s != HMC_OK) return s;
+    s = launch_reduce(r, ExpSum<T>{maxima, 0.0}, KeepF64{sums}, ctx->stream);
+    if (s != HMC_OK) return s;
+    const int64_t per_row = ceil_div(ceil_div(a.n, 16 / static_cast<int64_t>(sizeof(T))), kRThreads * 4);
+    const int64_t want = ceil_div(static_cast<int64_t>(ctx->sm_count) * 8, a.nrows);
+    dim3 grid(clamp_grid(per_row < want ? per_row : want, 1 << 16), clamp_grid(a.nrows, 65535));
+    if (log) softmax_normalize_kernel<T, true><<<grid, kRThreads, 0, ctx->stream>>>(a, maxima, sums);
+    else softmax_normalize_kernel<T, false><<<grid, kRThreads, 0, ctx->stream>>>(a, maxima, sums);
+    return launch_status("softmax normalize kernel launch");
+}
+
 template <class T, int G, int CV>
 hmc_status launch_softmax_cv(hmc_context_t ctx, const SoftmaxArgs &a, bool log) {
     constexpr int P = kRThreads / G;
@@ -648,7 +767,13 @@ HMC_API hmc_status hmc_softmax_workspace(const hmc_tensor_desc *src_rows, int64_
         hmc_status s = check_desc(src_rows, "the rows");
         if (s != HMC_OK) return s;
         if (n < 0 || src_stride < 0) return fail(HMC_INVALID, "negative row length or stride");
-        *bytes = 0;  // both plans work in registers and caches
+        *bytes = 0;  // the other plans work in registers, shared memory and caches
+        int64_t nrows = 1;
+        for (int k = 0; k < src_rows->ndim; ++k) nrows *= src_rows->sizes[k];
+        if (dtype_is_float(src_rows->dtype) && nrows > 0 && split_rows_plan(nrows, n)) {
+            SoftmaxArgs a{*src_rows, *src_rows, nrows, n, src_stride, src_stride};
+            *bytes = split_bytes(a);
+        }
         return HMC_OK;
     });
 }
@@ -664,6 +789,14 @@ HMC_API hmc_status hmc_test_softmax_plan(const hmc_tensor_desc *src_rows, int64_
         *kind = p.kind;
         *group = p.group;
         *cache = p.cache;
+        int64_t nrows = 1;
+        for (int k = 0; k < src_rows->ndim; ++k) nrows *= src_rows->sizes[k];
+        if (nrows > 0 && split_rows_plan(nrows, n)) {
+            *kind = 3;
+            *group = 256;
+            *cache = 0;
+            return HMC_OK;
+        }
         if (src_rows->dtype != HMC_F64) {
             // the plan for rows like these when the output has the same layout: a warp per row, staged in shared memory
             SoftmaxArgs a{*src_rows, *src_rows, 1, n, src_stride, src_stride};
@@ -694,13 +827,12 @@ HMC_API hmc_status hmc_softmax(hmc_context_t ctx, const hmc_tensor_desc *out_row
         if (!dtype_is_float(src_rows->dtype) || out_rows->dtype != src_rows->dtype) {
             return fail(HMC_INVALID, "softmax takes a floating point tensor and writes its dtype");
         }
-        (void)workspace;
-        (void)workspace_bytes;
         if (nrows == 0 || n == 0) return HMC_OK;
         SoftmaxArgs a{*out_rows, *src_rows, nrows, n, out_stride, src_stride};
         const SoftmaxPlan p = softmax_plan(src_rows->dtype, n);
         return dispatch_float(src_rows->dtype, [&](auto t) -> hmc_status {
             using T = decltype(t);
+            if (split_rows_plan(nrows, n)) return launch_softmax_split<T>(ctx, a, log != 0, workspace, workspace_bytes);
             if constexpr (!std::is_same_v<T, double>) {
                 if (staged_rows<T>(a)) return launch_softmax_staged<T>(ctx, a, log != 0);
             }

@@ -21,6 +21,8 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
+import weakref
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -310,6 +312,8 @@ class CudaBackend:
             from .caching import CachingAllocator, CudaMemory
             allocator = CachingAllocator(CudaMemory(self.lib, device, self))
         self.allocator = allocator
+        self.debug = os.environ.get("HOMURA_CUDA_DEBUG", "") not in ("", "0")
+        self._guarded, self.guard_failures = {}, []
 
     # ---- plumbing ----
     def _check(self, status: int) -> None:
@@ -319,6 +323,7 @@ class CudaBackend:
     def close(self) -> None:
         if self.ctx is not None:
             self.synchronize()
+            self.check_guards()
             self.allocator.destroy()
             self._check(self.lib.hmc_context_destroy(self.ctx))
             self.ctx = None
@@ -326,9 +331,62 @@ class CudaBackend:
     def synchronize(self) -> None:
         self._check(self.lib.hmc_context_synchronize(self.ctx))
 
+    GUARD = 256          # bytes of guard band either side of a debug allocation
+    GUARD_BYTE = 0xA5
+
     def storage(self, nbytes: int) -> Storage:
-        block = self.allocator.allocate(nbytes)
-        return Storage(nbytes, ptr=block.ptr, device=self.device, owner=block)
+        """Device memory for a tensor or a workspace. In a debug run (environment variable HOMURA_CUDA_DEBUG=1) the
+        memory is poisoned with 0xFF bytes, so that an element nothing wrote shows as NaN / -1 / true (what homura's
+        debug builds do with their "uninit" memory, src/tensor/mod.rs:404-437), and sits between two guard bands
+        that :meth:`check_guards` (called by :meth:`close`, and when a storage is dropped) finds intact or not: the
+        stand-in for a memory checker on machines where none can run."""
+        if not self.debug:
+            block = self.allocator.allocate(nbytes)
+            return Storage(nbytes, ptr=block.ptr, device=self.device, owner=block)
+        g = self.GUARD
+        padded = (nbytes + 15) // 16 * 16
+        block = self.allocator.allocate(padded + 2 * g)
+        lib, ctx = self.lib, self.ctx
+        self._check(lib.hmc_memset(ctx, block.ptr, self.GUARD_BYTE, g))
+        if padded:
+            self._check(lib.hmc_memset(ctx, block.ptr + g, 0xFF, padded))
+        self._check(lib.hmc_memset(ctx, block.ptr + g + padded, self.GUARD_BYTE, g))
+        st = Storage(nbytes, ptr=block.ptr + g, device=self.device, owner=block)
+        self._guarded[id(st)] = (block.ptr, padded)
+        weakref.finalize(st, self._dropped, id(st))
+        return st
+
+    def _dropped(self, key: int) -> None:
+        entry = self._guarded.pop(key, None)
+        if entry is not None and self.ctx is not None:
+            bad = self._guard_damage(*entry)
+            if bad:
+                self.guard_failures.append(bad)
+
+    def _guard_damage(self, base: int, padded: int) -> str:
+        g = self.GUARD
+        band = np.empty(2 * g, dtype=np.uint8)
+        self._check(self.lib.hmc_copy_to_host(self.ctx, band.ctypes.data, base, g))
+        self._check(self.lib.hmc_copy_to_host(self.ctx, band.ctypes.data + g, base + g + padded, g))
+        hit = np.nonzero(band != self.GUARD_BYTE)[0]
+        if hit.size == 0:
+            return ""
+        first = int(hit[0])
+        where = f"{g - first} bytes before its start" if first < g else f"{first - g} bytes past its end"
+        return f"the allocation of {padded} bytes at {base + g:#x} was written {where} ({hit.size} guard bytes changed)"
+
+    def check_guards(self) -> None:
+        """Raises if a kernel wrote outside any live (or since dropped) debug allocation. No-op outside debug runs."""
+        if not self.debug:
+            return
+        found = list(self.guard_failures)
+        for base, padded in list(self._guarded.values()):
+            bad = self._guard_damage(base, padded)
+            if bad:
+                found.append(bad)
+        self.guard_failures.clear()
+        if found:
+            raise BackendError(ffi.HMC_INTERNAL_ERROR, "out-of-bounds write: " + "; ".join(found))
 
     def empty(self, shape, dtype: int) -> TensorData:
         shape = tuple(shape)

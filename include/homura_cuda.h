@@ -475,8 +475,8 @@ void hmc_abi_check(hmc_abi_info *out);
  * fail_data(n, oom): the next n data operations fail before queueing anything.
  * reduce_plan / softmax_plan: which plan the library picks, so tests can reach every path.
  *   reduce: kind (0 rows, 1 columns, 2 generic), splits of the reduced range, elements per split.
- *   softmax: kind (0 row in registers, 1 streaming, 2 row staged in shared memory by a warp), lanes per
- *   row, vectors a lane keeps.
+ *   softmax: kind (0 row in registers, 1 streaming, 2 row staged in shared memory by a warp, 3 few long
+ *   rows split into three launches), lanes per row, vectors a lane keeps.
  * live_streams: streams the thread created and has not destroyed. */
 void hmc_test_fail_stream_create(int32_t n);
 void hmc_test_fail_after_probe(int32_t n);

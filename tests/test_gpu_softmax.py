@@ -17,7 +17,7 @@ EPS64 = 2.0 ** -53
 
 SHAPES = [((64, 2048), 1), ((64, 2048), 0), ((7, 100), 1), ((300, 33), 1), ((5, 17, 9), 1), ((3, 40000), 1),
           ((2, 9000), 1), ((1031,), 0), ((4, 4100), 1), ((), 0), ((5, 1), 1), ((16, 8192), 1), ((16, 8200), 1),
-          ((13, 600), 1), ((600, 13), 0), ((6, 1001), 1), ((4, 4101), 1), ((3, 12288), 1), ((1000, 64), 1), ((9, 2048), 1)]
+          ((13, 600), 1), ((600, 13), 0), ((6, 1001), 1), ((4, 4101), 1), ((3, 12288), 1), ((1000, 64), 1), ((9, 2048), 1), ((3, 70001), 1), ((2, 1 << 17), 1), ((70000, 2), 0)]
 
 
 def check_softmax(got, want, dtype, n, what, log):
@@ -52,6 +52,7 @@ def test_softmax_on_every_plan(oracle, cuda, dtype):
     # aligned rows staged in shared memory by a warp
     assert {(0, 32), (0, 128), (0, 256), (1, 256)} <= kinds, kinds
     assert dtype == F64 or (2, 32) in kinds, kinds
+    assert (3, 256) in kinds, kinds  # few long rows: maxima, sums and the outputs in three launches
 
 
 def test_causal_mask_rows(oracle, cuda):
