@@ -761,6 +761,9 @@ def main() -> None:
     ap.add_argument("--c4-batch", type=int, default=256,
                     help="matrices of [2048, 2048] logits in the c4 workload (256 = [8, 32, 2048, 2048]); a smaller "
                          "number keeps a profiler capture short")
+    ap.add_argument("--c5-log2n", type=int, default=29,
+                    help="log2 of the elements of the flat c5 tensors (29 = one GPU's eighth of 2^32); smaller for short "
+                         "profiler captures")
     ap.add_argument("--c5-param-scale", type=int, default=1,
                     help="shrinks the rows of every AdamW tensor by this factor (for short profiler captures)")
     ap.add_argument("--profile", action="store_true",
@@ -793,7 +796,7 @@ def main() -> None:
         if name == "c4":
             return C4Workload(be, seed=rank, batch=args.c4_batch)
         if name == "c5":
-            return C5Workload(be, seed=rank, param_scale=args.c5_param_scale)
+            return C5Workload(be, seed=rank, log2n=args.c5_log2n, param_scale=args.c5_param_scale)
         return InputsWorkload(be, seed=rank)
 
     def finish():

@@ -23,6 +23,7 @@ struct hmc_context {
     cudaStream_t stream;
     int32_t sm_count;
     hmc::TraceState *trace;  // per-call timing records, when the timing log is on (else null)
+    int *status;             // a word in device memory that a kernel sets when one of its bounded waits runs out
 };
 
 struct hmc_event {

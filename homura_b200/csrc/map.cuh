@@ -849,6 +849,12 @@ __global__ void __launch_bounds__(kThreads, HMC_TILE_MIN_BLOCKS) map_tile_kernel
     async_copy_wait(0);
 }
 
+}  // namespace hmc
+
+#include "transpose16.cuh"
+
+namespace hmc {
+
 // One operand of a launch: a description, or (for inputs) a constant given by its bits.
 struct MapOperand {
     const hmc_tensor_desc *desc = nullptr;
@@ -868,6 +874,36 @@ hmc_status check_operands(const hmc_tensor_desc *const *descs, int n, int64_t *c
 // constant false). `vec` and `unr` are those of the functor.
 void build_map_args(MapArgs &a, const hmc_tensor_desc *out, const MapOperand *inputs, int ninputs, int vec, int unr);
 
+// Queues transpose16_kernel for the layout in `a` when it qualifies (alignment of both sides); false: not taken.
+template <class F>
+bool launch_transpose16(hmc_context_t ctx, const MapArgs &a, const F &f, hmc_status &status) {
+    if (ctx->status == nullptr) return false;
+    const int da = a.ndim - 2, db = a.ndim - 1;
+    const int64_t size_a = a.sizes[da], size_b = a.sizes[db], outer = a.ndim == 3 ? a.sizes[0] : 1;
+    CUtensorMap in_map, out_map;
+    if (!t16_encode_map(&in_map, a.base[1], size_a, size_b, outer, a.strides[1][db], a.ndim == 3 ? a.strides[1][0] : 0)) return false;
+    if (!t16_encode_map(&out_map, a.base[0], size_b, size_a, outer, a.strides[0][da], a.ndim == 3 ? a.strides[0][0] : 0)) return false;
+    Transpose16Args args;
+    args.tiles_a = ceil_div(size_a, kT16Tile);
+    args.tiles_b = ceil_div(size_b, kT16Tile);
+    args.tiles = outer * args.tiles_a * args.tiles_b;
+    static bool raised[kTileKnownDevices] = {};
+    if (ctx->device >= kTileKnownDevices || !raised[ctx->device]) {
+        cudaError_t err = cudaFuncSetAttribute(transpose16_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(kT16SharedBytes));
+        if (err != cudaSuccess) {
+            status = cuda_fail(err, "cudaFuncSetAttribute");
+            return true;
+        }
+        if (ctx->device < kTileKnownDevices) raised[ctx->device] = true;
+    }
+    const int64_t resident = static_cast<int64_t>(ctx->sm_count) * 4;  // four blocks of 49 KB share an SM
+    const unsigned grid = static_cast<unsigned>(args.tiles < resident ? args.tiles : resident);
+    transpose16_kernel<F><<<grid, kT16Threads, kT16SharedBytes, ctx->stream>>>(in_map, out_map, args, f, ctx->status);
+    status = launch_status("transposing kernel launch");
+    return true;
+}
+
 template <class F>
 hmc_status launch_map(hmc_context_t ctx, const F &f, const hmc_tensor_desc *out, const MapOperand *inputs, int ninputs) {
     MapArgs a;
@@ -882,6 +918,15 @@ hmc_status launch_map(hmc_context_t ctx, const F &f, const hmc_tensor_desc *out,
             dim3 grid(static_cast<unsigned>(ceil_div(lean.n0, chunk)), static_cast<unsigned>(lean.rows < 65535 ? lean.rows : 65535));
             map_lean_kernel<F><<<grid, kThreads, 0, ctx->stream>>>(lean, f);
             return launch_status("elementwise kernel launch");
+        }
+    }
+    if constexpr (sizeof(typename F::Out) == 2 && size_or_zero<typename F::A>() == 2 && std::is_same_v<typename F::B, Unused> &&
+                  std::is_same_v<typename F::C, Unused>) {
+        // one transposed input of 2-byte elements, two or three dimensions: the copy engine and the matrix
+        // load / store instructions do the transposition
+        if (a.tile_mask == 2u && a.constant_mask == 0 && (a.ndim == 2 || a.ndim == 3)) {
+            hmc_status done = HMC_OK;
+            if (launch_transpose16<F>(ctx, a, f, done)) return done;
         }
     }
     if (a.tile_mask != 0) {

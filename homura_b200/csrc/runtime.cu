@@ -326,10 +326,15 @@ HMC_API hmc_status hmc_context_create(int32_t device, hmc_context_t *out) {
         err = cudaGetLastError();
         if (err == cudaSuccess) err = cudaMemcpyAsync(&answer, slot, sizeof answer, cudaMemcpyDeviceToHost, stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
-        cudaError_t free_err = cudaFree(slot);
-        if (err != cudaSuccess) return abandon(cuda_fail(err, "probe kernel"));
-        if (free_err != cudaSuccess) return abandon(cuda_fail(free_err, "probe: cudaFree"));
-        if (answer != kProbeWord) return abandon(fail(HMC_CUDA_ERROR, "probe kernel wrote the wrong value"));
+        // The probe's word stays with the context as its status word (zero: nothing to report).
+        if (err == cudaSuccess) err = cudaMemsetAsync(slot, 0, sizeof(uint32_t), stream);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+        auto abandon_slot = [&](hmc_status status) {
+            if (cudaFree(slot) != cudaSuccess) cudaGetLastError();
+            return abandon(status);
+        };
+        if (err != cudaSuccess) return abandon_slot(cuda_fail(err, "probe kernel"));
+        if (answer != kProbeWord) return abandon_slot(fail(HMC_CUDA_ERROR, "probe kernel wrote the wrong value"));
         // The scratch array of hmc_reduce_noalloc: looking up its address now makes the runtime load the module
         // that holds it while this call is allocating anyway. A failure here is not the context's: the entry point
         // looks the address up again when it is first used.
@@ -337,10 +342,10 @@ HMC_API hmc_status hmc_context_create(int32_t device, hmc_context_t *out) {
         hmc_context *ctx = nullptr;
         if (t.fail_after_probe > 0) {
             t.fail_after_probe -= 1;
-            return abandon(fail(HMC_OUT_OF_MEMORY, "out of host memory"));
+            return abandon_slot(fail(HMC_OUT_OF_MEMORY, "out of host memory"));
         }
-        ctx = new (std::nothrow) hmc_context{device, stream, prop.multiProcessorCount, nullptr};
-        if (ctx == nullptr) return abandon(fail(HMC_OUT_OF_MEMORY, "out of host memory"));
+        ctx = new (std::nothrow) hmc_context{device, stream, prop.multiProcessorCount, nullptr, reinterpret_cast<int *>(slot)};
+        if (ctx == nullptr) return abandon_slot(fail(HMC_OUT_OF_MEMORY, "out of host memory"));
         *out = ctx;
         return HMC_OK;
     });
@@ -356,6 +361,7 @@ HMC_API hmc_status hmc_context_destroy(hmc_context_t ctx) {
             else cudaGetLastError();
             destroy_trace(ctx);
         }
+        if (ctx->status != nullptr && cudaFree(ctx->status) != cudaSuccess) cudaGetLastError();
         cudaError_t err = cudaStreamDestroy(ctx->stream);
         if (err == cudaSuccess) thread_state().live_streams -= 1;
         delete ctx;
@@ -371,6 +377,16 @@ HMC_API hmc_status hmc_context_synchronize(hmc_context_t ctx) {
         if (guard.status() != HMC_OK) return guard.status();
         HMC_CUDA(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
         flush_trace(ctx);
+        if (ctx->status != nullptr) {
+            // kernels that wait on barriers give up after a bounded number of polls and say so here
+            int word = 0;
+            HMC_CUDA(cudaMemcpyAsync(&word, ctx->status, sizeof word, cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync (status)");
+            HMC_CUDA(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+            if (word != 0) {
+                HMC_CUDA(cudaMemsetAsync(ctx->status, 0, sizeof word, ctx->stream), "cudaMemsetAsync (status)");
+                return fail(HMC_CUDA_ERROR, "a kernel gave up a bounded wait on the device: results queued before this call are incomplete");
+            }
+        }
         return HMC_OK;
     });
 }

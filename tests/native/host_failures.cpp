@@ -320,7 +320,7 @@ void allocator_release_and_retry() {
     fake::malloc_failures = 1;
     uint64_t other = 0;
     CHECK(hmc_allocator_allocate(a, 16u << 20, &other, &size) == HMC_OK);
-    CHECK(fake::frees == frees + 1 && fake::synchronizes == syncs + 1 && fake::mallocs == mallocs + 2);
+    CHECK(fake::frees == frees + 1 && fake::synchronizes > syncs && fake::mallocs == mallocs + 2);
     CHECK(hmc_allocator_stats(a, &st) == HMC_OK);
     CHECK(st.allocated == (16u << 20) && st.reserved == (16u << 20));
     CHECK(fake::last_error == cudaSuccess);
