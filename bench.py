@@ -18,6 +18,8 @@ a write-only flush a read-only kernel is charged the write-back of the flush buf
 shows the difference on its first kernel):
     c3  reductions of f32 / i32 [16384, 4096] (sum, mean, var over rows and columns, max + argmax, full sums)
     c4  softmax / log_softmax of causally masked f32 [8, 32, 2048, 2048], row mean of squares of bf16 [32768, 4096]
+    fused  the headline expression silu(x) * scale + bias, contiguous and on x.t(), as one kernel each (6 bytes per
+        element instead of 14, the three kernels' bits)
     c5  one GPU's eighth of the sharded configuration: a * b + c on flat f32 2^29, its sum and maximum, and an
         AdamW step (lr 1e-4, wd 0.01) over the 291 Llama-3-8B-shaped f32 tensors (1/8 of the rows of each,
         1 003 782 656 parameters, one launch) with the gradient norm
@@ -172,6 +174,36 @@ class Workload:
             ("mul_scale_t", lambda: be.binary(ffi.HMC_BINARY_MUL, self.st, self.st, scale_t)),
             ("add_bias_t", lambda: be.binary_promoted(ffi.HMC_BINARY_ADD, self.yt, self.st, bias_t)),
             ("cast", lambda: be.copy(self.c, self.x)),
+        ]
+
+    def step(self):
+        for _, f in self.ops():
+            f()
+
+
+class FusedWorkload:
+    """The headline expression y = silu(x) * scale + bias, and the same on x.t(), each as ONE kernel that keeps the two
+    intermediates in registers and rounds them where the three kernels would (same bits): 6 bytes per element (read x,
+    write the f32 result) instead of the 14 the three-kernel form moves."""
+
+    name = "c2_fused_expression_bf16_8192x8192"
+    dtype = "bf16"
+
+    def __init__(self, be, rows: int = ROWS, cols: int = COLS, seed: int = 0):
+        w = Workload(be, rows, cols, seed)
+        self.w, self.be = w, be
+        n = rows * cols
+        self.op_bytes = {"silu_mul_add": 6 * n + 2 * cols + 4 * rows, "silu_mul_add_t": 6 * n + 2 * rows + 4 * cols}
+        self.launches_per_step = 2
+
+    def ops(self):
+        from homura_b200 import ffi
+        be, w = self.be, self.w
+        r, c = w.rows, w.cols
+        args = (ffi.HMC_UNARY_SILU, ffi.HMC_BINARY_MUL, ffi.HMC_BINARY_ADD)
+        return [
+            ("silu_mul_add", lambda: be.unary_binary_binary(*args, w.y, w.x, w.scale, w.bias)),
+            ("silu_mul_add_t", lambda: be.unary_binary_binary(*args, w.yt, w.x.t(), w.scale.reshape(c, 1), w.bias.reshape(1, r))),
         ]
 
     def step(self):
@@ -755,7 +787,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="all", choices=["all", "c2", "c3", "c4", "c5", "inputs"],
+    ap.add_argument("--workload", default="all", choices=["all", "c2", "c3", "c4", "c5", "fused", "inputs"],
                     help="all (default): the headline with the c3 / c4 / c5 records (and the sharded record with several "
                          "ranks); c2: the headline alone; another name: that workload's record alone")
     ap.add_argument("--c4-batch", type=int, default=256,
@@ -795,6 +827,8 @@ def main() -> None:
             return C3Workload(be, seed=rank)
         if name == "c4":
             return C4Workload(be, seed=rank, batch=args.c4_batch)
+        if name == "fused":
+            return FusedWorkload(be, seed=rank)
         if name == "c5":
             return C5Workload(be, seed=rank, log2n=args.c5_log2n, param_scale=args.c5_param_scale)
         return InputsWorkload(be, seed=rank)
@@ -847,7 +881,7 @@ def main() -> None:
     workloads, sharded = {}, None
     if args.workload == "all":
         with ClockSampler(local) as clocks2:
-            names = ["c3", "c4", "c5"] if world == 1 else ["c5"]   # c3 / c4 do not shard: measured on one GPU only
+            names = ["fused", "c3", "c4", "c5"] if world == 1 else ["c5"]   # the others do not shard: one GPU only
             for name in names:
                 wl = make(name)
                 workloads[name] = workload_record(runner, wl, max(3, args.steps // 4), args.warmup)

@@ -253,39 +253,48 @@ __device__ __forceinline__ void fold_run(const Op &op, typename Op::Acc &acc, co
             // same pieces again with the general step.
             if (w < w_whole) {
                 constexpr bool kMax = extreme_is_max<Op>::value;
-                const typename Op::Acc before = acc;
                 const int64_t w_first = w;
                 T best = p[w * N];
                 auto best_key = order_key(best);
-                int64_t best_at = w * N;
+                uint32_t best_at = 0;  // the element's place among those this lane takes: piece count * N + e
+                uint32_t count = 0;
                 float alarm = 0.0f;
-                auto take = [&](const Piece<T> &x, int64_t at) {
+                auto take = [&](const Piece<T> &x) {
+                    if constexpr (Tr<T>::kind == kFloat) {
+                        float sum = static_cast<float>(order_key(x.v[0]));
+#pragma unroll
+                        for (int e = 1; e < N; ++e) sum += static_cast<float>(order_key(x.v[e]));
+                        alarm += sum;
+                    }
 #pragma unroll
                     for (int e = 0; e < N; ++e) {
                         const auto k = order_key(x.v[e]);
-                        if constexpr (Tr<T>::kind == kFloat) alarm += static_cast<float>(k);
                         const bool better = kMax ? k > best_key : k < best_key;
                         best_key = better ? k : best_key;
                         best = better ? x.v[e] : best;
-                        best_at = better ? at + e : best_at;
+                        best_at = better ? count + e : best_at;
                     }
+                    count += N;
                 };
-                for (; w + (U - 1) * G < w_whole; w += U * G) {
-                    Piece<T> x[U];
+                // (a lane takes fewer than 2^32 elements of a run: longer runs fall back to the general step below)
+                if ((w_whole - w_first) / G < (int64_t{1} << 31) / N) {
+                    for (; w + (U - 1) * G < w_whole; w += U * G) {
+                        Piece<T> x[U];
 #pragma unroll
-                    for (int u = 0; u < U; ++u) x[u] = load_piece(p + (w + u * G) * N);
+                        for (int u = 0; u < U; ++u) x[u] = load_piece(p + (w + u * G) * N);
 #pragma unroll
-                    for (int u = 0; u < U; ++u) take(x[u], (w + u * G) * N);
-                }
-                for (; w < w_whole; w += G) take(load_piece(p + w * N), w * N);
-                if (alarm == alarm) {
-                    acc = op.combine(acc, typename Op::Acc{best, first + best_at});
-                } else {
-                    acc = before;
-                    for (int64_t v = w_first; v < w_whole; v += G) {
-                        const Piece<T> x = load_piece(p + v * N);
+                        for (int u = 0; u < U; ++u) take(x[u]);
+                    }
+                    for (; w < w_whole; w += G) take(load_piece(p + w * N));
+                    if (alarm == alarm) {
+                        const int64_t piece = w_first + static_cast<int64_t>(best_at / N) * G;
+                        acc = op.combine(acc, typename Op::Acc{best, first + piece * N + best_at % N});
+                    } else {
+                        for (int64_t v = w_first; v < w_whole; v += G) {
+                            const Piece<T> x = load_piece(p + v * N);
 #pragma unroll
-                        for (int e = 0; e < N; ++e) acc = fold_step(op, acc, x.v[e], o, first + v * N + e);
+                            for (int e = 0; e < N; ++e) acc = fold_step(op, acc, x.v[e], o, first + v * N + e);
+                        }
                     }
                 }
             }
@@ -339,9 +348,10 @@ __device__ __forceinline__ typename Op::Acc fold_span(const Op &op, const Reduce
 }
 
 // kind 0. Grid: (teams of outputs, chunks), every block launched at once: block (x, y) folds chunk y of the
-// 256 / G outputs x * (256 / G) ...
+// 256 / G outputs x * (256 / G) ... (Four blocks share an SM; max / min, whose lanes carry a candidate beside
+// the loads in flight, get the registers of two.)
 template <int G, class Op, class Sink>
-__global__ void __launch_bounds__(kRThreads) reduce_rows_kernel(const __grid_constant__ ReduceArgs a, const Op op, const Sink sink) {
+__global__ void __launch_bounds__(kRThreads, is_extreme<Op>::value ? 2 : 4) reduce_rows_kernel(const __grid_constant__ ReduceArgs a, const Op op, const Sink sink) {
     using Acc = typename Op::Acc;
     constexpr int kTeams = kRThreads / G;
     const ReducePlan &p = a.plan;

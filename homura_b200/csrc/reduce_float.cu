@@ -57,14 +57,17 @@ __global__ void __launch_bounds__(kRThreads) deviations_kernel(const __grid_cons
 }
 
 
-// ---- variance over columns in one pass ----
-// The layout of reduce_columns_kernel (a thread owns VC adjacent outputs, the 8 warps of a block take the reduced
-// indices j, j + 8, ...), but instead of a pass for the means and a pass for the deviations a thread keeps
-// (count, mean, M2 = sum of squared deviations from that mean) per output and merges batches of four rows into
-// them with the pairwise update of Chan, Golub and LeVeque: the batch's own mean and M2 first (exact two-pass
-// on its B values), then mean += d * B / n, M2 += M2_batch + d * d * (n - B) * B / n with d = batch mean - mean.
-// All in f64: the result differs from the two-pass value by a few f64 ulps, far below the rounding to F16,
-// BF16 or F32 (F64 tensors keep the two passes). One read of the source instead of two.
+// ---- variance in one pass ----
+// The CPU takes two passes (the mean, then the squared deviations from it, src/backend/cpu/reduce.rs:135-170).
+// One pass is enough when the deviations are taken from a nearby constant instead: with c the first value a thread
+// meets, d = x - c, s = sum of d and q = sum of d * d, the sum of squared deviations from the true mean is
+// M2 = q - s * s / n and the mean is c + s / n. Because c is one of the values, (mean - c)^2 is at most M2, so
+// q = M2 + n (mean - c)^2 <= (n + 1) M2: the subtraction cancels at most log2(n + 1) bits of an f64, which leaves
+// 30 and more for ranges up to 2^20 values per thread where F16, BF16 and F32 results need 24 (F64 tensors keep
+// the two passes). Four f64 operations an element (widen, subtract, add, fused multiply-add), none of them
+// waiting for the previous element's result except its own running sum. The moments (count, mean, M2) of
+// threads, warps and chunks are then merged pairwise in a fixed order with the update of Chan, Golub and
+// LeVeque: mean += d n_b / n, M2 += M2_b + d^2 n_a n_b / n with d = mean_b - mean.
 struct Moments {
     double mean, m2;
 };
@@ -81,9 +84,9 @@ __device__ __forceinline__ void merge_moments(double &n, double &mean, double &m
 }
 
 template <class T>
-__global__ void __launch_bounds__(kRThreads) var_columns_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+__global__ void __launch_bounds__(kRThreads, 2) var_columns_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
     constexpr int VC = (16 / sizeof(T)) > 8 ? 8 : (16 / sizeof(T));
-    constexpr int UNR = 4;  // rows of a batch, all in flight at once (8 measured slower: registers)
+    constexpr int UNR = 8;  // loads in flight per thread
     const ReducePlan &p = a.plan;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int64_t chunk = blockIdx.y;
@@ -105,56 +108,61 @@ __global__ void __launch_bounds__(kRThreads) var_columns_kernel(const __grid_con
     for (int e = 0; e < VC; ++e) mean[e] = m2[e] = 0.0;
     const bool in_range = c0 < p.ncols;
     const bool whole = c0 + VC <= p.ncols;
-    if (in_range) {
+    if (in_range && j0 + ty < j1) {
         const int64_t stride = a.red.strides[0];
         const bool single = a.red.ndim == 1;
         const bool walk = single && whole && (reinterpret_cast<uintptr_t>(src) & (alignof(RVec<T, VC>) - 1)) == 0 &&
                           (stride * static_cast<int64_t>(sizeof(T))) % static_cast<int64_t>(alignof(RVec<T, VC>)) == 0;
         auto red_off = [&](int64_t j) { return single ? j * stride : decompose(a.red, j, a.red.ndim); };
         int64_t j = j0 + ty;
+        // the shift of each column: the first value this thread meets
+        double shift[VC], s[VC], q[VC];
+        {
+            const T *first = src + red_off(j);
+#pragma unroll
+            for (int e = 0; e < VC; ++e) {
+                shift[e] = c0 + e < p.ncols ? to_f64(first[e]) : 0.0;
+                s[e] = q[e] = 0.0;
+            }
+        }
         if (walk) {
-            // whole aligned vectors along one reduced dimension: batches of four rows, a pointer that steps by eight
-            const T *q = src + j * stride;
+            // whole aligned vectors along one reduced dimension: a pointer that steps by eight rows, UNR loads in flight
+            const T *ptr = src + j * stride;
             const int64_t step = 8 * stride;
-            for (; j + (UNR - 1) * 8 < j1; j += UNR * 8, q += UNR * step) {
+            for (; j + (UNR - 1) * 8 < j1; j += UNR * 8, ptr += UNR * step) {
                 RVec<T, VC> x[UNR];
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VC> *>(q + u * step);
-                const double total = n + UNR;
-                const double w = UNR / total;
+                for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VC> *>(ptr + u * step);
 #pragma unroll
-                for (int e = 0; e < VC; ++e) {
-                    double v[UNR];
+                for (int u = 0; u < UNR; ++u) {
 #pragma unroll
-                    for (int u = 0; u < UNR; ++u) v[u] = to_f64(x[u].v[e]);
-                    double sum = 0.0;
-#pragma unroll
-                    for (int u = 0; u < UNR; ++u) sum += v[u];
-                    const double mb = sum * (1.0 / UNR);
-                    double sq = 0.0;
-#pragma unroll
-                    for (int u = 0; u < UNR; ++u) sq += (v[u] - mb) * (v[u] - mb);
-                    const double d = mb - mean[e];
-                    mean[e] = n == 0.0 ? mb : mean[e] + d * w;
-                    m2[e] = n == 0.0 ? sq : m2[e] + sq + d * d * n * w;
+                    for (int e = 0; e < VC; ++e) {
+                        const double d = to_f64(x[u].v[e]) - shift[e];
+                        s[e] += d;
+                        q[e] = __fma_rn(d, d, q[e]);
+                    }
                 }
-                n = total;
+                n += UNR;
             }
         }
         for (; j < j1; j += 8) {
-            const T *q = src + red_off(j);
-            const double total = n + 1.0;
-            const double w = 1.0 / total;
+            const T *row = src + red_off(j);
 #pragma unroll
             for (int e = 0; e < VC; ++e) {
                 if (c0 + e < p.ncols) {
-                    const double v = to_f64(q[e]);
-                    const double d = v - mean[e];
-                    mean[e] = n == 0.0 ? v : mean[e] + d * w;
-                    m2[e] = n == 0.0 ? 0.0 : m2[e] + d * d * n * w;
+                    const double d = to_f64(row[e]) - shift[e];
+                    s[e] += d;
+                    q[e] = __fma_rn(d, d, q[e]);
                 }
             }
-            n = total;
+            n += 1.0;
+        }
+        const double inv = 1.0 / n;
+#pragma unroll
+        for (int e = 0; e < VC; ++e) {
+            mean[e] = shift[e] + s[e] * inv;
+            const double spread = q[e] - s[e] * s[e] * inv;
+            m2[e] = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);  // (rounding may leave -0.0...; a NaN stays)
         }
     }
     if (ty > 0) {
@@ -197,89 +205,80 @@ __global__ void __launch_bounds__(kRThreads) var_combine_kernel(const __grid_con
 }
 
 // ---- variance over rows in one pass ----
-// The same moments for rows that are one unit-stride run of whole, aligned vectors (plan.simple): a lane merges
-// batches of up to four vectors (exact two-pass moments of the 16 or 32 values in registers) into its
-// (count, mean, M2), the lanes of a row are merged in lane order by shuffles and, for 256 lanes, the warps in
-// warp order through shared memory. The row is read once; the two-pass kernel above reads it twice and misses
-// the caches for part of the second walk.
-template <class T, int N>
-__device__ __forceinline__ void batch_moments(const double (&v)[N], double &mean_b, double &m2_b) {
-    double s = 0.0;
-#pragma unroll
-    for (int i = 0; i < N; ++i) s += v[i];
-    mean_b = s * (1.0 / N);
-    double sq = 0.0;
-#pragma unroll
-    for (int i = 0; i < N; ++i) sq += (v[i] - mean_b) * (v[i] - mean_b);
-    m2_b = sq;
-}
-
+// The same for rows that are one unit-stride run of whole, aligned vectors (plan.simple): a lane takes the shift
+// from its first element and keeps one (s, q) pair per position within a vector, so that consecutive elements add
+// to different running sums; the pairs share the shift and simply add up. The lanes of a row are merged in lane
+// order by shuffles and, for 256 lanes, the warps in warp order through shared memory. The row is read once; the
+// two-pass kernel above reads it twice and misses the caches for part of the second walk.
+// Grid: one block per 256 / G rows.
 template <int G, class T>
 __global__ void __launch_bounds__(kRThreads) var_rows_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
-    constexpr int P = kRThreads / G;
+    constexpr int kTeams = kRThreads / G;
     constexpr int VEC = 16 / sizeof(T);
     constexpr int UNR = 4;
     const ReducePlan &p = a.plan;
     const int lane = threadIdx.x % G;
-    const int slot = threadIdx.x / G;
     __shared__ double warp_n[8], warp_mean[8], warp_m2[8];
     const uint32_t nvec = static_cast<uint32_t>(p.nred) / VEC;
-    const int64_t tiles = (p.nout + P - 1) / P;
-    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-        const int64_t o = tile * P + slot;
-        const bool valid = o < p.nout;
-        double n = 0.0, mean = 0.0, m2 = 0.0;
-        if (valid) {
-            const T *row = static_cast<const T *>(a.kept.data) + a.kept.offset + decompose(a.kept, o, a.kept.ndim);
-            uint32_t v = lane;
-            for (; v + (UNR - 1) * G < nvec; v += UNR * G) {
-                RVec<T, VEC> x[UNR];
+    const int64_t o = static_cast<int64_t>(blockIdx.x) * kTeams + threadIdx.x / G;
+    const bool live = o < p.nout;
+    double n = 0.0, mean = 0.0, m2 = 0.0;
+    if (live && static_cast<uint32_t>(lane) < nvec) {
+        const T *row = static_cast<const T *>(a.kept.data) + a.kept.offset + decompose(a.kept, o, a.kept.ndim);
+        const double shift = to_f64(row[static_cast<size_t>(lane) * VEC]);
+        double s[VEC], q[VEC];
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VEC> *>(row + static_cast<size_t>(v + u * G) * VEC);
-                double w[UNR * VEC];
+        for (int e = 0; e < VEC; ++e) s[e] = q[e] = 0.0;
+        auto take = [&](const RVec<T, VEC> &x) {
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) {
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) w[u * VEC + e] = to_f64(x[u].v[e]);
-                }
-                double mb, sq;
-                batch_moments<T, UNR * VEC>(w, mb, sq);
-                merge_moments(n, mean, m2, static_cast<double>(UNR * VEC), mb, sq);
+            for (int e = 0; e < VEC; ++e) {
+                const double d = to_f64(x.v[e]) - shift;
+                s[e] += d;
+                q[e] = __fma_rn(d, d, q[e]);
             }
-            for (; v < nvec; v += G) {
-                const RVec<T, VEC> x = *reinterpret_cast<const RVec<T, VEC> *>(row + static_cast<size_t>(v) * VEC);
-                double w[VEC];
+        };
+        uint32_t v = lane, taken = 0;
+        for (; v + (UNR - 1) * G < nvec; v += UNR * G, taken += UNR) {
+            RVec<T, VEC> x[UNR];
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) w[e] = to_f64(x.v[e]);
-                double mb, sq;
-                batch_moments<T, VEC>(w, mb, sq);
-                merge_moments(n, mean, m2, static_cast<double>(VEC), mb, sq);
-            }
+            for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VEC> *>(row + static_cast<size_t>(v + u * G) * VEC);
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) take(x[u]);
         }
-        if constexpr (G > 1) {
+        for (; v < nvec; v += G, ++taken) take(*reinterpret_cast<const RVec<T, VEC> *>(row + static_cast<size_t>(v) * VEC));
+        double st = s[0], qt = q[0];
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) {
-                const double on = __shfl_down_sync(0xFFFFFFFFu, n, d);
-                const double om = __shfl_down_sync(0xFFFFFFFFu, mean, d);
-                const double o2 = __shfl_down_sync(0xFFFFFFFFu, m2, d);
-                merge_moments(n, mean, m2, on, om, o2);
-            }
+        for (int e = 1; e < VEC; ++e) {
+            st += s[e];
+            qt += q[e];
         }
-        if constexpr (G == 256) {
-            const int warp = threadIdx.x >> 5;
-            if ((threadIdx.x & 31) == 0) {
-                warp_n[warp] = n;
-                warp_mean[warp] = mean;
-                warp_m2[warp] = m2;
-            }
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                for (int w = 1; w < 8; ++w) merge_moments(n, mean, m2, warp_n[w], warp_mean[w], warp_m2[w]);
-            }
-            __syncthreads();
-        }
-        if (lane == 0 && valid) sink.put(o, m2, p.nred);
+        n = static_cast<double>(taken) * VEC;
+        mean = shift + st / n;
+        const double spread = qt - st * st / n;
+        m2 = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);
     }
+    if constexpr (G > 1) {
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const double on = __shfl_down_sync(0xFFFFFFFFu, n, d);
+            const double om = __shfl_down_sync(0xFFFFFFFFu, mean, d);
+            const double o2 = __shfl_down_sync(0xFFFFFFFFu, m2, d);
+            merge_moments(n, mean, m2, on, om, o2);
+        }
+    }
+    if constexpr (G == 256) {
+        const int warp = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) {
+            warp_n[warp] = n;
+            warp_mean[warp] = mean;
+            warp_m2[warp] = m2;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < 8; ++w) merge_moments(n, mean, m2, warp_n[w], warp_mean[w], warp_m2[w]);
+        }
+    }
+    if (lane == 0 && live) sink.put(o, m2, p.nred);
 }
 
 }  // namespace
@@ -301,7 +300,8 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
                 for (int k = 0; k < a.kept.ndim; ++k) aligned = aligned && (a.kept.strides[k] * static_cast<int64_t>(sizeof(T))) % 16 == 0;
                 if (aligned) {
                     const int64_t per = kRThreads / p.group;
-                    const unsigned g = clamp_grid((p.nout + per - 1) / per, 1 << 20);
+                    if ((p.nout + per - 1) / per > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
+                    const unsigned g = static_cast<unsigned>((p.nout + per - 1) / per);
                     if (p.group == 256) var_rows_kernel<256, T><<<g, kRThreads, 0, ctx->stream>>>(a, sink);
                     else var_rows_kernel<32, T><<<g, kRThreads, 0, ctx->stream>>>(a, sink);
                     return launch_status("var kernel launch");

@@ -454,6 +454,15 @@ class CudaBackend:
             return
         self._check(self.lib.hmc_binary_promoted(self.ctx, op, d[0], d[1], d[2]))
 
+    def unary_binary_binary(self, unary_op: int, first_op: int, second_op: int, out: TensorData, x: TensorData,
+                            b: TensorData, c: TensorData) -> None:
+        """out = (unary(x) first_op b) second_op c in one kernel with the three kernels' roundings; b and c
+        broadcast to out's shape."""
+        d = descs("unary_binary_binary", [out, x.expand(out.shape), b.expand(out.shape), c.expand(out.shape)])
+        if d is None:
+            return
+        self._check(self.lib.hmc_unary_binary_binary(self.ctx, unary_op, first_op, second_op, d[0], d[1], d[2], d[3]))
+
     def binary_constant(self, op: int, out: TensorData, a: TensorData, value, constant_first: bool) -> None:
         bits = scalar_bits(value, a.dtype)
         d = descs("binary_constant", [out, a])

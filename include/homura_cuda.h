@@ -385,6 +385,17 @@ hmc_status hmc_reduce_noalloc(hmc_context_t ctx, int32_t op, const hmc_tensor_de
 hmc_status hmc_binary_promoted(hmc_context_t ctx, int32_t op, const hmc_tensor_desc *out,
                                const hmc_tensor_desc *a, const hmc_tensor_desc *b);
 
+/* out = (unary(x) first_op b) second_op c in one kernel, with the roundings of the three elementwise kernels
+ * homura's front end would issue for it (src/ops/unary.rs:18-57, src/ops/binary.rs:70-143): unary(x) and the
+ * first binary result are rounded to the dtype T of x and b, then both operands of the second op are converted to
+ * the promoted dtype of (T, dtype of c), which `out` has. The output has the bits of hmc_unary, hmc_binary and
+ * hmc_binary_promoted run one after the other, with neither intermediate written to memory. unary_op: RELU, EXP,
+ * TANH, SIGMOID, SILU, GELU or GELU_TANH; the binary ops: ADD, SUB or MUL; T: F16, BF16 or F32 with c of the same
+ * dtype, or F16 / BF16 with an F32 c. Operands broadcast by stride 0 as everywhere. */
+hmc_status hmc_unary_binary_binary(hmc_context_t ctx, int32_t unary_op, int32_t first_op, int32_t second_op,
+                                   const hmc_tensor_desc *out, const hmc_tensor_desc *x,
+                                   const hmc_tensor_desc *b, const hmc_tensor_desc *c);
+
 /* Scalars of one AdamW step (src/optim/adam.rs:125-171), each already rounded to the parameter
  * dtype's computation type by the caller, as the op-by-op path rounds them. */
 typedef struct hmc_adamw_scalars {

@@ -46,9 +46,9 @@ def test_poison_and_guard_bands():
         be.copy(t, x.t())
         be.synchronize()
         be.check_guards()
-        # a destination described two elements longer than its storage: the write lands in the guard band
-        small = be.empty((10,), F32)
-        lying = TensorData(small.storage, F32, (12,), (1,))
+        # a destination described four elements longer than its storage: the write lands in the guard band
+        small = be.empty((12,), F32)
+        lying = TensorData(small.storage, F32, (16,), (1,))
         be.fill(lying, 1.0)
         be.synchronize()
         try:

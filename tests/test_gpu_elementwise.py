@@ -313,3 +313,39 @@ def test_unsupported_combinations_are_refused(cuda):
         cuda.binary(ffi.HMC_BINARY_SUB, cuda.empty((8,), BOOL), b, b)
     with pytest.raises(BackendError):
         cuda.binary(99, out, x, x)
+
+
+@pytest.mark.parametrize("dtypes", [(BF16, F32), (F16, F32), (BF16, BF16), (F16, F16), (F32, F32)],
+                         ids=["bf16+f32", "f16+f32", "bf16", "f16", "f32"])
+def test_unary_binary_binary_in_one_kernel_has_the_three_kernels_bits(oracle, cuda, dtypes):
+    """(unary(x) op b) op c fused: the bits of hmc_unary, hmc_binary and the promoting binary run one after the other
+    on the GPU, and of the CPU checker's three steps wherever the unary step has the CPU's bits; contiguous
+    operands, a row and a column broadcast, and a transposed x."""
+    t, tc = dtypes
+    rows, cols = 300, 520
+    x_raw = f64_to_storage(uniform(rows * cols, 6.0, 71), t)
+    b_raw = f64_to_storage(uniform(cols, 2.0, 72), t)
+    c_raw = f64_to_storage(uniform(rows, 3.0, 73), tc)
+    (ox, gx), (ob, gb), (oc, gc) = (both(oracle, cuda, x_raw, t, (rows, cols)), both(oracle, cuda, b_raw, t, (1, cols)),
+                                    both(oracle, cuda, c_raw, tc, (rows, 1)))
+    names = {"relu": ffi.HMC_UNARY_RELU, "exp": ffi.HMC_UNARY_EXP, "tanh": ffi.HMC_UNARY_TANH, "sigmoid": ffi.HMC_UNARY_SIGMOID,
+             "silu": ffi.HMC_UNARY_SILU, "gelu": ffi.HMC_UNARY_GELU, "gelu_tanh": ffi.HMC_UNARY_GELU_TANH}
+    binops = {"add": ffi.HMC_BINARY_ADD, "sub": ffi.HMC_BINARY_SUB, "mul": ffi.HMC_BINARY_MUL}
+    for uname, first, second in (("silu", "mul", "add"), ("gelu_tanh", "add", "mul"), ("tanh", "sub", "sub"), ("relu", "mul", "add"),
+                                 ("exp", "mul", "sub"), ("sigmoid", "add", "add"), ("gelu", "mul", "mul")):
+        def steps(u, b, c):
+            un = u.gelu("none") if uname == "gelu" else (u.gelu("tanh") if uname == "gelu_tanh" else getattr(u, uname)())
+            return getattr(getattr(un, first)(b), second)(c)
+        want_gpu = steps(gx, gb, gc)
+        out = cuda.empty((rows, cols), want_gpu.dtype)
+        cuda.unary_binary_binary(names[uname], binops[first], binops[second], out, gx.data, gb.data, gc.data)
+        assert_bitwise(cuda.download(out), want_gpu.raw(), want_gpu.dtype, f"{uname} {first} {second}: one kernel vs three")
+        # the same on x.t() (the tiled kernel with three inputs)
+        gxt = T(cuda, cuda.upload(np.ascontiguousarray(x_raw.reshape(rows, cols).T), t, (cols, rows))).view(lambda d: d.t())
+        cuda.unary_binary_binary(names[uname], binops[first], binops[second], out, gxt.data, gb.data, gc.data)
+        assert_bitwise(cuda.download(out), want_gpu.raw(), want_gpu.dtype, f"{uname} {first} {second}: transposed x")
+        if t == F32 and uname != "gelu":
+            # f32 unary steps are the CPU's bits, so the whole chain is
+            assert_bitwise(cuda.download(out), steps(ox, ob, oc).raw(), want_gpu.dtype, f"{uname} {first} {second}: vs the CPU's three steps")
+    with pytest.raises(Exception):
+        cuda.unary_binary_binary(ffi.HMC_UNARY_LOG, ffi.HMC_BINARY_ADD, ffi.HMC_BINARY_ADD, out, gx.data, gb.data, gc.data)
