@@ -518,13 +518,16 @@ class Runner:
         for _ in range(warmup):
             w.step()
         out = []
+        self.host_ms_per_region = []  # how long the host took to queue a region (well below the region: not host-bound)
         start, stop = self.ev.new(), self.ev.new()
         for _ in range(repeats):
             self.barrier()
+            t0 = time.perf_counter()
             self.ev.record(start)
             for _ in range(steps):
                 w.step()
             self.ev.record(stop)
+            self.host_ms_per_region.append((time.perf_counter() - t0) * 1e3)
             self.be.synchronize()
             out.append(self.ev.elapsed(start, stop))
         self.barrier()
@@ -549,23 +552,37 @@ class Runner:
             be.reduce(ffi.HMC_REDUCE_SUM, self.scratch_sum, TensorData(self.scratch, U8, (self.scratch.nbytes,), (1,)), [True])
 
     def flushed_per_op(self, ops, reps: int = 10, warm: int = 3, read_back: bool = True) -> dict:
-        """Mean ms of each op alone, the L2 emptied before every launch (see flush)."""
+        """Mean ms of each op alone, the L2 emptied before every launch (see flush).
+
+        The host must not be what is timed: an op whose launch reaches the stream after the flush before it has
+        finished shows the host's delay as device time between its two events (seen here as a constant 8 us on the ops
+        whose Python glue also asks for a workspace). So all iterations of an op are queued without waiting in between,
+        each behind a flush that is longer on the device (the buffer is written twice) than an iteration takes to
+        queue; the warm-up iterations absorb the start. The record carries both rates so that this can be checked."""
         ev = self.ev
         per_op = {}
-        a, b = ev.new(), ev.new()
+        pairs = [(ev.new(), ev.new()) for _ in range(warm + reps)]
+        self.host_ms_per_iteration, self.device_ms_per_iteration = 0.0, float("inf")
+        self.queue_rates = {}
         for name, f in ops:
-            times = []
-            for i in range(warm + reps):
+            self.be.synchronize()
+            t0 = time.perf_counter()
+            for i, (a, b) in enumerate(pairs):
+                self.flush(i + 1, read_back=False)
                 self.flush(i, read_back)
                 ev.record(a)
                 f()
                 ev.record(b)
-                t_ms = ev.elapsed(a, b)
-                if i >= warm:
-                    times.append(t_ms)
-            per_op[name] = float(np.mean(times))
-        ev.destroy(a)
-        ev.destroy(b)
+            host_ms = (time.perf_counter() - t0) * 1e3 / len(pairs)
+            self.be.synchronize()
+            device_ms = ev.elapsed(pairs[0][0], pairs[-1][1]) / (len(pairs) - 1)
+            self.queue_rates[name] = (host_ms, device_ms)
+            self.host_ms_per_iteration = max(self.host_ms_per_iteration, host_ms)
+            self.device_ms_per_iteration = min(self.device_ms_per_iteration, device_ms)
+            per_op[name] = float(np.mean([ev.elapsed(a, b) for a, b in pairs[warm:]]))
+        for a, b in pairs:
+            ev.destroy(a)
+            ev.destroy(b)
         return per_op
 
 
@@ -589,6 +606,8 @@ def workload_record(runner: Runner, w, steps: int, warmup: int) -> dict:
     """One `workloads` entry: every kernel alone with L2 flushed (the honest per-kernel figures, and their sum as
     the step), plus the same step back to back."""
     per_op = runner.flushed_per_op(w.ops())
+    rates = (runner.host_ms_per_iteration, runner.device_ms_per_iteration)
+    queue_rates = dict(runner.queue_rates)
     per_op = dict(zip(per_op.keys(), runner.max_over_ranks(per_op.values())))
     regions = runner.timed_steps(w, steps, warmup, 3)
     step_bytes = sum(w.op_bytes.values())
@@ -601,6 +620,8 @@ def workload_record(runner: Runner, w, steps: int, warmup: int) -> dict:
     flush_note = {"op": first[0][0], "ms_after_write_then_read_flush": per_op[first[0][0]], "ms_after_write_only_flush": write_only,
                   "note": "a flush that only writes leaves the L2 full of modified lines whose write-back is then charged to the "
                           "timed kernel; the figures of this record are taken after a flush that writes and reads back"}
+    flush_note["host_ms_to_queue_an_iteration"], flush_note["device_ms_per_iteration"] = rates
+    flush_note["host_and_device_ms_per_iteration_by_op"] = queue_rates
     return {"workload": w.name, "dtype": w.dtype, "metric": METRIC, "unit": UNIT, "flush": flush_note,
             "value": step_bytes / (flushed_ms * 1e-3) / 1e9, "ms_per_step": flushed_ms,
             "value_basis": "sum of the kernels' times, each alone with L2 flushed before it",
@@ -869,6 +890,7 @@ def main() -> None:
         per_op = dict(zip(per_op.keys(), runner.max_over_ranks(per_op.values())))
         launches += w.launches_per_step * 13
     ms = float(np.median(regions))
+    host_ms_per_region = float(np.median(runner.host_ms_per_region))
     value = STEP_BYTES * args.steps * world / (ms * 1e-3) / 1e9
     peak, peak_kind = peaks()
     r = roofline_of(w, per_op, NCU_TRAFFIC_BYTES)
@@ -909,7 +931,8 @@ def main() -> None:
             "repeats": {"n": len(regions), "steps_each": args.steps, "value_is": "median",
                         "gbs_median": value, "gbs_best": STEP_BYTES * args.steps * world / (min(regions) * 1e-3) / 1e9,
                         "gbs_worst": STEP_BYTES * args.steps * world / (max(regions) * 1e-3) / 1e9,
-                        "ms_per_step_all": [t / args.steps for t in regions]},
+                        "ms_per_step_all": [t / args.steps for t in regions],
+                        "host_ms_to_queue_a_region": host_ms_per_region, "device_ms_per_region": ms},
             "clocks": clocks.summary(),
             "e2e": e2e,
             "gpu_launches": 7 * args.steps * len(regions),

@@ -17,6 +17,8 @@
 
 namespace hmc {
 struct TraceState;
+constexpr int kTickets = 1024;       // counters per context
+constexpr int kTicketsOffset = 64;   // words between the status word and the first counter (same allocation)
 }
 struct hmc_context {
     int32_t device;
@@ -24,6 +26,8 @@ struct hmc_context {
     int32_t sm_count;
     hmc::TraceState *trace;  // per-call timing records, when the timing log is on (else null)
     int *status;             // a word in device memory that a kernel sets when one of its bounded waits runs out
+    unsigned *tickets;       // hmc::kTickets counters in device memory, zero between kernels: the blocks of a reduction that
+                             // share partials count themselves off on one, and the last resets it
 };
 
 struct hmc_event {

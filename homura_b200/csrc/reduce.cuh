@@ -23,8 +23,12 @@
 //    and are combined in warp order through shared memory. Global loads are fully coalesced.
 //
 // When the outputs alone cannot fill the GPU, the reduced range is cut into `splits` chunks; each
-// chunk writes a 16-byte partial per output into the caller's workspace and a second kernel folds
-// the partials of an output in chunk order.
+// chunk writes a partial per output into the caller's workspace (slots of 16 bytes are reserved) and the
+// partials of an output are folded in an order that depends on the plan alone. Who folds them: the block
+// that finishes last among those sharing blockIdx.x (each takes a ticket from a counter of the context
+// when its partials are written; the one that draws the last ticket resets the counter and folds), so that
+// no second launch is paid; or, when a block would have too many partials to fold by itself or there are
+// more blocks along x than counters, a second kernel. Both fold in the same order.
 //
 // Accumulators follow homura's CPU fold (src/backend/cpu/reduce.rs:42-131): floats in f64,
 // integers wrapping in i64, extremes as (value, index) with "first NaN, then first of equals".
@@ -55,7 +59,7 @@ struct ReducePlan {
     int64_t row, step;  // last reduced dimension: size and source stride
     int64_t splits, chunk;
     int64_t ncols, kouter, xtiles;  // kind 1: last kept size, product of the others, column tiles
-    // kind 0, no chunks, and every output folds one unit-stride run of whole 16-byte vectors (nred < 2^31): what the
+    // kind 0, no chunks, and every output folds one unit-stride run of whole 32-byte pieces (nred < 2^31): what the
     // one-pass variance kernel for rows requires.
     int32_t simple;
 };
@@ -65,6 +69,7 @@ struct ReduceArgs {
     hmc_tensor_desc red;
     ReducePlan plan;
     void *partials;
+    unsigned *tickets;  // the context's counters (kTickets of them, all zero between kernels), or null
 };
 
 inline int64_t desc_count(const hmc_tensor_desc &d) {
@@ -116,6 +121,63 @@ __device__ __forceinline__ Acc shuffle_down(Acc v, int delta) {
         memcpy(&v, w, 16);
     }
     return v;
+}
+
+// ---- partials ----
+// A partial that another block wrote, read past this SM's L1.
+template <class Acc>
+__device__ __forceinline__ Acc load_partial(const Acc *p) {
+    static_assert(sizeof(Acc) == 4 || sizeof(Acc) == 8 || sizeof(Acc) == 16, "accumulator size");
+    Acc v;
+    if constexpr (sizeof(Acc) == 4) {
+        const unsigned w = __ldcg(reinterpret_cast<const unsigned *>(p));
+        memcpy(&v, &w, 4);
+    } else if constexpr (sizeof(Acc) == 8) {
+        const unsigned long long w = __ldcg(reinterpret_cast<const unsigned long long *>(p));
+        memcpy(&v, &w, 8);
+    } else {
+        const ulonglong2 w = __ldcg(reinterpret_cast<const ulonglong2 *>(p));
+        memcpy(&v, &w, 16);
+    }
+    return v;
+}
+
+// Called by every thread of a block once the block's partials are stored: true in the block that is the last of
+// the gridDim.y blocks sharing blockIdx.x to get here, which may then read all their partials. (No block waits
+// for another: a block that is not the last simply leaves.)
+__device__ __forceinline__ bool drew_last_ticket(unsigned *tickets) {
+    __shared__ bool last;
+    __threadfence();  // this thread's partials are visible to the device before the ticket is
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned mine = atomicAdd(&tickets[blockIdx.x], 1u);
+        last = mine + 1 == gridDim.y;
+        if (last) tickets[blockIdx.x] = 0;  // everybody has drawn: ready for the next kernel
+    }
+    __syncthreads();
+    const bool result = last;
+    if (result) __threadfence();
+    return result;
+}
+
+// The partials of output o folded in chunk order by one thread, eight loads in flight.
+template <class Op>
+__device__ __forceinline__ typename Op::Acc fold_partials_in_order(const Op &op, const typename Op::Acc *partials, int64_t o,
+                                                                   int64_t nout, int64_t splits) {
+    using Acc = typename Op::Acc;
+    Acc acc = op.init();
+    for (int64_t c0 = 0; c0 < splits; c0 += 8) {
+        Acc x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (c0 + u < splits) x[u] = load_partial(partials + (c0 + u) * nout + o);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (c0 + u < splits) acc = op.combine(acc, x[u]);
+        }
+    }
+    return acc;
 }
 
 // ---- teams ----
@@ -347,11 +409,35 @@ __device__ __forceinline__ typename Op::Acc fold_span(const Op &op, const Reduce
     return acc;
 }
 
+// A lane's share of the partials of output o: chunks lane, lane + G, ... in order (a single lane: all, in order).
+template <int G, class Op>
+__device__ __forceinline__ typename Op::Acc team_partials(const Op &op, const typename Op::Acc *partials, int64_t o, bool live,
+                                                          int lane, const ReducePlan &p) {
+    using Acc = typename Op::Acc;
+    if constexpr (G == 1) {
+        return live ? fold_partials_in_order(op, partials, o, p.nout, p.splits) : op.init();
+    } else {
+        Acc acc = op.init();
+        if (live) {
+            int64_t c = lane;
+            for (; c + 3 * G < p.splits; c += 4 * G) {
+                Acc x[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) x[u] = load_partial(partials + (c + u * G) * p.nout + o);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc = op.combine(acc, x[u]);
+            }
+            for (; c < p.splits; c += G) acc = op.combine(acc, load_partial(partials + c * p.nout + o));
+        }
+        return acc;
+    }
+}
+
 // kind 0. Grid: (teams of outputs, chunks), every block launched at once: block (x, y) folds chunk y of the
 // 256 / G outputs x * (256 / G) ... (Four blocks share an SM; max / min, whose lanes carry a candidate beside
 // the loads in flight, get the registers of two.)
 template <int G, class Op, class Sink>
-__global__ void __launch_bounds__(kRThreads, is_extreme<Op>::value ? 2 : 4) reduce_rows_kernel(const __grid_constant__ ReduceArgs a, const Op op, const Sink sink) {
+__global__ void __launch_bounds__(kRThreads, is_extreme<Op>::value ? 3 : 4) reduce_rows_kernel(const __grid_constant__ ReduceArgs a, const Op op, const Sink sink) {
     using Acc = typename Op::Acc;
     constexpr int kTeams = kRThreads / G;
     const ReducePlan &p = a.plan;
@@ -366,17 +452,22 @@ __global__ void __launch_bounds__(kRThreads, is_extreme<Op>::value ? 2 : 4) redu
         acc = fold_span<G>(op, a, o, a.kept.offset + decompose(a.kept, o, a.kept.ndim), j0, j1, lane);
     }
     acc = fold_team<G>(op, acc);
-    if (lane == 0 && live) {
-        if (p.splits == 1) sink.put(o, acc, p.nred);
-        else static_cast<Acc *>(a.partials)[chunk * p.nout + o] = acc;
+    if (p.splits == 1) {
+        if (lane == 0 && live) sink.put(o, acc, p.nred);
+        return;
     }
+    Acc *partials = static_cast<Acc *>(a.partials);
+    if (lane == 0 && live) partials[chunk * p.nout + o] = acc;
+    if (a.tickets == nullptr || !drew_last_ticket(a.tickets)) return;
+    acc = fold_team<G>(op, team_partials<G>(op, partials, o, live, lane, p));
+    if (lane == 0 && live) sink.put(o, acc, p.nred);
 }
 
 // kind 1. Grid: (kouter * xtiles, splits), every block launched at once; block 32 x 8: thread (tx, ty) owns the VC
 // adjacent outputs tx * VC .. of its strip of 32 * VC outputs and folds the reduced indices j0 + ty, j0 + ty + 8, ...
 // of its chunk; the eight warps are then folded in warp order through shared memory.
 template <class Op, class Sink>
-__global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_constant__ ReduceArgs a, const Op op,
+__global__ void __launch_bounds__(kRThreads, is_extreme<Op>::value ? 2 : 4) reduce_columns_kernel(const __grid_constant__ ReduceArgs a, const Op op,
                                                                    const Sink sink) {
     using T = typename Op::T;
     using Acc = typename Op::Acc;
@@ -445,6 +536,7 @@ __global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_
         for (int e = 0; e < VC; ++e) stage[ty - 1][tx * VC + e] = acc[e];
     }
     __syncthreads();
+    Acc *partials = static_cast<Acc *>(a.partials);
     if (ty == 0 && in_range) {
 #pragma unroll
         for (int e = 0; e < VC; ++e) {
@@ -452,8 +544,15 @@ __global__ void __launch_bounds__(kRThreads) reduce_columns_kernel(const __grid_
             Acc r = acc[e];
             for (int w = 0; w < 7; ++w) r = op.combine(r, stage[w][tx * VC + e]);
             if (p.splits == 1) sink.put(o0 + e, r, p.nred);
-            else static_cast<Acc *>(a.partials)[chunk * p.nout + o0 + e] = r;
+            else partials[chunk * p.nout + o0 + e] = r;
         }
+    }
+    if (p.splits == 1 || a.tickets == nullptr || !drew_last_ticket(a.tickets)) return;
+    // the strip's outputs, one per thread
+    const int64_t c = tile * (32 * VC) + threadIdx.x;
+    if (threadIdx.x < 32 * VC && c < p.ncols) {
+        const int64_t o = outer * p.ncols + c;
+        sink.put(o, fold_partials_in_order(op, partials, o, p.nout, p.splits), p.nred);
     }
 }
 
@@ -467,14 +566,14 @@ __global__ void __launch_bounds__(kRThreads) reduce_combine_kernel(const __grid_
     const Acc *partials = static_cast<const Acc *>(a.partials);
     const int lane = threadIdx.x % L;
     const int64_t o = static_cast<int64_t>(blockIdx.x) * (kRThreads / L) + threadIdx.x / L;
-    Acc acc = op.init();
-    if (o < p.nout) {
-#pragma unroll 4
-        for (int64_t c = lane; c < p.splits; c += L) acc = op.combine(acc, partials[c * p.nout + o]);
-    }
-    acc = fold_team<L>(op, acc);
-    if (lane == 0 && o < p.nout) sink.put(o, acc, p.nred);
+    const bool live = o < p.nout;
+    const Acc acc = fold_team<L>(op, team_partials<L>(op, partials, o, live, lane, p));
+    if (lane == 0 && live) sink.put(o, acc, p.nred);
 }
+
+// The number of partials up to which the block that finishes last folds them itself: a thread per output takes
+// them one after another (columns, single-lane rows), a team shares them (32- and 256-lane rows).
+constexpr int64_t kSelfFoldSplits = 32;
 
 inline unsigned clamp_grid(int64_t n, int64_t cap) { return static_cast<unsigned>(n < cap ? (n < 1 ? 1 : n) : cap); }
 
@@ -484,24 +583,27 @@ hmc_status launch_reduce(const ReduceArgs &a, const Op &op, const Sink &sink, cu
     static_assert(sizeof(typename Op::Acc) <= kPartialBytes, "accumulator too large for a partial");
     const ReducePlan &p = a.plan;
     if (p.nout == 0) return HMC_OK;
+    // the lanes that share an output's partials (part of the fold order, so a function of the plan alone)
+    const int lanes = p.kind == 0 ? p.group : (p.splits > kSelfFoldSplits ? 32 : 1);
+    ReduceArgs args = a;
+    const int64_t blocks_x = p.kind == 1 ? p.kouter * p.xtiles : (p.nout + kRThreads / p.group - 1) / (kRThreads / p.group);
+    const bool self_fold = p.splits > 1 && a.tickets != nullptr && blocks_x <= kTickets &&
+                           (p.kind == 0 ? (p.group > 1 || p.splits <= kSelfFoldSplits) : lanes == 1);
+    if (!self_fold) args.tickets = nullptr;
     if (p.kind == 1) {
-        if (p.kouter * p.xtiles > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 strips of outputs");
-        dim3 grid(static_cast<unsigned>(p.kouter * p.xtiles), static_cast<unsigned>(p.splits));
-        reduce_columns_kernel<Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        if (blocks_x > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 strips of outputs");
+        dim3 grid(static_cast<unsigned>(blocks_x), static_cast<unsigned>(p.splits));
+        reduce_columns_kernel<Op, Sink><<<grid, kRThreads, 0, stream>>>(args, op, sink);
     } else {
-        const int64_t teams = kRThreads / p.group;
-        const int64_t blocks = (p.nout + teams - 1) / teams;
-        if (blocks > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
-        dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(p.splits));
-        if (p.group == 256) reduce_rows_kernel<256, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
-        else if (p.group == 32) reduce_rows_kernel<32, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
-        else reduce_rows_kernel<1, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        if (blocks_x > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
+        dim3 grid(static_cast<unsigned>(blocks_x), static_cast<unsigned>(p.splits));
+        if (p.group == 256) reduce_rows_kernel<256, Op, Sink><<<grid, kRThreads, 0, stream>>>(args, op, sink);
+        else if (p.group == 32) reduce_rows_kernel<32, Op, Sink><<<grid, kRThreads, 0, stream>>>(args, op, sink);
+        else reduce_rows_kernel<1, Op, Sink><<<grid, kRThreads, 0, stream>>>(args, op, sink);
     }
     hmc_status s = launch_status("reduction kernel launch");
     if (s != HMC_OK) return s;
-    if (p.splits > 1) {
-        // a few outputs with very many partials each (a full reduction): a block per output; many partials: a warp
-        const int lanes = (p.splits >= 512 && p.nout <= 64) ? 256 : (p.splits >= 64 ? 32 : 1);
+    if (p.splits > 1 && !self_fold) {
         const int64_t blocks = (p.nout + kRThreads / lanes - 1) / (kRThreads / lanes);
         if (blocks > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
         const unsigned grid = static_cast<unsigned>(blocks);

@@ -68,9 +68,12 @@ __global__ void __launch_bounds__(kRThreads) deviations_kernel(const __grid_cons
 // waiting for the previous element's result except its own running sum. The moments (count, mean, M2) of
 // threads, warps and chunks are then merged pairwise in a fixed order with the update of Chan, Golub and
 // LeVeque: mean += d n_b / n, M2 += M2_b + d^2 n_a n_b / n with d = mean_b - mean.
-struct Moments {
+struct alignas(16) Moments {
     double mean, m2;
 };
+// Blocks of the column kernel that share an SM: four for f32 (four columns a thread); the half types' eight columns a
+// thread need the registers of three.
+template <class T> constexpr int kVarColumnBlocks = sizeof(T) == 4 ? 4 : 3;
 static_assert(sizeof(Moments) == kPartialBytes, "the moments of a chunk are one partial");
 
 __device__ __forceinline__ void merge_moments(double &n, double &mean, double &m2, double nb, double mean_b, double m2_b) {
@@ -83,8 +86,30 @@ __device__ __forceinline__ void merge_moments(double &n, double &mean, double &m
     n = total;
 }
 
+// The chunks' moments of output o merged in chunk order by one thread (a chunk's count follows from the plan),
+// eight loads in flight.
+__device__ __forceinline__ double merged_m2(const Moments *partials, int64_t o, const ReducePlan &p) {
+    double n = 0.0, mean = 0.0, m2 = 0.0;
+    for (int64_t c0 = 0; c0 < p.splits; c0 += 8) {
+        Moments m[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (c0 + u < p.splits) m[u] = load_partial(partials + (c0 + u) * p.nout + o);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (c0 + u < p.splits) {
+                const int64_t j0 = (c0 + u) * p.chunk;
+                const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
+                merge_moments(n, mean, m2, static_cast<double>(j1 - j0), m[u].mean, m[u].m2);
+            }
+        }
+    }
+    return m2;
+}
+
 template <class T>
-__global__ void __launch_bounds__(kRThreads, 2) var_columns_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+__global__ void __launch_bounds__(kRThreads, kVarColumnBlocks<T>) var_columns_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
     constexpr int VC = (16 / sizeof(T)) > 8 ? 8 : (16 / sizeof(T));
     constexpr int UNR = 8;  // loads in flight per thread
     const ReducePlan &p = a.plan;
@@ -184,75 +209,72 @@ __global__ void __launch_bounds__(kRThreads, 2) var_columns_kernel(const __grid_
             else static_cast<Moments *>(a.partials)[chunk * p.nout + o0 + e] = Moments{cm, c2};
         }
     }
+    if (p.splits == 1 || a.tickets == nullptr || !drew_last_ticket(a.tickets)) return;
+    // this block is the last of its strip's: the strip's outputs, one per thread
+    const int64_t c = tile * (32 * VC) + threadIdx.x;
+    if (threadIdx.x < 32 * VC && c < p.ncols) {
+        const int64_t o = outer * p.ncols + c;
+        sink.put(o, merged_m2(static_cast<const Moments *>(a.partials), o, p), p.nred);
+    }
 }
 
 // The chunks' moments of each output merged in chunk order (a chunk's count follows from the plan).
 template <class T>
-__global__ void __launch_bounds__(kRThreads) var_combine_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+__global__ void __launch_bounds__(64) var_combine_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
     const ReducePlan &p = a.plan;
     const Moments *partials = static_cast<const Moments *>(a.partials);
-    for (int64_t o = blockIdx.x * static_cast<int64_t>(kRThreads) + threadIdx.x; o < p.nout;
-         o += static_cast<int64_t>(gridDim.x) * kRThreads) {
-        double n = 0.0, mean = 0.0, m2 = 0.0;
-        for (int64_t c = 0; c < p.splits; ++c) {
-            const int64_t j0 = c * p.chunk;
-            const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
-            const Moments m = partials[c * p.nout + o];
-            merge_moments(n, mean, m2, static_cast<double>(j1 - j0), m.mean, m.m2);
-        }
-        sink.put(o, m2, p.nred);
+    for (int64_t o = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; o < p.nout;
+         o += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        sink.put(o, merged_m2(partials, o, p), p.nred);
     }
 }
 
 // ---- variance over rows in one pass ----
-// The same for rows that are one unit-stride run of whole, aligned vectors (plan.simple): a lane takes the shift
-// from its first element and keeps one (s, q) pair per position within a vector, so that consecutive elements add
-// to different running sums; the pairs share the shift and simply add up. The lanes of a row are merged in lane
+// The same for rows that are one unit-stride run of whole, aligned 32-byte pieces (plan.simple): piece w belongs to
+// lane w mod G, read by one 256-bit load, four in flight; a lane takes the shift from its first element and keeps
+// four (s, q) pairs, so that consecutive elements add to different running sums; the pairs share the shift and
+// simply add up. The lanes of a row are merged in lane
 // order by shuffles and, for 256 lanes, the warps in warp order through shared memory. The row is read once; the
 // two-pass kernel above reads it twice and misses the caches for part of the second walk.
 // Grid: one block per 256 / G rows.
 template <int G, class T>
-__global__ void __launch_bounds__(kRThreads) var_rows_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+__global__ void __launch_bounds__(kRThreads, 4) var_rows_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
     constexpr int kTeams = kRThreads / G;
-    constexpr int VEC = 16 / sizeof(T);
-    constexpr int UNR = 4;
+    constexpr int N = Piece<T>::N;  // elements of a 32-byte piece
+    constexpr int K = 4;            // running sums per lane: element e of a piece adds to pair e % K
+    constexpr int UNR = 4;          // pieces in flight
     const ReducePlan &p = a.plan;
     const int lane = threadIdx.x % G;
     __shared__ double warp_n[8], warp_mean[8], warp_m2[8];
-    const uint32_t nvec = static_cast<uint32_t>(p.nred) / VEC;
+    const uint32_t pieces = static_cast<uint32_t>(p.nred) / N;
     const int64_t o = static_cast<int64_t>(blockIdx.x) * kTeams + threadIdx.x / G;
     const bool live = o < p.nout;
     double n = 0.0, mean = 0.0, m2 = 0.0;
-    if (live && static_cast<uint32_t>(lane) < nvec) {
+    if (live && static_cast<uint32_t>(lane) < pieces) {
         const T *row = static_cast<const T *>(a.kept.data) + a.kept.offset + decompose(a.kept, o, a.kept.ndim);
-        const double shift = to_f64(row[static_cast<size_t>(lane) * VEC]);
-        double s[VEC], q[VEC];
+        const double shift = to_f64(row[static_cast<size_t>(lane) * N]);
+        double s[K], q[K];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) s[e] = q[e] = 0.0;
-        auto take = [&](const RVec<T, VEC> &x) {
+        for (int k = 0; k < K; ++k) s[k] = q[k] = 0.0;
+        auto take = [&](const Piece<T> &x) {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) {
+            for (int e = 0; e < N; ++e) {
                 const double d = to_f64(x.v[e]) - shift;
-                s[e] += d;
-                q[e] = __fma_rn(d, d, q[e]);
+                s[e % K] += d;
+                q[e % K] = __fma_rn(d, d, q[e % K]);
             }
         };
-        uint32_t v = lane, taken = 0;
-        for (; v + (UNR - 1) * G < nvec; v += UNR * G, taken += UNR) {
-            RVec<T, VEC> x[UNR];
+        uint32_t w = lane, taken = 0;
+        for (; w + (UNR - 1) * G < pieces; w += UNR * G, taken += UNR) {
+            Piece<T> x[UNR];
 #pragma unroll
-            for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VEC> *>(row + static_cast<size_t>(v + u * G) * VEC);
+            for (int u = 0; u < UNR; ++u) x[u] = load_piece(row + static_cast<size_t>(w + u * G) * N);
 #pragma unroll
             for (int u = 0; u < UNR; ++u) take(x[u]);
         }
-        for (; v < nvec; v += G, ++taken) take(*reinterpret_cast<const RVec<T, VEC> *>(row + static_cast<size_t>(v) * VEC));
-        double st = s[0], qt = q[0];
-#pragma unroll
-        for (int e = 1; e < VEC; ++e) {
-            st += s[e];
-            qt += q[e];
-        }
-        n = static_cast<double>(taken) * VEC;
+        for (; w < pieces; w += G, ++taken) take(load_piece(row + static_cast<size_t>(w) * N));
+        double st = (s[0] + s[1]) + (s[2] + s[3]), qt = (q[0] + q[1]) + (q[2] + q[3]);
+        n = static_cast<double>(taken) * N;
         mean = shift + st / n;
         const double spread = qt - st * st / n;
         m2 = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);
@@ -294,10 +316,10 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
         VarSink<T> sink{o, divisor, take_sqrt};
         if (p.kind == 0 && p.splits == 1) {
             if constexpr (!std::is_same_v<T, double>) {
-                // every row one aligned run of whole vectors: the one-pass kernel
+                // every row one aligned run of whole pieces: the one-pass kernel
                 bool aligned = p.simple && p.group > 1 &&
-                               (reinterpret_cast<uintptr_t>(a.kept.data) + static_cast<uintptr_t>(a.kept.offset) * sizeof(T)) % 16 == 0;
-                for (int k = 0; k < a.kept.ndim; ++k) aligned = aligned && (a.kept.strides[k] * static_cast<int64_t>(sizeof(T))) % 16 == 0;
+                               (reinterpret_cast<uintptr_t>(a.kept.data) + static_cast<uintptr_t>(a.kept.offset) * sizeof(T)) % 32 == 0;
+                for (int k = 0; k < a.kept.ndim; ++k) aligned = aligned && (a.kept.strides[k] * static_cast<int64_t>(sizeof(T))) % 32 == 0;
                 if (aligned) {
                     const int64_t per = kRThreads / p.group;
                     if ((p.nout + per - 1) / per > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
@@ -320,10 +342,14 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
             if (p.kind == 1) {
                 if (p.kouter * p.xtiles > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 strips of outputs");
                 dim3 grid(static_cast<unsigned>(p.kouter * p.xtiles), static_cast<unsigned>(p.splits));
-                var_columns_kernel<T><<<grid, kRThreads, 0, ctx->stream>>>(a, sink);
+                // few chunks: the block that finishes last merges its strip's; else a second kernel (same order)
+                const bool self_merge = p.splits > 1 && a.tickets != nullptr && p.kouter * p.xtiles <= kTickets && p.splits <= kSelfFoldSplits;
+                ReduceArgs args = a;
+                if (!self_merge) args.tickets = nullptr;
+                var_columns_kernel<T><<<grid, kRThreads, 0, ctx->stream>>>(args, sink);
                 hmc_status s1 = launch_status("var kernel launch");
-                if (s1 != HMC_OK || p.splits == 1) return s1;
-                var_combine_kernel<T><<<clamp_grid((p.nout + kRThreads - 1) / kRThreads, 1 << 16), kRThreads, 0, ctx->stream>>>(a, sink);
+                if (s1 != HMC_OK || p.splits == 1 || self_merge) return s1;
+                var_combine_kernel<T><<<clamp_grid((p.nout + 63) / 64, 1 << 16), 64, 0, ctx->stream>>>(a, sink);
                 return launch_status("var combine kernel launch");
             }
         }

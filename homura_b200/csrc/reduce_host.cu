@@ -56,7 +56,7 @@ ReducePlan make_reduce_plan(const hmc_tensor_desc &kept, const hmc_tensor_desc &
         const int64_t worth = p.nred / (static_cast<int64_t>(p.group) * p.vec * 16);
         p.splits = std::max<int64_t>(1, std::min({want, worth, kMaxSplits}));
     }
-    p.simple = p.splits == 1 && p.group > 1 && red.ndim == 1 && p.step == 1 && p.nred % (16 / es) == 0 && p.nred < (int64_t{1} << 31);
+    p.simple = p.splits == 1 && p.group > 1 && red.ndim == 1 && p.step == 1 && p.nred % (32 / es) == 0 && p.nred < (int64_t{1} << 31);
     if (p.splits > 1) {
         // Whole pieces per lane and chunk, so that only a range's two ends can be ragged.
         const int64_t unit = static_cast<int64_t>(p.group) * p.vec;
@@ -164,7 +164,7 @@ HMC_API hmc_status hmc_reduce(hmc_context_t ctx, int32_t op, const hmc_tensor_de
         hmc_status s = check_reduction(kept, red);
         if (s != HMC_OK) return s;
         if (op < HMC_REDUCE_SUM || op > HMC_REDUCE_ANY) return fail(HMC_INVALID, "unknown reduction");
-        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr};
+        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr, ctx->tickets};
         s = check_output(out, kept, "the output", a.plan.nout);
         if (s != HMC_OK) return s;
         const int dt = kept->dtype;
@@ -206,7 +206,7 @@ HMC_API hmc_status hmc_var(hmc_context_t ctx, const hmc_tensor_desc *out, const 
         hmc_status s = check_reduction(kept, red);
         if (s != HMC_OK) return s;
         if (!dtype_is_float(kept->dtype)) return fail(HMC_INVALID, "var and std need a floating point tensor");
-        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr};
+        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr, ctx->tickets};
         s = check_output(out, kept, "the output", a.plan.nout);
         if (s != HMC_OK) return s;
         if (out->dtype != kept->dtype) return fail(HMC_INVALID, "the output of var has the source's dtype");
@@ -227,7 +227,7 @@ HMC_API hmc_status hmc_arg_reduce(hmc_context_t ctx, const hmc_tensor_desc *valu
         hmc_status s = check_reduction(kept, red);
         if (s != HMC_OK) return s;
         if (red->ndim > 1) return fail(HMC_INVALID, "an arg reduction folds one dimension");
-        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr};
+        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr, ctx->tickets};
         s = check_output(indices, kept, "the indices", a.plan.nout);
         if (s != HMC_OK) return s;
         if (indices->dtype != HMC_I64) return fail(HMC_INVALID, "the indices are an I64 tensor");

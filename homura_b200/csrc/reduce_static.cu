@@ -74,7 +74,7 @@ HMC_API hmc_status hmc_reduce_noalloc(hmc_context_t ctx, int32_t op, const hmc_t
         hmc_status s = check_reduction(kept, red);
         if (s != HMC_OK) return s;
         if (op < HMC_REDUCE_SUM || op > HMC_REDUCE_ANY) return fail(HMC_INVALID, "unknown reduction");
-        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr};
+        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr, ctx->tickets};
         s = check_output(out, kept, "the output", a.plan.nout);
         if (s != HMC_OK) return s;
         const int dt = kept->dtype;

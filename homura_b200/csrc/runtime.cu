@@ -318,7 +318,9 @@ HMC_API hmc_status hmc_context_create(int32_t device, hmc_context_t *out) {
             return status;
         };
         uint32_t *slot = nullptr;
-        cudaError_t err = cudaMalloc(&slot, sizeof(uint32_t));
+        // one allocation: the probe's word, which stays as the status word, and the reductions' counters after it
+        constexpr size_t kSlotBytes = (kTicketsOffset + kTickets) * sizeof(uint32_t);
+        cudaError_t err = cudaMalloc(&slot, kSlotBytes);
         if (err != cudaSuccess) return abandon(cuda_fail(err, "probe: cudaMalloc"));
         uint32_t answer = 0;
         forget_earlier_error();
@@ -327,7 +329,7 @@ HMC_API hmc_status hmc_context_create(int32_t device, hmc_context_t *out) {
         if (err == cudaSuccess) err = cudaMemcpyAsync(&answer, slot, sizeof answer, cudaMemcpyDeviceToHost, stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
         // The probe's word stays with the context as its status word (zero: nothing to report).
-        if (err == cudaSuccess) err = cudaMemsetAsync(slot, 0, sizeof(uint32_t), stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(slot, 0, kSlotBytes, stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
         auto abandon_slot = [&](hmc_status status) {
             if (cudaFree(slot) != cudaSuccess) cudaGetLastError();
@@ -344,7 +346,7 @@ HMC_API hmc_status hmc_context_create(int32_t device, hmc_context_t *out) {
             t.fail_after_probe -= 1;
             return abandon_slot(fail(HMC_OUT_OF_MEMORY, "out of host memory"));
         }
-        ctx = new (std::nothrow) hmc_context{device, stream, prop.multiProcessorCount, nullptr, reinterpret_cast<int *>(slot)};
+        ctx = new (std::nothrow) hmc_context{device, stream, prop.multiProcessorCount, nullptr, reinterpret_cast<int *>(slot), slot + kTicketsOffset};
         if (ctx == nullptr) return abandon_slot(fail(HMC_OUT_OF_MEMORY, "out of host memory"));
         *out = ctx;
         return HMC_OK;

@@ -108,7 +108,7 @@ HMC_API hmc_status hmc_reduce_partial(hmc_context_t ctx, int32_t op, double *par
         if (!dtype_is_float(kept->dtype) || red->dtype != kept->dtype) {
             return fail(HMC_INVALID, "hmc_reduce_partial takes a floating point tensor");
         }
-        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr};
+        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr, ctx->tickets};
         if (a.plan.nout == 0) return HMC_OK;
         if (partial == nullptr) return fail(HMC_INVALID, "null partials");
         if (a.plan.nred > 0 && kept->data == nullptr) return fail(HMC_INVALID, "null data pointer");
@@ -216,7 +216,7 @@ HMC_API hmc_status hmc_var_partial(hmc_context_t ctx, double *partial, const hmc
         s = check_desc(red, "the reduced dimensions");
         if (s != HMC_OK) return s;
         if (!dtype_is_float(kept->dtype) || red->dtype != kept->dtype) return fail(HMC_INVALID, "hmc_var_partial takes a floating point tensor");
-        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr};
+        ReduceArgs a{*kept, *red, make_reduce_plan(*kept, *red), nullptr, ctx->tickets};
         if (a.plan.nout == 0) return HMC_OK;
         if (partial == nullptr || means == nullptr) return fail(HMC_INVALID, "null partials or means");
         if (a.plan.nred > 0 && kept->data == nullptr) return fail(HMC_INVALID, "null data pointer");

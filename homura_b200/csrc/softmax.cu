@@ -581,13 +581,10 @@ hmc_status launch_softmax_staged(hmc_context_t ctx, const SoftmaxArgs &a, bool l
     const int row_bytes = static_cast<int>(a.n * sizeof(T));
     // as many warps per block as two row buffers each allow within ~96 KB, so that two blocks share an SM
     int warps = 8;
-    int budget = 96 * 1024;
-    if (const char *e = std::getenv("HMC_TUNE_SOFTMAX_BUDGET")) budget = std::atoi(e);
+    const int budget = 96 * 1024;
     while (warps > 1 && static_cast<int64_t>(warps) * 2 * row_bytes > budget) warps >>= 1;
-    if (const char *e = std::getenv("HMC_TUNE_SOFTMAX_WARPS")) warps = std::atoi(e);
     const size_t shared = static_cast<size_t>(warps) * 2 * row_bytes;
     int per_sm = std::max<int>(1, std::min<int>(8, static_cast<int>((220 * 1024) / (shared + 1024))));
-    if (const char *e = std::getenv("HMC_TUNE_SOFTMAX_PER_SM")) per_sm = std::atoi(e);
     const int64_t blocks_needed = ceil_div(a.nrows, warps);
     const unsigned grid = clamp_grid(blocks_needed, static_cast<int64_t>(ctx->sm_count) * per_sm);
     auto kernel = log ? softmax_staged_kernel<T, true> : softmax_staged_kernel<T, false>;
@@ -679,6 +676,7 @@ void rows_as_reduction(const SoftmaxArgs &a, ReduceArgs &r) {
     r.red.strides[0] = a.si;
     r.plan = make_reduce_plan(r.kept, r.red);
     r.partials = nullptr;
+    r.tickets = nullptr;
 }
 
 // Few rows, each long enough that cutting it fills the GPU better than a block per row does.
@@ -705,6 +703,7 @@ hmc_status launch_softmax_split(hmc_context_t ctx, const SoftmaxArgs &a, bool lo
     double *maxima = static_cast<double *>(workspace);
     double *sums = reinterpret_cast<double *>(static_cast<char *>(workspace) + block);
     r.partials = static_cast<char *>(workspace) + 2 * block;
+    r.tickets = ctx->tickets;
     hmc_status s = launch_reduce(r, MaxSkippingNaN<T>{}, KeepF64{maxima}, ctx->stream);
     if (s != HMC_OK) return s;
     s = launch_reduce(r, ExpSum<T>{maxima, 0.0}, KeepF64{sums}, ctx->stream);

@@ -16,7 +16,7 @@
 //     of the output tile, again swizzled, which one cp.async.bulk.tensor store sends to global memory in whole
 //     128-byte rows.
 //
-// A block of 128 threads keeps a ring of input tiles in flight (the copies of the next tiles run while one is
+// A block of 256 threads keeps a ring of input tiles in flight (the copies of the next tiles run while one is
 // computed) and two output tiles (one being written while the next is filled). No thread issues a global load
 // or store. Every wait on an mbarrier is bounded: when one runs out the block stops taking tiles and sets the
 // context's status word, which hmc_context_synchronize reports.
@@ -34,7 +34,8 @@ namespace hmc {
 constexpr int kT16Tile = 64;                              // elements along either edge of a tile
 constexpr int kT16TileBytes = kT16Tile * kT16Tile * 2;    // 8 KB
 constexpr int kT16Stages = 4;                             // input tiles in flight per block
-constexpr int kT16Threads = 128;
+constexpr int kT16Threads = 256;
+constexpr int kT16Warps = kT16Threads / 32;
 constexpr int kT16WaitLimit = 1 << 22;                    // polls of an mbarrier before a wait gives up
 constexpr size_t kT16SharedBytes = static_cast<size_t>(kT16Stages + 2) * kT16TileBytes + 1024;  // + room to align
 
@@ -163,10 +164,10 @@ __global__ void __launch_bounds__(kT16Threads) transpose16_kernel(const __grid_c
         // the store issued two tiles ago has finished reading this output tile
         if (threadIdx.x == 0) t16_stores_read<1>();
         __syncthreads();
-        // a warp takes the 8 x 32 pieces (a-block ia, b-group jb) number warp, warp + 4, ... of the sixteen
+        // a warp takes the 8 x 32 pieces (a-block ia, b-group jb) number warp, warp + 8 of the sixteen
 #pragma unroll
-        for (int piece = 0; piece < 4; ++piece) {
-            const int id = piece * 4 + warp;
+        for (int piece = 0; piece < 16 / kT16Warps; ++piece) {
+            const int id = piece * kT16Warps + warp;
             const int ia = id >> 1, jb = id & 1;
             // lane l names row b = jb * 32 + l of the input tile, the 16-byte chunk ia of it (swizzled by the row)
             const int row_in = jb * 32 + lane;

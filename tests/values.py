@@ -202,7 +202,13 @@ def ulp_stats(got: np.ndarray, want: np.ndarray, dtype: int, what: str):
     inf = np.isinf(gf) | np.isinf(wf)
     assert (gf[inf] == wf[inf]).all(), f"{what} [{DTYPE_NAMES[dtype]}]: infinities differ"
     ok = ~(gn | inf)
-    d = np.abs(ordered(got, dtype)[ok].astype(np.float64) - ordered(want, dtype)[ok].astype(np.float64))
+    og, ow = ordered(got, dtype)[ok], ordered(want, dtype)[ok]
+    # exact integer distances (an f64 difference of 63-bit integers would be rounded to multiples of 512); values of
+    # opposite sign, whose distance could overflow, are apart by their magnitudes' sum, computed in f64 when it is huge
+    same_sign = (og >= 0) == (ow >= 0)
+    with np.errstate(over="ignore"):
+        d = np.where(same_sign, np.abs(og - ow), 0).astype(np.float64)
+    d = np.where(same_sign, d, np.abs(og.astype(np.float64)) + np.abs(ow.astype(np.float64)))
     # +0 and -0 are the same value
     zero = (gf[ok] == 0) & (wf[ok] == 0)
     d = np.where(zero, 0, d)
