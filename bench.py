@@ -268,6 +268,31 @@ class C3Workload:
         for _, f in self.ops():
             f()
 
+    def size_sweep(self, runner) -> dict:
+        """The row, column and full sums and the row variance on 1, 4 and 8 copies of the input (268 MB, 1 GB, 2 GB), each
+        kernel alone with L2 flushed: what a launch costs at the start and the end shrinks with the size, what the kernel
+        sustains does not."""
+        from homura_b200 import ffi
+        from homura_b200.host import F32
+        be = self.be
+        r, c = self.x.shape
+        out = {}
+        for copies in (1, 4, 8):
+            x = self.x if copies == 1 else be.empty((copies * r, c), F32)
+            if copies > 1:
+                _tile_fill(be, x, self.x)
+            rows_f, full_f = be.empty((copies * r,), F32), be.empty((), F32)
+            ops = [("sum_rows", lambda: be.reduce(ffi.HMC_REDUCE_SUM, rows_f, x, [False, True])),
+                   ("var_rows", lambda: be.var(rows_f, x, [False, True], 1.0, False)),
+                   ("sum_cols", lambda: be.reduce(ffi.HMC_REDUCE_SUM, self.out["cols_f"], x, [True, False])),
+                   ("var_cols", lambda: be.var(self.out["cols_f"], x, [True, False], 1.0, False)),
+                   ("sum_full", lambda: be.reduce(ffi.HMC_REDUCE_SUM, full_f, x, [True, True]))]
+            per_op = runner.flushed_per_op(ops, reps=7)
+            nbytes = 4 * copies * r * c
+            out[f"{nbytes / 1e6:.0f} MB"] = {k: {"gbs": nbytes / (v * 1e-3) / 1e9, "ms": v} for k, v in per_op.items()}
+            del x, rows_f, full_f
+        return out
+
 
 class C4Workload:
     """softmax / log_softmax of causally masked f32 logits [8, 32, 2048, 2048] and the row mean of squares of
@@ -622,6 +647,7 @@ def workload_record(runner: Runner, w, steps: int, warmup: int) -> dict:
                           "timed kernel; the figures of this record are taken after a flush that writes and reads back"}
     flush_note["host_ms_to_queue_an_iteration"], flush_note["device_ms_per_iteration"] = rates
     flush_note["host_and_device_ms_per_iteration_by_op"] = queue_rates
+    extra = {"size_sweep": w.size_sweep(runner)} if hasattr(w, "size_sweep") and runner.world == 1 else {}
     return {"workload": w.name, "dtype": w.dtype, "metric": METRIC, "unit": UNIT, "flush": flush_note,
             "value": step_bytes / (flushed_ms * 1e-3) / 1e9, "ms_per_step": flushed_ms,
             "value_basis": "sum of the kernels' times, each alone with L2 flushed before it",
@@ -629,7 +655,7 @@ def workload_record(runner: Runner, w, steps: int, warmup: int) -> dict:
                              "note": "consecutive kernels over one input are partly served from the 126 MB L2"},
             "algorithmic_bytes_per_step": step_bytes, "kernels_per_step": w.launches_per_step,
             "roofline": dict(r["worst"], per_kernel_gbs=r["per_kernel_gbs"], per_kernel_ms=r["per_kernel_ms"]),
-            "frac_of_measured_copy": {k: v / r["worst"]["peak"] for k, v in r["per_kernel_gbs"].items()}}
+            "frac_of_measured_copy": {k: v / r["worst"]["peak"] for k, v in r["per_kernel_gbs"].items()}, **extra}
 
 
 def cpu_sample(seconds_budget: float = 20.0) -> dict:

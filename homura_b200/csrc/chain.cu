@@ -24,6 +24,9 @@ struct Chain {
     using Compute = typename Comp<P>::C;
     int first, second;
     static constexpr bool kFast = std::is_same_v<T, F16> || std::is_same_v<T, BF16>;
+    // b and c are broadcasts in the expressions this is for (a scale per column, a bias per row): what is in flight
+    // per thread is x, 16 bytes a vector
+    static constexpr int kUnroll = 2;
     __device__ __forceinline__ Compute compute(T x, T b, TC c) const {
         using Ct = typename Comp<T>::C;
         const T t1 = down<T>(unary_math<UOP, Ct, kFast>(up(x)));

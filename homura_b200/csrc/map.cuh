@@ -75,7 +75,13 @@ template <class F> constexpr int vec_of() {
 template <class T> constexpr int size_or_zero() { return sizeof(T); }
 template <> constexpr int size_or_zero<Unused>() { return 0; }
 
+// A functor may state its own unrolling as a member kUnroll (one whose operands are mostly broadcasts, which the
+// rule below counts as traffic, knows better how many bytes it really has in flight).
+template <class F, class = void> struct has_unroll : std::false_type {};
+template <class F> struct has_unroll<F, std::void_t<decltype(F::kUnroll)>> : std::true_type {};
+
 template <class F> constexpr int unroll_of() {
+    if constexpr (has_unroll<F>::value) return F::kUnroll;
     // About 64 bytes of inputs in flight per thread and iteration (the loads of all inputs are issued before
     // the first store), and never more than 64 bytes of output held at once.
     constexpr int in_bytes = (size_or_zero<typename F::A>() + size_or_zero<typename F::B>() + size_or_zero<typename F::C>()) *
@@ -883,10 +889,12 @@ bool launch_transpose16(hmc_context_t ctx, const MapArgs &a, const F &f, hmc_sta
     CUtensorMap in_map, out_map;
     if (!t16_encode_map(&in_map, a.base[1], size_a, size_b, outer, a.strides[1][db], a.ndim == 3 ? a.strides[1][0] : 0)) return false;
     if (!t16_encode_map(&out_map, a.base[0], size_b, size_a, outer, a.strides[0][da], a.ndim == 3 ? a.strides[0][0] : 0)) return false;
+    const int64_t tiles_a = ceil_div(size_a, kT16Tile), tiles_b = ceil_div(size_b, kT16Tile);
+    if (tiles_a * tiles_b >= (int64_t{1} << 31) / (outer > 0 ? outer : 1)) return false;  // the kernel counts tiles in 32 bits
     Transpose16Args args;
-    args.tiles_a = ceil_div(size_a, kT16Tile);
-    args.tiles_b = ceil_div(size_b, kT16Tile);
-    args.tiles = outer * args.tiles_a * args.tiles_b;
+    args.tiles_a = static_cast<uint32_t>(tiles_a);
+    args.tiles_b = static_cast<uint32_t>(tiles_b);
+    args.tiles = static_cast<uint32_t>(outer * tiles_a * tiles_b);
     static bool raised[kTileKnownDevices] = {};
     if (ctx->device >= kTileKnownDevices || !raised[ctx->device]) {
         cudaError_t err = cudaFuncSetAttribute(transpose16_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -897,8 +905,8 @@ bool launch_transpose16(hmc_context_t ctx, const MapArgs &a, const F &f, hmc_sta
         }
         if (ctx->device < kTileKnownDevices) raised[ctx->device] = true;
     }
-    const int64_t resident = static_cast<int64_t>(ctx->sm_count) * 4;  // four blocks of 49 KB share an SM
-    const unsigned grid = static_cast<unsigned>(args.tiles < resident ? args.tiles : resident);
+    const int64_t resident = static_cast<int64_t>(ctx->sm_count) * kT16BlocksPerSm;
+    const unsigned grid = static_cast<unsigned>(static_cast<int64_t>(args.tiles) < resident ? args.tiles : resident);
     transpose16_kernel<F><<<grid, kT16Threads, kT16SharedBytes, ctx->stream>>>(in_map, out_map, args, f, ctx->status);
     status = launch_status("transposing kernel launch");
     return true;

@@ -123,6 +123,21 @@ __device__ __forceinline__ Acc shuffle_down(Acc v, int delta) {
     return v;
 }
 
+// ---- a thread's own ring of 16-byte slots in shared memory, filled by asynchronous copies ----
+// A thread only reads the slots it copied itself, so waiting for its own copy groups is all the synchronisation
+// there is; the data in flight occupies no registers.
+__device__ __forceinline__ void ring_copy_16(void *shared_dst, const void *global_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(shared_dst))),
+                 "l"(global_src)
+                 : "memory");
+}
+__device__ __forceinline__ void ring_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Until at most N of this thread's copy groups are still in flight.
+template <int N>
+__device__ __forceinline__ void ring_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ---- partials ----
 // A partial that another block wrote, read past this SM's L1.
 template <class Acc>
@@ -147,9 +162,9 @@ __device__ __forceinline__ Acc load_partial(const Acc *p) {
 // for another: a block that is not the last simply leaves.)
 __device__ __forceinline__ bool drew_last_ticket(unsigned *tickets) {
     __shared__ bool last;
-    __threadfence();  // this thread's partials are visible to the device before the ticket is
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence();  // the block's partials (ordered before this by the barrier) are visible to the device before the ticket is
         const unsigned mine = atomicAdd(&tickets[blockIdx.x], 1u);
         last = mine + 1 == gridDim.y;
         if (last) tickets[blockIdx.x] = 0;  // everybody has drawn: ready for the next kernel
@@ -189,9 +204,10 @@ __device__ __forceinline__ typename Op::Acc fold_team(const Op &op, typename Op:
     if constexpr (G == 1) {
         return acc;
     } else {
-        // lane l takes lane l + d: after the last step lane 0 holds lanes 0..31 in order
+        // lane l takes lane l + d: after the last step the team's lane 0 holds its lanes in order (teams of
+        // fewer than 32 lanes are aligned groups of a warp's lanes)
 #pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
+        for (int d = 1; d < (G < 32 ? G : 32); d <<= 1) {
             const Acc later = shuffle_down(acc, d);
             acc = op.combine(acc, later);
         }
@@ -463,6 +479,12 @@ __global__ void __launch_bounds__(kRThreads, is_extreme<Op>::value ? 3 : 4) redu
     if (lane == 0 && live) sink.put(o, acc, p.nred);
 }
 
+// The lanes that share the partials of an output of the column kernel when there are few chunks (lane l folds
+// chunks l, l + 8, ... in order, the lanes are folded in lane order): the block that finishes last has 128 or 256
+// outputs to fold, and a thread per output reading its partials one after another would stretch the kernel's end
+// over a dozen round trips to the L2.
+constexpr int kColumnFoldLanes = 8;
+
 // kind 1. Grid: (kouter * xtiles, splits), every block launched at once; block 32 x 8: thread (tx, ty) owns the VC
 // adjacent outputs tx * VC .. of its strip of 32 * VC outputs and folds the reduced indices j0 + ty, j0 + ty + 8, ...
 // of its chunk; the eight warps are then folded in warp order through shared memory.
@@ -548,11 +570,16 @@ __global__ void __launch_bounds__(kRThreads, is_extreme<Op>::value ? 2 : 4) redu
         }
     }
     if (p.splits == 1 || a.tickets == nullptr || !drew_last_ticket(a.tickets)) return;
-    // the strip's outputs, one per thread
-    const int64_t c = tile * (32 * VC) + threadIdx.x;
-    if (threadIdx.x < 32 * VC && c < p.ncols) {
+    // the strip's outputs, each by a team of kColumnFoldLanes lanes
+    constexpr int kTeams = kRThreads / kColumnFoldLanes;
+    const int lane = threadIdx.x % kColumnFoldLanes;
+#pragma unroll 2
+    for (int first = 0; first < 32 * VC; first += kTeams) {
+        const int64_t c = tile * (32 * VC) + first + threadIdx.x / kColumnFoldLanes;
+        const bool live = c < p.ncols;
         const int64_t o = outer * p.ncols + c;
-        sink.put(o, fold_partials_in_order(op, partials, o, p.nout, p.splits), p.nred);
+        const Acc r = fold_team<kColumnFoldLanes>(op, team_partials<kColumnFoldLanes>(op, partials, live ? o : 0, live, lane, p));
+        if (lane == 0 && live) sink.put(o, r, p.nred);
     }
 }
 
@@ -571,9 +598,9 @@ __global__ void __launch_bounds__(kRThreads) reduce_combine_kernel(const __grid_
     if (lane == 0 && live) sink.put(o, acc, p.nred);
 }
 
-// The number of partials up to which the block that finishes last folds them itself: a thread per output takes
-// them one after another (columns, single-lane rows), a team shares them (32- and 256-lane rows).
-constexpr int64_t kSelfFoldSplits = 32;
+// The number of partials up to which the block that finishes last folds them itself where only a few lanes share an
+// output's partials (columns: eight; single-lane rows: one); teams of 32 and 256 lanes always do.
+constexpr int64_t kSelfFoldSplits = 64;
 
 inline unsigned clamp_grid(int64_t n, int64_t cap) { return static_cast<unsigned>(n < cap ? (n < 1 ? 1 : n) : cap); }
 
@@ -584,11 +611,11 @@ hmc_status launch_reduce(const ReduceArgs &a, const Op &op, const Sink &sink, cu
     const ReducePlan &p = a.plan;
     if (p.nout == 0) return HMC_OK;
     // the lanes that share an output's partials (part of the fold order, so a function of the plan alone)
-    const int lanes = p.kind == 0 ? p.group : (p.splits > kSelfFoldSplits ? 32 : 1);
+    const int lanes = p.kind == 0 ? p.group : (p.splits > kSelfFoldSplits ? 32 : kColumnFoldLanes);
     ReduceArgs args = a;
     const int64_t blocks_x = p.kind == 1 ? p.kouter * p.xtiles : (p.nout + kRThreads / p.group - 1) / (kRThreads / p.group);
     const bool self_fold = p.splits > 1 && a.tickets != nullptr && blocks_x <= kTickets &&
-                           (p.kind == 0 ? (p.group > 1 || p.splits <= kSelfFoldSplits) : lanes == 1);
+                           (p.kind == 0 ? (p.group > 1 || p.splits <= kSelfFoldSplits) : lanes == kColumnFoldLanes);
     if (!self_fold) args.tickets = nullptr;
     if (p.kind == 1) {
         if (blocks_x > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 strips of outputs");
@@ -609,6 +636,7 @@ hmc_status launch_reduce(const ReduceArgs &a, const Op &op, const Sink &sink, cu
         const unsigned grid = static_cast<unsigned>(blocks);
         if (lanes == 256) reduce_combine_kernel<256, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
         else if (lanes == 32) reduce_combine_kernel<32, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        else if (lanes == kColumnFoldLanes) reduce_combine_kernel<kColumnFoldLanes, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
         else reduce_combine_kernel<1, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
         s = launch_status("reduction combine kernel launch");
     }

@@ -71,9 +71,6 @@ __global__ void __launch_bounds__(kRThreads) deviations_kernel(const __grid_cons
 struct alignas(16) Moments {
     double mean, m2;
 };
-// Blocks of the column kernel that share an SM: four for f32 (four columns a thread); the half types' eight columns a
-// thread need the registers of three.
-template <class T> constexpr int kVarColumnBlocks = sizeof(T) == 4 ? 4 : 3;
 static_assert(sizeof(Moments) == kPartialBytes, "the moments of a chunk are one partial");
 
 __device__ __forceinline__ void merge_moments(double &n, double &mean, double &m2, double nb, double mean_b, double m2_b) {
@@ -86,41 +83,68 @@ __device__ __forceinline__ void merge_moments(double &n, double &mean, double &m
     n = total;
 }
 
-// The chunks' moments of output o merged in chunk order by one thread (a chunk's count follows from the plan),
-// eight loads in flight.
-__device__ __forceinline__ double merged_m2(const Moments *partials, int64_t o, const ReducePlan &p) {
+// The chunks' moments of output o merged by a team of kColumnFoldLanes lanes (a chunk's count follows from the plan):
+// lane l merges chunks l, l + 8, ... in order, then the lanes are merged in lane order. Valid in the team's lane 0;
+// all lanes of the warp call it.
+__device__ __forceinline__ double merged_m2(const Moments *partials, int64_t o, bool live, int lane, const ReducePlan &p) {
     double n = 0.0, mean = 0.0, m2 = 0.0;
-    for (int64_t c0 = 0; c0 < p.splits; c0 += 8) {
-        Moments m[8];
+    auto count = [&](int64_t c) {
+        const int64_t j0 = c * p.chunk;
+        const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
+        return static_cast<double>(j1 - j0);
+    };
+    if (live) {
+        int64_t c = lane;
+        for (; c + 3 * kColumnFoldLanes < p.splits; c += 4 * kColumnFoldLanes) {
+            Moments m[4];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            if (c0 + u < p.splits) m[u] = load_partial(partials + (c0 + u) * p.nout + o);
-        }
+            for (int u = 0; u < 4; ++u) m[u] = load_partial(partials + (c + u * kColumnFoldLanes) * p.nout + o);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            if (c0 + u < p.splits) {
-                const int64_t j0 = (c0 + u) * p.chunk;
-                const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
-                merge_moments(n, mean, m2, static_cast<double>(j1 - j0), m[u].mean, m[u].m2);
-            }
+            for (int u = 0; u < 4; ++u) merge_moments(n, mean, m2, count(c + u * kColumnFoldLanes), m[u].mean, m[u].m2);
         }
+        for (; c < p.splits; c += kColumnFoldLanes) {
+            const Moments m = load_partial(partials + c * p.nout + o);
+            merge_moments(n, mean, m2, count(c), m.mean, m.m2);
+        }
+    }
+#pragma unroll
+    for (int d = 1; d < kColumnFoldLanes; d <<= 1) {
+        const double on = __shfl_down_sync(0xFFFFFFFFu, n, d);
+        const double om = __shfl_down_sync(0xFFFFFFFFu, mean, d);
+        const double o2 = __shfl_down_sync(0xFFFFFFFFu, m2, d);
+        merge_moments(n, mean, m2, on, om, o2);
     }
     return m2;
 }
 
+// Block 32 x 8 as in the column kernel of the engine: thread (tx, ty) owns VC adjacent columns of its strip and the rows
+// j0 + ty, j0 + ty + 8, ... of its chunk. The rows in flight sit in a ring of kVarStages 16-byte slots per thread in
+// shared memory, filled by asynchronous copies, so that a thread has 256 bytes on their way at any time without a
+// register spent on them (with the loads in registers beside the twelve f64 accumulators of four columns, the
+// compiler could keep only half as many in flight).
+constexpr int kVarStages = 16;
+constexpr int kKnownDevices = 64;
+constexpr int64_t kSharedShiftRows = 4096;
+constexpr int kVarBatch = 4;  // slots consumed and refilled at a time
+constexpr size_t kVarSharedBytes = static_cast<size_t>(kVarStages) * kRThreads * 16;
+
 template <class T>
-__global__ void __launch_bounds__(kRThreads, kVarColumnBlocks<T>) var_columns_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+__global__ void __launch_bounds__(kRThreads, 3) var_columns_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
     constexpr int VC = (16 / sizeof(T)) > 8 ? 8 : (16 / sizeof(T));
-    constexpr int UNR = 8;  // loads in flight per thread
     const ReducePlan &p = a.plan;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int64_t chunk = blockIdx.y;
     const int64_t j0 = chunk * p.chunk;
     const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
     const int last = a.kept.ndim - 1;
-    __shared__ double stage_mean[7][32 * VC];
-    __shared__ double stage_m2[7][32 * VC];
-    __shared__ double stage_n[8];
+    extern __shared__ __align__(16) unsigned char var_shared[];
+    // during the walk: the ring; afterwards: the warps' moments on their way to warp 0
+    RVec<T, VC> *ring = reinterpret_cast<RVec<T, VC> *>(var_shared) + threadIdx.x;
+    static_assert(sizeof(RVec<T, VC>) == 16, "a slot is 16 bytes");
+    double(*stage_mean)[32 * VC] = reinterpret_cast<double(*)[32 * VC]>(var_shared);
+    double(*stage_m2)[32 * VC] = stage_mean + 7;
+    double *stage_n = reinterpret_cast<double *>(stage_m2 + 7);
+    static_assert((14 * 32 * VC + 8) * sizeof(double) <= kVarSharedBytes, "the moments fit into the ring's memory");
     // Grid: (kouter * xtiles, splits), one block per strip of 32 * VC outputs and chunk.
     const int64_t outer = blockIdx.x / p.xtiles;
     const int64_t tile = blockIdx.x - outer * p.xtiles;
@@ -128,68 +152,107 @@ __global__ void __launch_bounds__(kRThreads, kVarColumnBlocks<T>) var_columns_ke
     const int64_t base = a.kept.offset + (last > 0 ? decompose(a.kept, outer, last) : 0);
     const int64_t o0 = outer * p.ncols + c0;
     const T *src = static_cast<const T *>(a.kept.data) + base + c0;
-    double n = 0.0, mean[VC], m2[VC];
+    double n = 0.0, mean[VC], m2[VC], held[VC];  // (held: warp 0's shifts when the block shares them)
 #pragma unroll
-    for (int e = 0; e < VC; ++e) mean[e] = m2[e] = 0.0;
+    for (int e = 0; e < VC; ++e) mean[e] = m2[e] = held[e] = 0.0;
     const bool in_range = c0 < p.ncols;
     const bool whole = c0 + VC <= p.ncols;
+    // Chunks of up to kSharedShiftRows rows take one shift per column for the whole block: the warps' sums then simply
+    // add up, which spares every block eight merges and a division at its end (the cancellation in q - s^2 / n grows
+    // with the number of values that share a shift: at most log2(rows + 1) bits, 12 of an f64's 53 here).
+    const bool shared_shift = j1 - j0 <= kSharedShiftRows;
     if (in_range && j0 + ty < j1) {
         const int64_t stride = a.red.strides[0];
         const bool single = a.red.ndim == 1;
-        const bool walk = single && whole && (reinterpret_cast<uintptr_t>(src) & (alignof(RVec<T, VC>) - 1)) == 0 &&
-                          (stride * static_cast<int64_t>(sizeof(T))) % static_cast<int64_t>(alignof(RVec<T, VC>)) == 0;
+        const bool walk = single && whole && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+                          (stride * static_cast<int64_t>(sizeof(T))) % 16 == 0;
         auto red_off = [&](int64_t j) { return single ? j * stride : decompose(a.red, j, a.red.ndim); };
-        int64_t j = j0 + ty;
-        // the shift of each column: the first value this thread meets
+        // the shift of each column: the first value of the chunk (shared by the block's warps), or, for long chunks, the
+        // first value this thread meets
         double shift[VC], s[VC], q[VC];
         {
-            const T *first = src + red_off(j);
+            const T *first = src + red_off(shared_shift ? j0 : j0 + ty);
 #pragma unroll
             for (int e = 0; e < VC; ++e) {
                 shift[e] = c0 + e < p.ncols ? to_f64(first[e]) : 0.0;
                 s[e] = q[e] = 0.0;
             }
         }
+        auto take = [&](const RVec<T, VC> &x) {
+#pragma unroll
+            for (int e = 0; e < VC; ++e) {
+                const double d = to_f64(x.v[e]) - shift[e];
+                s[e] += d;
+                q[e] = __fma_rn(d, d, q[e]);
+            }
+        };
         if (walk) {
-            // whole aligned vectors along one reduced dimension: a pointer that steps by eight rows, UNR loads in flight
-            const T *ptr = src + j * stride;
+            // whole aligned vectors along one reduced dimension: this thread's rows are r = 0 .. rows - 1 at ptr + r * step
+            const T *ptr = src + (j0 + ty) * stride;
             const int64_t step = 8 * stride;
-            for (; j + (UNR - 1) * 8 < j1; j += UNR * 8, ptr += UNR * step) {
-                RVec<T, VC> x[UNR];
+            const int64_t rows = (j1 - (j0 + ty) + 7) / 8;
+            static_assert(kVarStages % kVarBatch == 0, "a batch never wraps round the ring");
+            // (the copies walk a pointer of their own, kVarStages rows ahead of the row that is consumed)
+            const T *ahead = ptr;
+            int64_t to_copy = rows;
+            auto request = [&](int slot) {  // (a group is committed also when there is nothing left to copy)
+                if (to_copy > 0) {
+                    ring_copy_16(ring + slot * kRThreads, ahead);
+                    ahead += step;
+                    --to_copy;
+                }
+                ring_commit();
+            };
+            for (int slot = 0; slot < kVarStages; ++slot) request(slot);
+            int64_t r = 0;
+            int slot = 0;  // of row r
+            for (; r + kVarBatch <= rows; r += kVarBatch) {
+                ring_wait<kVarStages - kVarBatch>();
+                RVec<T, VC> x[kVarBatch];
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) x[u] = *reinterpret_cast<const RVec<T, VC> *>(ptr + u * step);
+                for (int u = 0; u < kVarBatch; ++u) x[u] = ring[(slot + u) * kRThreads];
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) {
+                for (int u = 0; u < kVarBatch; ++u) take(x[u]);
 #pragma unroll
-                    for (int e = 0; e < VC; ++e) {
-                        const double d = to_f64(x[u].v[e]) - shift[e];
+                for (int u = 0; u < kVarBatch; ++u) request(slot + u);
+                slot = slot + kVarBatch == kVarStages ? 0 : slot + kVarBatch;
+            }
+            ring_wait<0>();
+            for (; r < rows; ++r, ++slot) take(ring[slot * kRThreads]);
+            n = static_cast<double>(rows);
+        } else {
+            for (int64_t j = j0 + ty; j < j1; j += 8) {
+                const T *row = src + red_off(j);
+#pragma unroll
+                for (int e = 0; e < VC; ++e) {
+                    if (c0 + e < p.ncols) {
+                        const double d = to_f64(row[e]) - shift[e];
                         s[e] += d;
                         q[e] = __fma_rn(d, d, q[e]);
                     }
                 }
-                n += UNR;
+                n += 1.0;
             }
         }
-        for (; j < j1; j += 8) {
-            const T *row = src + red_off(j);
+        if (shared_shift) {
+            // (s, q) travel as they are; warp 0 keeps the shifts for when it has the block's sums
 #pragma unroll
             for (int e = 0; e < VC; ++e) {
-                if (c0 + e < p.ncols) {
-                    const double d = to_f64(row[e]) - shift[e];
-                    s[e] += d;
-                    q[e] = __fma_rn(d, d, q[e]);
-                }
+                mean[e] = s[e];
+                m2[e] = q[e];
+                held[e] = shift[e];
             }
-            n += 1.0;
-        }
-        const double inv = 1.0 / n;
+        } else {
+            const double inv = 1.0 / n;
 #pragma unroll
-        for (int e = 0; e < VC; ++e) {
-            mean[e] = shift[e] + s[e] * inv;
-            const double spread = q[e] - s[e] * s[e] * inv;
-            m2[e] = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);  // (rounding may leave -0.0...; a NaN stays)
+            for (int e = 0; e < VC; ++e) {
+                mean[e] = shift[e] + s[e] * inv;
+                const double spread = q[e] - s[e] * s[e] * inv;
+                m2[e] = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);  // (rounding may leave -0.0...; a NaN stays)
+            }
         }
     }
+    __syncthreads();  // every thread is done with its ring: the memory now carries the warps' moments
     if (ty > 0) {
 #pragma unroll
         for (int e = 0; e < VC; ++e) {
@@ -204,17 +267,35 @@ __global__ void __launch_bounds__(kRThreads, kVarColumnBlocks<T>) var_columns_ke
         for (int e = 0; e < VC; ++e) {
             if (c0 + e >= p.ncols) continue;
             double cn = n, cm = mean[e], c2 = m2[e];
-            for (int w = 0; w < 7; ++w) merge_moments(cn, cm, c2, stage_n[w + 1], stage_mean[w][tx * VC + e], stage_m2[w][tx * VC + e]);
+            if (shared_shift) {
+                // the warps' sums in warp order, then the chunk's moments from them
+                for (int w = 0; w < 7; ++w) {
+                    cm += stage_mean[w][tx * VC + e];
+                    c2 += stage_m2[w][tx * VC + e];
+                }
+                const double rows = static_cast<double>(j1 - j0);
+                const double inv = reciprocal_short(rows);
+                const double spread = c2 - cm * cm * inv;
+                c2 = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);
+                cm = held[e] + cm * inv;
+            } else {
+                for (int w = 0; w < 7; ++w) merge_moments(cn, cm, c2, stage_n[w + 1], stage_mean[w][tx * VC + e], stage_m2[w][tx * VC + e]);
+            }
             if (p.splits == 1) sink.put(o0 + e, c2, p.nred);
             else static_cast<Moments *>(a.partials)[chunk * p.nout + o0 + e] = Moments{cm, c2};
         }
     }
     if (p.splits == 1 || a.tickets == nullptr || !drew_last_ticket(a.tickets)) return;
-    // this block is the last of its strip's: the strip's outputs, one per thread
-    const int64_t c = tile * (32 * VC) + threadIdx.x;
-    if (threadIdx.x < 32 * VC && c < p.ncols) {
+    // this block is the last of its strip's: the strip's outputs, each by a team of lanes
+    constexpr int kTeams = kRThreads / kColumnFoldLanes;
+    const int lane = threadIdx.x % kColumnFoldLanes;
+#pragma unroll 2
+    for (int first = 0; first < 32 * VC; first += kTeams) {
+        const int64_t c = tile * (32 * VC) + first + threadIdx.x / kColumnFoldLanes;
+        const bool live = c < p.ncols;
         const int64_t o = outer * p.ncols + c;
-        sink.put(o, merged_m2(static_cast<const Moments *>(a.partials), o, p), p.nred);
+        const double r = merged_m2(static_cast<const Moments *>(a.partials), live ? o : 0, live, lane, p);
+        if (lane == 0 && live) sink.put(o, r, p.nred);
     }
 }
 
@@ -223,9 +304,14 @@ template <class T>
 __global__ void __launch_bounds__(64) var_combine_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
     const ReducePlan &p = a.plan;
     const Moments *partials = static_cast<const Moments *>(a.partials);
-    for (int64_t o = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; o < p.nout;
-         o += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        sink.put(o, merged_m2(partials, o, p), p.nred);
+    // (64 threads: eight outputs a block and round)
+    const int lane = threadIdx.x % kColumnFoldLanes;
+    const int64_t teams = blockDim.x / kColumnFoldLanes;
+    for (int64_t first = blockIdx.x * teams; first < p.nout; first += static_cast<int64_t>(gridDim.x) * teams) {
+        const int64_t o = first + threadIdx.x / kColumnFoldLanes;
+        const bool live = o < p.nout;
+        const double r = merged_m2(partials, live ? o : 0, live, lane, p);
+        if (lane == 0 && live) sink.put(o, r, p.nred);
     }
 }
 
@@ -346,10 +432,17 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
                 const bool self_merge = p.splits > 1 && a.tickets != nullptr && p.kouter * p.xtiles <= kTickets && p.splits <= kSelfFoldSplits;
                 ReduceArgs args = a;
                 if (!self_merge) args.tickets = nullptr;
-                var_columns_kernel<T><<<grid, kRThreads, 0, ctx->stream>>>(args, sink);
+                static bool raised[kKnownDevices] = {};  // (a race between threads only repeats the call)
+                if (ctx->device >= kKnownDevices || !raised[ctx->device]) {
+                    HMC_CUDA(cudaFuncSetAttribute(var_columns_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  static_cast<int>(kVarSharedBytes)),
+                             "shared memory size of the variance kernel");
+                    if (ctx->device < kKnownDevices) raised[ctx->device] = true;
+                }
+                var_columns_kernel<T><<<grid, kRThreads, kVarSharedBytes, ctx->stream>>>(args, sink);
                 hmc_status s1 = launch_status("var kernel launch");
                 if (s1 != HMC_OK || p.splits == 1 || self_merge) return s1;
-                var_combine_kernel<T><<<clamp_grid((p.nout + 63) / 64, 1 << 16), 64, 0, ctx->stream>>>(a, sink);
+                var_combine_kernel<T><<<clamp_grid((p.nout + 7) / 8, 1 << 16), 64, 0, ctx->stream>>>(a, sink);
                 return launch_status("var combine kernel launch");
             }
         }
