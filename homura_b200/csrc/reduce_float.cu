@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(kRThreads, 3) var_columns_kernel(const __grid_
         const int64_t stride = a.red.strides[0];
         const bool single = a.red.ndim == 1;
         const bool walk = single && whole && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
-                          (stride * static_cast<int64_t>(sizeof(T))) % 16 == 0;
+                          (stride * static_cast<int64_t>(sizeof(T))) % 16 == 0 && j1 - j0 < (int64_t{1} << 31);
         auto red_off = [&](int64_t j) { return single ? j * stride : decompose(a.red, j, a.red.ndim); };
         // the shift of each column: the first value of the chunk (shared by the block's warps), or, for long chunks, the
         // first value this thread meets
@@ -190,11 +190,11 @@ __global__ void __launch_bounds__(kRThreads, 3) var_columns_kernel(const __grid_
             // whole aligned vectors along one reduced dimension: this thread's rows are r = 0 .. rows - 1 at ptr + r * step
             const T *ptr = src + (j0 + ty) * stride;
             const int64_t step = 8 * stride;
-            const int64_t rows = (j1 - (j0 + ty) + 7) / 8;
+            const int rows = static_cast<int>((j1 - (j0 + ty) + 7) / 8);  // (32-bit counters: the loop's bookkeeping is a third of its instructions otherwise)
             static_assert(kVarStages % kVarBatch == 0, "a batch never wraps round the ring");
             // (the copies walk a pointer of their own, kVarStages rows ahead of the row that is consumed)
             const T *ahead = ptr;
-            int64_t to_copy = rows;
+            int to_copy = rows;
             auto request = [&](int slot) {  // (a group is committed also when there is nothing left to copy)
                 if (to_copy > 0) {
                     ring_copy_16(ring + slot * kRThreads, ahead);
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(kRThreads, 3) var_columns_kernel(const __grid_
                 ring_commit();
             };
             for (int slot = 0; slot < kVarStages; ++slot) request(slot);
-            int64_t r = 0;
+            int r = 0;
             int slot = 0;  // of row r
             for (; r + kVarBatch <= rows; r += kVarBatch) {
                 ring_wait<kVarStages - kVarBatch>();
@@ -426,11 +426,13 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
         }
         if constexpr (!std::is_same_v<T, double>) {
             if (p.kind == 1) {
-                if (p.kouter * p.xtiles > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 strips of outputs");
-                dim3 grid(static_cast<unsigned>(p.kouter * p.xtiles), static_cast<unsigned>(p.splits));
-                // few chunks: the block that finishes last merges its strip's; else a second kernel (same order)
-                const bool self_merge = p.splits > 1 && a.tickets != nullptr && p.kouter * p.xtiles <= kTickets && p.splits <= kSelfFoldSplits;
+                const int64_t strips = p.kouter * p.xtiles;
+                if (strips > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 strips of outputs");
                 ReduceArgs args = a;
+                const ReducePlan &q = args.plan;
+                dim3 grid(static_cast<unsigned>(strips), static_cast<unsigned>(q.splits));
+                // few chunks: the block that finishes last merges its strip's; else a second kernel (same order)
+                const bool self_merge = q.splits > 1 && a.tickets != nullptr && strips <= kTickets && q.splits <= kSelfFoldSplits;
                 if (!self_merge) args.tickets = nullptr;
                 static bool raised[kKnownDevices] = {};  // (a race between threads only repeats the call)
                 if (ctx->device >= kKnownDevices || !raised[ctx->device]) {
@@ -441,8 +443,8 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
                 }
                 var_columns_kernel<T><<<grid, kRThreads, kVarSharedBytes, ctx->stream>>>(args, sink);
                 hmc_status s1 = launch_status("var kernel launch");
-                if (s1 != HMC_OK || p.splits == 1 || self_merge) return s1;
-                var_combine_kernel<T><<<clamp_grid((p.nout + 7) / 8, 1 << 16), 64, 0, ctx->stream>>>(a, sink);
+                if (s1 != HMC_OK || q.splits == 1 || self_merge) return s1;
+                var_combine_kernel<T><<<clamp_grid((p.nout + 7) / 8, 1 << 16), 64, 0, ctx->stream>>>(args, sink);
                 return launch_status("var combine kernel launch");
             }
         }
