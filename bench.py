@@ -61,11 +61,11 @@ METRIC = "hbm_gbs_algorithmic"
 UNIT = "GB/s"
 WORKLOAD = "c2_elementwise_broadcast_bf16_8192x8192"
 REPEATS = 7
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel of the headline step, from one
-# `ncu --set full` capture on B200. Writes are below the algorithmic output where the tail of the output still
-# sits in L2 when the capture ends.
-NCU_TRAFFIC_BYTES = {"silu": 219.4e6, "mul_scale": 215.7e6, "add_bias": 345.7e6, "silu_t": 218.6e6, "mul_scale_t": 217.0e6,
-                     "add_bias_t": 347.3e6, "cast": 346.2e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel of the headline step, from one ncu
+# capture on B200 (profiles/c2_step_elementwise_kernels.md). Writes are below the algorithmic output where the
+# tail of the output still sits in L2 when the capture ends.
+NCU_TRAFFIC_BYTES = {"silu": 216.5e6, "mul_scale": 211.3e6, "add_bias": 340.7e6, "silu_t": 214.7e6, "mul_scale_t": 211.2e6,
+                     "add_bias_t": 341.1e6, "cast": 343.6e6}
 
 
 def philox_normal(n: int, seed: int) -> np.ndarray:
