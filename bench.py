@@ -62,7 +62,7 @@ UNIT = "GB/s"
 WORKLOAD = "c2_elementwise_broadcast_bf16_8192x8192"
 REPEATS = 7
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel of the headline step, from one ncu
-# capture on B200 (profiles/c2_step_elementwise_kernels.md). Writes are below the algorithmic output where the
+# capture on B200 (summarised under profiles/). Writes are below the algorithmic output where the
 # tail of the output still sits in L2 when the capture ends.
 NCU_TRAFFIC_BYTES = {"silu": 216.5e6, "mul_scale": 211.3e6, "add_bias": 340.7e6, "silu_t": 214.7e6, "mul_scale_t": 211.2e6,
                      "add_bias_t": 341.1e6, "cast": 343.6e6}
@@ -613,7 +613,7 @@ class Runner:
 
 def roofline_of(w, per_op: dict, traffic: dict | None = None) -> dict:
     """The roofline entry of a workload: its kernel furthest below the HBM peak that carries real traffic (ops
-    of a few KB, such as folding 291 partial sums, are launch-bound and not judged against bandwidth)."""
+    of a few KB, such as folding 291 partial sums, are launch-bound and not measured against bandwidth)."""
     peak, peak_kind = peaks()
     gbs = {k: w.op_bytes[k] / (v * 1e-3) / 1e9 for k, v in per_op.items()}
     streaming = [k for k in per_op if w.op_bytes[k] >= (64 << 20)] or list(per_op)

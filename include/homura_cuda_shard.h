@@ -58,9 +58,9 @@ hmc_status hmc_shard_combine_extreme(hmc_context_t ctx, int32_t is_max, const hm
 
 /* Variance / standard deviation across shards, two rounds as on one GPU (cpu::var, src/backend/cpu/reduce.rs:135-170:
  * the mean in f64, then the squared deviations from it):
- *   round 1: hmc_reduce_partial(SUM) -> all-gather -> hmc_shard_combine_means: means[o] = (sum over the ranks in
+ *   first exchange: hmc_reduce_partial(SUM) -> all-gather -> hmc_shard_combine_means: means[o] = (sum over the ranks in
  *            rank order) / total_count, kept in f64 (one per output, device memory);
- *   round 2: hmc_var_partial: partial[o] = the f64 sum over this shard of (x - means[o])^2 (workspace as for
+ *   second exchange: hmc_var_partial: partial[o] = the f64 sum over this shard of (x - means[o])^2 (workspace as for
  *            hmc_reduce) -> all-gather -> hmc_shard_combine_var: out[o] = round(sum over the ranks / (total_count -
  *            correction)), its square root with take_sqrt, NaN when total_count is 0, infinity or NaN when the
  *            divisor is not positive (as hmc_var). */

@@ -14,7 +14,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 LIB = HERE / "_build" / "liboracle.so"
 REF_LIB = HERE / "_ref" / "libref_casts.so"
-# A checkout of homura, if there is one: HOMURA_SRC names it (README.md gives the default of the build machine).
+# A checkout of homura, if there is one: HOMURA_SRC names it (the default is a `reference` directory in the home directory).
 REFERENCE = Path(os.environ.get("HOMURA_SRC") or Path.home() / "reference")
 CXXFLAGS = ["-O2", "-std=c++17", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared", "-Wall", "-Wno-sign-compare",
             "-Wno-type-limits"]

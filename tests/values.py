@@ -1,4 +1,4 @@
-"""Inputs and judges of the differential tests, after homura's tests/common/rocm.rs: deterministic words
+"""Inputs and comparisons of the differential tests, after homura's tests/common/rocm.rs: deterministic words
 (SplitMix64), special values of every dtype followed by random *bit patterns* (every float pattern can
 occur, NaN payloads and subnormals included), the eleven layouts every kernel is run on, and the comparison
 classes (same bits with NaN ~ NaN; distance in ulps; bounded absolute error)."""
