@@ -64,8 +64,8 @@ REPEATS = 7
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel of the headline step, from one ncu
 # capture on B200 (summarised under profiles/). Writes are below the algorithmic output where the
 # tail of the output still sits in L2 when the capture ends.
-NCU_TRAFFIC_BYTES = {"silu": 216.5e6, "mul_scale": 211.3e6, "add_bias": 340.7e6, "silu_t": 214.7e6, "mul_scale_t": 211.2e6,
-                     "add_bias_t": 341.1e6, "cast": 343.6e6}
+NCU_TRAFFIC_BYTES = {"silu": 216.6e6, "mul_scale": 213.2e6, "add_bias": 342.4e6, "silu_t": 215.0e6, "mul_scale_t": 213.4e6,
+                     "add_bias_t": 343.6e6, "cast": 343.6e6}
 
 
 def philox_normal(n: int, seed: int) -> np.ndarray:

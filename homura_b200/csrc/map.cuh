@@ -419,6 +419,7 @@ __global__ void __launch_bounds__(kThreads, HMC_MAP_MIN_BLOCKS) map_kernel(const
 // Resident blocks per SM the lean kernel is compiled for: 4 (64 registers) by default; functors that need few
 // registers can ask for more by specialising this, which puts more loads in flight for latency-bound layouts.
 template <class F> struct LeanMinBlocks { static constexpr int value = 4; };
+constexpr int64_t kLeanBlocksWanted = 148 * 16;  // blocks below which a launch keeps one row per block
 struct LeanArgs {
     char *base[kOperands];
     int64_t row_stride[kOperands];  // elements
@@ -923,7 +924,16 @@ hmc_status launch_map(hmc_context_t ctx, const F &f, const hmc_tensor_desc *out,
                                       size_or_zero<typename F::B>(), size_or_zero<typename F::C>()};
         if (a.tile_mask == 0 && build_lean_args(lean, a, sizes, vec_of<F>())) {
             const int64_t chunk = static_cast<int64_t>(kThreads) * vec_of<F>() * unroll_of<F>();
-            dim3 grid(static_cast<unsigned>(ceil_div(lean.n0, chunk)), static_cast<unsigned>(lean.rows < 65535 ? lean.rows : 65535));
+            // A block takes up to four rows (row y, y + grid.y, ...) while that leaves enough blocks to fill the GPU
+            // several times over: a thread's set-up is paid once, and a quarter of the blocks are scheduled.
+            // Measured on B200 for bf16 [8192, 8192] times a row-broadcast scale: 47.1 us with one row a block, 43.4
+            // with two, 43.0 with four, 45.0 with eight. (Cutting a long single row into such rows as well measured
+            // 4 % slower for a bf16 silu and 2 % slower for an f32 product of 2^29 elements.)
+            const int64_t gx = ceil_div(lean.n0, chunk);
+            int64_t per_block = 1;
+            while (per_block < 4 && gx * ceil_div(lean.rows, per_block * 2) >= kLeanBlocksWanted) per_block *= 2;
+            const int64_t gy = ceil_div(lean.rows, per_block);
+            dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy < 65535 ? gy : 65535));
             map_lean_kernel<F><<<grid, kThreads, 0, ctx->stream>>>(lean, f);
             return launch_status("elementwise kernel launch");
         }
