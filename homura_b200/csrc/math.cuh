@@ -4,13 +4,16 @@
 // roundings unless fma() is spelled out, which is where the CPU calls mul_add.
 //
 // exp, log, log1p, tanh and pow of the float computation type restate the host C library's algorithms and
-// return its bits (libm32.cuh). sin, cos and erf of the float computation type are evaluated in double and
+// return its bits (libm32.cuh); so do exp, log1p and tanh of the double computation type (libm64.cuh), and with
+// them sigmoid, silu, log_sigmoid, erf, gelu and gelu_tanh of F64 tensors; log, sin, cos and pow of F64 tensors are
+// the CUDA library's (within an ulp or two of the C library's). sin, cos and erf of the float computation type are evaluated in double and
 // rounded once: the correctly rounded f32 value except within ~1e-9 ulp of a tie, hence within one ulp of
 // the C library's sinf / cosf (whose own error is below one ulp) and of the CPU's f64 erf rounded to f32.
 #pragma once
 
 #include "elem.cuh"
 #include "libm32.cuh"
+#include "libm64.cuh"
 
 namespace hmc {
 
@@ -76,11 +79,11 @@ __device__ __forceinline__ double reciprocal_short(double s) {
 // The f32 exponential, logarithm, log1p, tanh and power return the host C library's bits (libm32.cuh), so
 // that formulas built on them (sigmoid, silu, log_sigmoid, gelu_tanh) are the CPU's bit for bit as well.
 __device__ __forceinline__ float m_exp(float x) { return lm::expf(x); }
-__device__ __forceinline__ double m_exp(double x) { return exp(x); }
+__device__ __forceinline__ double m_exp(double x) { return lm64::exp(x); }
 __device__ __forceinline__ float m_log(float x) { return lm::logf(x); }
 __device__ __forceinline__ double m_log(double x) { return log(x); }
 __device__ __forceinline__ float m_log1p(float x) { return lm::log1pf(x); }
-__device__ __forceinline__ double m_log1p(double x) { return log1p(x); }
+__device__ __forceinline__ double m_log1p(double x) { return lm64::log1p(x); }
 __device__ __forceinline__ float m_sqrt(float x) { return sqrtf(x); }
 __device__ __forceinline__ double m_sqrt(double x) { return sqrt(x); }
 __device__ __forceinline__ float m_sin(float x) { return static_cast<float>(sin(static_cast<double>(x))); }
@@ -88,7 +91,7 @@ __device__ __forceinline__ double m_sin(double x) { return sin(x); }
 __device__ __forceinline__ float m_cos(float x) { return static_cast<float>(cos(static_cast<double>(x))); }
 __device__ __forceinline__ double m_cos(double x) { return cos(x); }
 __device__ __forceinline__ float m_tanh(float x) { return lm::tanhf(x); }
-__device__ __forceinline__ double m_tanh(double x) { return tanh(x); }
+__device__ __forceinline__ double m_tanh(double x) { return lm64::tanh(x); }
 __device__ __forceinline__ float m_pow(float x, float y) {
     // x^2 (homura's `x.pow(2)`, e.g. in its rms_norm) is x * x rounded once. The C library's powf(x, 2) is within
     // 0.82 ulp of x^2 but not always the nearest value, so this differs from the CPU's result by one ulp for about
@@ -118,11 +121,11 @@ __device__ inline double erf_series(double x) {
             term *= 2.0 * x2 / (2.0 * n + 1.0);
             sum += term;
         }
-        r = 1.12837916709551257390 * exp(-x2) * sum;
+        r = 1.12837916709551257390 * lm64::exp(-x2) * sum;
     } else if (ax < 6.0) {
         double f = ax;
         for (int k = 80; k >= 1; --k) f = ax + (static_cast<double>(k) * 0.5) / f;
-        r = 1.0 - exp(-ax * ax) / (1.7724538509055159 * f);
+        r = 1.0 - lm64::exp(-ax * ax) / (1.7724538509055159 * f);
     } else {
         r = 1.0;
     }

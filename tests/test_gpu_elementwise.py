@@ -78,6 +78,11 @@ ULP_REPORT = {}
 ULP_BAR = {"exp": 0, "log": 0, "tanh": 0, "sigmoid": 0, "silu": 0, "log_sigmoid": 0, "gelu_tanh": 0,
            "sin": 1, "cos": 1, "erf": 1, "gelu": 1}
 HALF_FAST = ("exp", "sigmoid", "silu")
+# F64 tensors: exp, tanh and log1p restate the C library's double-precision algorithms as well
+# (homura_b200/csrc/libm64.cuh), so every op built on them alone has the CPU's bits; log, sin and cos are the CUDA
+# library's against glibc's (each within an ulp of the true value).
+ULP_BAR_F64 = {"exp": 0, "tanh": 0, "sigmoid": 0, "silu": 0, "log_sigmoid": 0, "gelu_tanh": 0, "erf": 0, "gelu": 0,
+               "log": 1, "sin": 1, "cos": 1}
 
 
 @pytest.mark.parametrize("op", list(TRANSCENDENTAL))
@@ -103,9 +108,11 @@ def test_transcendental_unary_ops(oracle, cuda, op, dtype):
         worst, differ, total = max(worst, mu), differ + nd, total + want.size
     ULP_REPORT[(op, DTYPE_NAMES[dtype])] = (worst, differ, total)
     print(f"ulp {op:<12} {DTYPE_NAMES[dtype]:<5}: max {worst} ulp, {differ} of {total} elements differ")
-    if dtype != F64:
+    if dtype == F64:
+        bar = ULP_BAR_F64[op]
+    else:
         bar = 1 if (dtype in (F16, BF16) and op in HALF_FAST) else ULP_BAR[op]
-        assert worst <= bar, f"{op}: {worst} ulp from the CPU result (bar {bar}), {differ} of {total} differ"
+    assert worst <= bar, f"{op}: {worst} ulp from the CPU result (bar {bar}), {differ} of {total} differ"
 
 
 def test_the_bound_rejects_wrong_results(oracle, cuda):
