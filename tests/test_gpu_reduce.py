@@ -24,6 +24,8 @@ SHAPES = [
     ((64, 2048), [1]), ((2048, 64), [0]), ((1 << 20,), []), ((4, 5), [0, 1]), ((1, 1), [0]), ((6, 0), [1]), ((0, 6), [1]),
     # long rows folded by one warp each (many outputs): whole vectors, and a ragged row length
     ((4800, 1028), [1]), ((4740, 1026), [1]),
+    # a tall strip of columns: hundreds of chunks, folded by a second kernel instead of the last block
+    ((400000, 40), [0]),
 ]
 
 
@@ -59,6 +61,7 @@ def test_every_plan_is_reached(cuda):
         seen.add((kind, splits > 1))
     for want in [(1001, False), (1032, False), (1256, False), (1256, True), (1, False), (1, True)]:
         assert want in seen, f"no shape reaches plan {want}: {sorted(seen)}"
+    assert plan_of(cuda, cuda.empty((400000, 40), F32), [True, False])[1] > 64, "the tall strip is not cut into many chunks"
 
 
 @pytest.mark.parametrize("dtype", ALL_DTYPES, ids=DTYPE_NAMES)
