@@ -479,11 +479,33 @@ __global__ void __launch_bounds__(kRThreads, is_extreme<Op>::value ? 3 : 4) redu
     if (lane == 0 && live) sink.put(o, acc, p.nred);
 }
 
-// The lanes that share the partials of an output of the column kernel when there are few chunks (lane l folds
-// chunks l, l + 8, ... in order, the lanes are folded in lane order): the block that finishes last has 128 or 256
-// outputs to fold, and a thread per output reading its partials one after another would stretch the kernel's end
-// over a dozen round trips to the L2.
-constexpr int kColumnFoldLanes = 8;
+// The partials of a strip of W outputs (W = 64, 128 or 256) folded by one block: thread t takes output t % W and, of
+// its chunks, every (256 / W)-th starting with chunk t / W, in order, with all its loads (or sixteen at a time)
+// in flight at once; the threads of an output are then folded in that order. A warp reads 32 neighbouring outputs
+// of one chunk, whole sectors. (A block that walked through its outputs a few at a time, one round trip to the L2
+// after another, took 7 us for 128 outputs of 32 chunks; this takes under 2.)
+template <int W, class Op>
+__device__ __forceinline__ typename Op::Acc strip_share(const Op &op, const typename Op::Acc *partials, int64_t o, bool live,
+                                                        int h, const ReducePlan &p) {
+    using Acc = typename Op::Acc;
+    constexpr int H = kRThreads / W;
+    constexpr int B = sizeof(Acc) > 8 ? 8 : 16;
+    Acc acc = op.init();
+    if (live) {
+        for (int64_t c0 = h; c0 < p.splits; c0 += static_cast<int64_t>(B) * H) {
+            Acc x[B];
+#pragma unroll
+            for (int u = 0; u < B; ++u) {
+                if (c0 + u * H < p.splits) x[u] = load_partial(partials + (c0 + u * H) * p.nout + o);
+            }
+#pragma unroll
+            for (int u = 0; u < B; ++u) {
+                if (c0 + u * H < p.splits) acc = op.combine(acc, x[u]);
+            }
+        }
+    }
+    return acc;
+}
 
 // kind 1. Grid: (kouter * xtiles, splits), every block launched at once; block 32 x 8: thread (tx, ty) owns the VC
 // adjacent outputs tx * VC .. of its strip of 32 * VC outputs and folds the reduced indices j0 + ty, j0 + ty + 8, ...
@@ -570,17 +592,50 @@ __global__ void __launch_bounds__(kRThreads, is_extreme<Op>::value ? 2 : 4) redu
         }
     }
     if (p.splits == 1 || a.tickets == nullptr || !drew_last_ticket(a.tickets)) return;
-    // the strip's outputs, each by a team of kColumnFoldLanes lanes
-    constexpr int kTeams = kRThreads / kColumnFoldLanes;
-    const int lane = threadIdx.x % kColumnFoldLanes;
-#pragma unroll 2
-    for (int first = 0; first < 32 * VC; first += kTeams) {
-        const int64_t c = tile * (32 * VC) + first + threadIdx.x / kColumnFoldLanes;
-        const bool live = c < p.ncols;
-        const int64_t o = outer * p.ncols + c;
-        const Acc r = fold_team<kColumnFoldLanes>(op, team_partials<kColumnFoldLanes>(op, partials, live ? o : 0, live, lane, p));
-        if (lane == 0 && live) sink.put(o, r, p.nred);
+    // the strip's outputs (the warps' staging area is free again: every thread passed the ticket's barriers)
+    constexpr int W = 32 * VC, H = kRThreads / W;
+    const int w = threadIdx.x % W, h = threadIdx.x / W;
+    const int64_t c = tile * W + w;
+    const bool live = c < p.ncols;
+    const int64_t o = outer * p.ncols + c;
+    Acc r = strip_share<W>(op, partials, live ? o : 0, live, h, p);
+    if constexpr (H > 1) {
+        if (h > 0) stage[h - 1][w] = r;
+        __syncthreads();
+        if (h == 0) {
+#pragma unroll
+            for (int k = 1; k < H; ++k) r = op.combine(r, stage[k - 1][w]);
+        }
     }
+    if (h == 0 && live) sink.put(o, r, p.nred);
+}
+
+// The same fold as a kernel of its own, for launches whose blocks cannot take tickets. Grid: one block per strip.
+template <class Op, class Sink>
+__global__ void __launch_bounds__(kRThreads) reduce_strip_combine_kernel(const __grid_constant__ ReduceArgs a, const Op op,
+                                                                         const Sink sink) {
+    using T = typename Op::T;
+    using Acc = typename Op::Acc;
+    constexpr int VC = (16 / sizeof(T)) > 8 ? 8 : (16 / sizeof(T));
+    constexpr int W = 32 * VC, H = kRThreads / W;
+    const ReducePlan &p = a.plan;
+    __shared__ Acc stage[H > 1 ? H - 1 : 1][W];
+    const int64_t outer = blockIdx.x / p.xtiles;
+    const int64_t tile = blockIdx.x - outer * p.xtiles;
+    const int w = threadIdx.x % W, h = threadIdx.x / W;
+    const int64_t c = tile * W + w;
+    const bool live = c < p.ncols;
+    const int64_t o = outer * p.ncols + c;
+    Acc r = strip_share<W>(op, static_cast<const Acc *>(a.partials), live ? o : 0, live, h, p);
+    if constexpr (H > 1) {
+        if (h > 0) stage[h - 1][w] = r;
+        __syncthreads();
+        if (h == 0) {
+#pragma unroll
+            for (int k = 1; k < H; ++k) r = op.combine(r, stage[k - 1][w]);
+        }
+    }
+    if (h == 0 && live) sink.put(o, r, p.nred);
 }
 
 // The partials of an output folded in chunk order by a team of L lanes (1, 32 or 256): lane l takes chunks
@@ -598,8 +653,8 @@ __global__ void __launch_bounds__(kRThreads) reduce_combine_kernel(const __grid_
     if (lane == 0 && live) sink.put(o, acc, p.nred);
 }
 
-// The number of partials up to which the block that finishes last folds them itself where only a few lanes share an
-// output's partials (columns: eight; single-lane rows: one); teams of 32 and 256 lanes always do.
+// The number of partials up to which the block that finishes last folds them itself where few threads share an
+// output's partials (columns: one to four; single-lane rows: one); teams of 32 and 256 lanes always do.
 constexpr int64_t kSelfFoldSplits = 64;
 
 inline unsigned clamp_grid(int64_t n, int64_t cap) { return static_cast<unsigned>(n < cap ? (n < 1 ? 1 : n) : cap); }
@@ -611,11 +666,11 @@ hmc_status launch_reduce(const ReduceArgs &a, const Op &op, const Sink &sink, cu
     const ReducePlan &p = a.plan;
     if (p.nout == 0) return HMC_OK;
     // the lanes that share an output's partials (part of the fold order, so a function of the plan alone)
-    const int lanes = p.kind == 0 ? p.group : (p.splits > kSelfFoldSplits ? 32 : kColumnFoldLanes);
+    const int lanes = p.kind == 0 ? p.group : (p.splits > kSelfFoldSplits ? 32 : 0);  // (0: the strip's block folds)
     ReduceArgs args = a;
     const int64_t blocks_x = p.kind == 1 ? p.kouter * p.xtiles : (p.nout + kRThreads / p.group - 1) / (kRThreads / p.group);
     const bool self_fold = p.splits > 1 && a.tickets != nullptr && blocks_x <= kTickets &&
-                           (p.kind == 0 ? (p.group > 1 || p.splits <= kSelfFoldSplits) : lanes == kColumnFoldLanes);
+                           (p.kind == 0 ? (p.group > 1 || p.splits <= kSelfFoldSplits) : lanes == 0);
     if (!self_fold) args.tickets = nullptr;
     if (p.kind == 1) {
         if (blocks_x > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 strips of outputs");
@@ -631,13 +686,16 @@ hmc_status launch_reduce(const ReduceArgs &a, const Op &op, const Sink &sink, cu
     hmc_status s = launch_status("reduction kernel launch");
     if (s != HMC_OK) return s;
     if (p.splits > 1 && !self_fold) {
-        const int64_t blocks = (p.nout + kRThreads / lanes - 1) / (kRThreads / lanes);
-        if (blocks > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
-        const unsigned grid = static_cast<unsigned>(blocks);
-        if (lanes == 256) reduce_combine_kernel<256, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
-        else if (lanes == 32) reduce_combine_kernel<32, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
-        else if (lanes == kColumnFoldLanes) reduce_combine_kernel<kColumnFoldLanes, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
-        else reduce_combine_kernel<1, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        if (lanes == 0) {
+            reduce_strip_combine_kernel<Op, Sink><<<static_cast<unsigned>(blocks_x), kRThreads, 0, stream>>>(a, op, sink);
+        } else {
+            const int64_t blocks = (p.nout + kRThreads / lanes - 1) / (kRThreads / lanes);
+            if (blocks > 0x7FFFFFFF) return fail(HMC_INVALID, "a reduction with more than 2^31 blocks of outputs");
+            const unsigned grid = static_cast<unsigned>(blocks);
+            if (lanes == 256) reduce_combine_kernel<256, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+            else if (lanes == 32) reduce_combine_kernel<32, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+            else reduce_combine_kernel<1, Op, Sink><<<grid, kRThreads, 0, stream>>>(a, op, sink);
+        }
         s = launch_status("reduction combine kernel launch");
     }
     return s;

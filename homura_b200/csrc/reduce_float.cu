@@ -83,38 +83,85 @@ __device__ __forceinline__ void merge_moments(double &n, double &mean, double &m
     n = total;
 }
 
-// The chunks' moments of output o merged by a team of kColumnFoldLanes lanes (a chunk's count follows from the plan):
-// lane l merges chunks l, l + 8, ... in order, then the lanes are merged in lane order. Valid in the team's lane 0;
-// all lanes of the warp call it.
-__device__ __forceinline__ double merged_m2(const Moments *partials, int64_t o, bool live, int lane, const ReducePlan &p) {
-    double n = 0.0, mean = 0.0, m2 = 0.0;
-    auto count = [&](int64_t c) {
-        const int64_t j0 = c * p.chunk;
-        const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
-        return static_cast<double>(j1 - j0);
-    };
-    if (live) {
-        int64_t c = lane;
-        for (; c + 3 * kColumnFoldLanes < p.splits; c += 4 * kColumnFoldLanes) {
-            Moments m[4];
+// A thread's share of the chunks' partials of output o in the fold of a strip (see strip_share): chunks h, h + H, ...
+// in order, four loads in flight. With a shift common to all chunks the partials are the sums (s, q) themselves
+// and simply add up (n counts nothing then); otherwise they are (mean, M2) pairs merged with their counts, which
+// follow from the plan.
+struct MomentShare {
+    double n, a, b;
+};
+template <int W>
+__device__ __forceinline__ MomentShare moment_share(const Moments *partials, int64_t o, bool live, int h, const ReducePlan &p,
+                                                    bool common_shift) {
+    constexpr int H = kRThreads / W;
+    constexpr int B = 4;
+    MomentShare r{0.0, 0.0, 0.0};
+    if (!live) return r;
+    for (int64_t c0 = h; c0 < p.splits; c0 += static_cast<int64_t>(B) * H) {
+        Moments m[B];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) m[u] = load_partial(partials + (c + u * kColumnFoldLanes) * p.nout + o);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) merge_moments(n, mean, m2, count(c + u * kColumnFoldLanes), m[u].mean, m[u].m2);
+        for (int u = 0; u < B; ++u) {
+            if (c0 + u * H < p.splits) m[u] = load_partial(partials + (c0 + u * H) * p.nout + o);
         }
-        for (; c < p.splits; c += kColumnFoldLanes) {
-            const Moments m = load_partial(partials + c * p.nout + o);
-            merge_moments(n, mean, m2, count(c), m.mean, m.m2);
+#pragma unroll
+        for (int u = 0; u < B; ++u) {
+            const int64_t c = c0 + u * H;
+            if (c < p.splits) {
+                if (common_shift) {
+                    r.a += m[u].mean;
+                    r.b += m[u].m2;
+                } else {
+                    const int64_t j0 = c * p.chunk;
+                    const int64_t j1 = j0 + p.chunk < p.nred ? j0 + p.chunk : p.nred;
+                    merge_moments(r.n, r.a, r.b, static_cast<double>(j1 - j0), m[u].mean, m[u].m2);
+                }
+            }
         }
     }
+    return r;
+}
+
+// The strip's fold, by every thread of a block; `memory` holds 3 * (H - 1) * W doubles.
+template <int W, class Sink>
+__device__ __forceinline__ void fold_moment_strip(const ReduceArgs &a, int64_t outer, int64_t tile, bool common_shift, double *memory,
+                                                  const Sink &sink) {
+    constexpr int H = kRThreads / W;
+    const ReducePlan &p = a.plan;
+    const int w = threadIdx.x % W, h = threadIdx.x / W;
+    const int64_t c = tile * W + w;
+    const bool live = c < p.ncols;
+    const int64_t o = outer * p.ncols + c;
+    MomentShare r = moment_share<W>(static_cast<const Moments *>(a.partials), live ? o : 0, live, h, p, common_shift);
+    if constexpr (H > 1) {
+        if (h > 0) {
+            double *slot = memory + (static_cast<size_t>(h - 1) * W + w) * 3;
+            slot[0] = r.n;
+            slot[1] = r.a;
+            slot[2] = r.b;
+        }
+        __syncthreads();
+        if (h == 0) {
 #pragma unroll
-    for (int d = 1; d < kColumnFoldLanes; d <<= 1) {
-        const double on = __shfl_down_sync(0xFFFFFFFFu, n, d);
-        const double om = __shfl_down_sync(0xFFFFFFFFu, mean, d);
-        const double o2 = __shfl_down_sync(0xFFFFFFFFu, m2, d);
-        merge_moments(n, mean, m2, on, om, o2);
+            for (int k = 1; k < H; ++k) {
+                const double *slot = memory + (static_cast<size_t>(k - 1) * W + w) * 3;
+                if (common_shift) {
+                    r.a += slot[1];
+                    r.b += slot[2];
+                } else {
+                    merge_moments(r.n, r.a, r.b, slot[0], slot[1], slot[2]);
+                }
+            }
+        }
     }
-    return m2;
+    if (h == 0 && live) {
+        double m2 = r.b;
+        if (common_shift) {
+            // (s, q) over the whole column about one shift: M2 = q - s^2 / n
+            const double spread = r.b - r.a * r.a * reciprocal_short(static_cast<double>(p.nred));
+            m2 = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);
+        }
+        sink.put(o, m2, p.nred);
+    }
 }
 
 // Block 32 x 8 as in the column kernel of the engine: thread (tx, ty) owns VC adjacent columns of its strip and the rows
@@ -125,6 +172,7 @@ __device__ __forceinline__ double merged_m2(const Moments *partials, int64_t o, 
 constexpr int kVarStages = 16;
 constexpr int kKnownDevices = 64;
 constexpr int64_t kSharedShiftRows = 4096;
+constexpr int64_t kCommonShiftRows = int64_t{1} << 18;
 constexpr int kVarBatch = 4;  // slots consumed and refilled at a time
 constexpr size_t kVarSharedBytes = static_cast<size_t>(kVarStages) * kRThreads * 16;
 
@@ -161,6 +209,10 @@ __global__ void __launch_bounds__(kRThreads, 3) var_columns_kernel(const __grid_
     // add up, which spares every block eight merges and a division at its end (the cancellation in q - s^2 / n grows
     // with the number of values that share a shift: at most log2(rows + 1) bits, 12 of an f64's 53 here).
     const bool shared_shift = j1 - j0 <= kSharedShiftRows;
+    // With several chunks of a column that is not too long, all of them take the column's first value: their sums
+    // (s, q) then add up across chunks as well, and the fold at the end needs no merges (the cancellation bound
+    // becomes log2(nred + 1) bits, 18 at most here, of which the accumulation error of a thread's 512 rows leaves 26).
+    const bool common_shift = (p.chunk < p.nred ? p.chunk : p.nred) <= kSharedShiftRows && p.splits > 1 && p.nred <= kCommonShiftRows;
     if (in_range && j0 + ty < j1) {
         const int64_t stride = a.red.strides[0];
         const bool single = a.red.ndim == 1;
@@ -171,7 +223,7 @@ __global__ void __launch_bounds__(kRThreads, 3) var_columns_kernel(const __grid_
         // first value this thread meets
         double shift[VC], s[VC], q[VC];
         {
-            const T *first = src + red_off(shared_shift ? j0 : j0 + ty);
+            const T *first = src + red_off(common_shift ? 0 : (shared_shift ? j0 : j0 + ty));
 #pragma unroll
             for (int e = 0; e < VC; ++e) {
                 shift[e] = c0 + e < p.ncols ? to_f64(first[e]) : 0.0;
@@ -273,11 +325,13 @@ __global__ void __launch_bounds__(kRThreads, 3) var_columns_kernel(const __grid_
                     cm += stage_mean[w][tx * VC + e];
                     c2 += stage_m2[w][tx * VC + e];
                 }
-                const double rows = static_cast<double>(j1 - j0);
-                const double inv = reciprocal_short(rows);
-                const double spread = c2 - cm * cm * inv;
-                c2 = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);
-                cm = held[e] + cm * inv;
+                if (!common_shift) {
+                    const double rows = static_cast<double>(j1 - j0);
+                    const double inv = reciprocal_short(rows);
+                    const double spread = c2 - cm * cm * inv;
+                    c2 = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);
+                    cm = held[e] + cm * inv;
+                }
             } else {
                 for (int w = 0; w < 7; ++w) merge_moments(cn, cm, c2, stage_n[w + 1], stage_mean[w][tx * VC + e], stage_m2[w][tx * VC + e]);
             }
@@ -286,33 +340,22 @@ __global__ void __launch_bounds__(kRThreads, 3) var_columns_kernel(const __grid_
         }
     }
     if (p.splits == 1 || a.tickets == nullptr || !drew_last_ticket(a.tickets)) return;
-    // this block is the last of its strip's: the strip's outputs, each by a team of lanes
-    constexpr int kTeams = kRThreads / kColumnFoldLanes;
-    const int lane = threadIdx.x % kColumnFoldLanes;
-#pragma unroll 2
-    for (int first = 0; first < 32 * VC; first += kTeams) {
-        const int64_t c = tile * (32 * VC) + first + threadIdx.x / kColumnFoldLanes;
-        const bool live = c < p.ncols;
-        const int64_t o = outer * p.ncols + c;
-        const double r = merged_m2(static_cast<const Moments *>(a.partials), live ? o : 0, live, lane, p);
-        if (lane == 0 && live) sink.put(o, r, p.nred);
-    }
+    // this block is the last of its strip's (and every thread is past the staging area): fold the strip
+    fold_moment_strip<32 * VC>(a, outer, tile, common_shift, reinterpret_cast<double *>(var_shared), sink);
 }
 
-// The chunks' moments of each output merged in chunk order (a chunk's count follows from the plan).
+// The same fold as a kernel of its own (more chunks than a last block folds, or no counters). Grid: one block per strip.
 template <class T>
-__global__ void __launch_bounds__(64) var_combine_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+__global__ void __launch_bounds__(kRThreads) var_combine_kernel(const __grid_constant__ ReduceArgs a, const VarSink<T> sink) {
+    constexpr int VC = (16 / sizeof(T)) > 8 ? 8 : (16 / sizeof(T));
+    constexpr int W = 32 * VC, H = kRThreads / W;
+    __shared__ double memory[3 * (H > 1 ? H - 1 : 1) * W];
     const ReducePlan &p = a.plan;
-    const Moments *partials = static_cast<const Moments *>(a.partials);
-    // (64 threads: eight outputs a block and round)
-    const int lane = threadIdx.x % kColumnFoldLanes;
-    const int64_t teams = blockDim.x / kColumnFoldLanes;
-    for (int64_t first = blockIdx.x * teams; first < p.nout; first += static_cast<int64_t>(gridDim.x) * teams) {
-        const int64_t o = first + threadIdx.x / kColumnFoldLanes;
-        const bool live = o < p.nout;
-        const double r = merged_m2(partials, live ? o : 0, live, lane, p);
-        if (lane == 0 && live) sink.put(o, r, p.nred);
-    }
+    const int64_t outer = blockIdx.x / p.xtiles;
+    const int64_t tile = blockIdx.x - outer * p.xtiles;
+    const int64_t chunk_rows = p.chunk < p.nred ? p.chunk : p.nred;
+    const bool common_shift = chunk_rows <= kSharedShiftRows && p.splits > 1 && p.nred <= kCommonShiftRows;
+    fold_moment_strip<W>(a, outer, tile, common_shift, memory, sink);
 }
 
 // ---- variance over rows in one pass ----
@@ -444,7 +487,7 @@ hmc_status reduce_var(hmc_context_t ctx, const hmc_tensor_desc *out, ReduceArgs 
                 var_columns_kernel<T><<<grid, kRThreads, kVarSharedBytes, ctx->stream>>>(args, sink);
                 hmc_status s1 = launch_status("var kernel launch");
                 if (s1 != HMC_OK || q.splits == 1 || self_merge) return s1;
-                var_combine_kernel<T><<<clamp_grid((p.nout + 7) / 8, 1 << 16), 64, 0, ctx->stream>>>(args, sink);
+                var_combine_kernel<T><<<static_cast<unsigned>(strips), kRThreads, 0, ctx->stream>>>(args, sink);
                 return launch_status("var combine kernel launch");
             }
         }
