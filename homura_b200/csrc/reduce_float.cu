@@ -173,6 +173,7 @@ constexpr int kVarStages = 16;
 constexpr int kKnownDevices = 64;
 constexpr int64_t kSharedShiftRows = 4096;
 constexpr int64_t kCommonShiftRows = int64_t{1} << 18;
+constexpr int64_t kRowShiftElements = int64_t{1} << 16;
 constexpr int kVarBatch = 4;  // slots consumed and refilled at a time
 constexpr size_t kVarSharedBytes = static_cast<size_t>(kVarStages) * kRThreads * 16;
 
@@ -379,9 +380,13 @@ __global__ void __launch_bounds__(kRThreads, 4) var_rows_kernel(const __grid_con
     const int64_t o = static_cast<int64_t>(blockIdx.x) * kTeams + threadIdx.x / G;
     const bool live = o < p.nout;
     double n = 0.0, mean = 0.0, m2 = 0.0;
+    // Rows of up to kRowShiftElements share one shift, the row's first element: the lanes' sums then simply add up
+    // (shuffles and additions instead of five merges with a reciprocal each per row), at a cancellation of at most
+    // log2(nred + 1) = 16 bits, of which the accumulation error of a lane's 2048 elements leaves 26.
+    const bool row_shift = p.nred <= kRowShiftElements;
     if (live && static_cast<uint32_t>(lane) < pieces) {
         const T *row = static_cast<const T *>(a.kept.data) + a.kept.offset + decompose(a.kept, o, a.kept.ndim);
-        const double shift = to_f64(row[static_cast<size_t>(lane) * N]);
+        const double shift = to_f64(row[row_shift ? 0 : static_cast<size_t>(lane) * N]);
         double s[K], q[K];
 #pragma unroll
         for (int k = 0; k < K; ++k) s[k] = q[k] = 0.0;
@@ -403,10 +408,44 @@ __global__ void __launch_bounds__(kRThreads, 4) var_rows_kernel(const __grid_con
         }
         for (; w < pieces; w += G, ++taken) take(load_piece(row + static_cast<size_t>(w) * N));
         double st = (s[0] + s[1]) + (s[2] + s[3]), qt = (q[0] + q[1]) + (q[2] + q[3]);
-        n = static_cast<double>(taken) * N;
-        mean = shift + st / n;
-        const double spread = qt - st * st / n;
-        m2 = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);
+        if (row_shift) {
+            mean = st;  // (the sums travel in the places of mean and M2)
+            m2 = qt;
+        } else {
+            n = static_cast<double>(taken) * N;
+            mean = shift + st / n;
+            const double spread = qt - st * st / n;
+            m2 = spread > 0.0 ? spread : (spread == spread ? 0.0 : spread);
+        }
+    }
+    if (row_shift) {
+        // the lanes' sums in lane order, the warps' in warp order, then the row's M2 from them
+        if constexpr (G > 1) {
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                mean += __shfl_down_sync(0xFFFFFFFFu, mean, d);
+                m2 += __shfl_down_sync(0xFFFFFFFFu, m2, d);
+            }
+        }
+        if constexpr (G == 256) {
+            const int warp = threadIdx.x >> 5;
+            if ((threadIdx.x & 31) == 0) {
+                warp_mean[warp] = mean;
+                warp_m2[warp] = m2;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int w = 1; w < 8; ++w) {
+                    mean += warp_mean[w];
+                    m2 += warp_m2[w];
+                }
+            }
+        }
+        if (lane == 0 && live) {
+            const double spread = m2 - mean * mean * reciprocal_short(static_cast<double>(p.nred));
+            sink.put(o, spread > 0.0 ? spread : (spread == spread ? 0.0 : spread), p.nred);
+        }
+        return;
     }
     if constexpr (G > 1) {
 #pragma unroll
