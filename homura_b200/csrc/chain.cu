@@ -27,6 +27,8 @@ struct Chain {
     // b and c are broadcasts in the expressions this is for (a scale per column, a bias per row): what is in flight
     // per thread is x, 16 bytes a vector
     static constexpr int kUnroll = 2;
+    // with a transposed x (and b, c in the output's orientation) the copy engine and ldmatrix do the transposition
+    static constexpr bool kTransposedFirst = true;
     __device__ __forceinline__ Compute compute(T x, T b, TC c) const {
         using Ct = typename Comp<T>::C;
         const T t1 = down<T>(unary_math<UOP, Ct, kFast>(up(x)));

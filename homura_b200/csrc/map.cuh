@@ -913,6 +913,45 @@ bool launch_transpose16(hmc_context_t ctx, const MapArgs &a, const F &f, hmc_sta
     return true;
 }
 
+// Queues transpose16_three_kernel for the layout in `a` when it qualifies: the first input transposed and of 2-byte
+// elements, the output with unit stride along the last dimension, the other two inputs tensors of any strides.
+template <class F>
+bool launch_transpose16_three(hmc_context_t ctx, const MapArgs &a, const F &f, hmc_status &status) {
+    if (ctx->status == nullptr) return false;
+    const int da = a.ndim - 2, db = a.ndim - 1;
+    if (a.strides[0][db] != 1) return false;
+    const int64_t size_a = a.sizes[da], size_b = a.sizes[db], outer = a.ndim == 3 ? a.sizes[0] : 1;
+    CUtensorMap in_map;
+    if (!t16_encode_map(&in_map, a.base[1], size_a, size_b, outer, a.strides[1][db], a.ndim == 3 ? a.strides[1][0] : 0)) return false;
+    const int64_t tiles_a = ceil_div(size_a, kT16Tile), tiles_b = ceil_div(size_b, kT16Tile);
+    if (tiles_a * tiles_b >= (int64_t{1} << 31) / (outer > 0 ? outer : 1) || size_a >= (int64_t{1} << 31) - kT16Tile ||
+        size_b >= (int64_t{1} << 31) - kT16Tile) {
+        return false;  // the kernel counts tiles, rows and columns in 32 bits
+    }
+    Transpose16Args3 args;
+    args.tiles_a = static_cast<uint32_t>(tiles_a);
+    args.tiles_b = static_cast<uint32_t>(tiles_b);
+    args.tiles = static_cast<uint32_t>(outer * tiles_a * tiles_b);
+    args.size_a = size_a;
+    args.size_b = size_b;
+    args.out = a.base[0];
+    args.out_stride_a = a.strides[0][da];
+    args.out_stride_outer = a.ndim == 3 ? a.strides[0][0] : 0;
+    args.b = Transpose16Operand{a.base[2], a.strides[2][da], a.strides[2][db], a.ndim == 3 ? a.strides[2][0] : 0};
+    args.c = Transpose16Operand{a.base[3], a.strides[3][da], a.strides[3][db], a.ndim == 3 ? a.strides[3][0] : 0};
+    constexpr size_t kShared = static_cast<size_t>(kT16Stages) * kT16TileBytes + 1024;
+    const int64_t resident = static_cast<int64_t>(ctx->sm_count) * kT16BlocksPerSm;
+    const unsigned grid = static_cast<unsigned>(static_cast<int64_t>(args.tiles) < resident ? args.tiles : resident);
+    transpose16_three_kernel<F><<<grid, kT16Threads, kShared, ctx->stream>>>(in_map, args, f, ctx->status);
+    status = launch_status("transposing kernel launch");
+    return true;
+}
+
+// Functors of three inputs that want the kernel above when only their first input is transposed say so with a member
+// kTransposedFirst.
+template <class F, class = void> struct wants_transposed_first : std::false_type {};
+template <class F> struct wants_transposed_first<F, std::void_t<decltype(F::kTransposedFirst)>> : std::bool_constant<F::kTransposedFirst> {};
+
 template <class F>
 hmc_status launch_map(hmc_context_t ctx, const F &f, const hmc_tensor_desc *out, const MapOperand *inputs, int ninputs) {
     MapArgs a;
@@ -945,6 +984,12 @@ hmc_status launch_map(hmc_context_t ctx, const F &f, const hmc_tensor_desc *out,
         if (a.tile_mask == 2u && a.constant_mask == 0 && (a.ndim == 2 || a.ndim == 3)) {
             hmc_status done = HMC_OK;
             if (launch_transpose16<F>(ctx, a, f, done)) return done;
+        }
+    }
+    if constexpr (wants_transposed_first<F>::value && size_or_zero<typename F::A>() == 2) {
+        if (a.tile_mask == 2u && a.constant_mask == 0 && (a.ndim == 2 || a.ndim == 3)) {
+            hmc_status done = HMC_OK;
+            if (launch_transpose16_three<F>(ctx, a, f, done)) return done;
         }
     }
     if (a.tile_mask != 0) {

@@ -222,4 +222,174 @@ __global__ void __launch_bounds__(kT16Threads) transpose16_kernel(const __grid_c
     if (threadIdx.x == 0) t16_stores_done();
 }
 
+// ---- the same for functions of three operands of which the first is the transposed one ----
+// out[.., a, b] = f(x[.., b, a], B[.., a, b], C[.., a, b]) for a 2-byte x that has its unit stride along a; B and C are
+// addressed by their strides in the output's orientation (a bias per row, a scale per column, whole tensors), the
+// output may be of any size (the fused chain's f32 result). The input side is the kernel above; the output side
+// needs no tile: after ldmatrix.trans a lane holds pairs of elements that are neighbours along b, which it combines with
+// its B and C values and stores straight to global memory, eight lanes filling a 32-byte sector of a 4-byte output.
+struct Transpose16Operand {
+    const void *base;
+    int64_t stride_a, stride_b, stride_outer;  // elements
+};
+struct Transpose16Args3 {
+    uint32_t tiles_a, tiles_b, tiles;
+    int64_t size_a, size_b;
+    void *out;
+    int64_t out_stride_a, out_stride_outer;    // elements; the output has unit stride along b
+    Transpose16Operand b, c;
+};
+
+template <class F>
+__global__ void __launch_bounds__(kT16Threads) transpose16_three_kernel(const __grid_constant__ CUtensorMap in_map,
+                                                                         const __grid_constant__ Transpose16Args3 args, const F f,
+                                                                         int *status) {
+    using TX = typename F::A;
+    using TB = typename F::B;
+    using TC = typename F::C;
+    using TO = typename F::Out;
+    static_assert(sizeof(TX) == 2, "a 2-byte first operand");
+    extern __shared__ unsigned char t16_memory[];
+    __shared__ __align__(8) uint64_t full[kT16Stages];
+    __shared__ int gave_up;
+    unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(t16_memory) + 1023) & ~uintptr_t{1023});
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kT16Stages; ++s) t16_barrier_init(&full[s]);
+        gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto coordinates = [&](uint32_t t, int &ta, int &tb, int &outer) {
+        const uint32_t per_outer = args.tiles_a * args.tiles_b;
+        const uint32_t o = t / per_outer, rest = t - o * per_outer;
+        const uint32_t per_strip = kT16Strip * args.tiles_b;
+        const uint32_t strip = rest / per_strip, in_strip = rest - strip * per_strip;
+        const uint32_t left = args.tiles_a - strip * kT16Strip;
+        const uint32_t width = left < kT16Strip ? left : kT16Strip;
+        const uint32_t b = in_strip / width;
+        outer = static_cast<int>(o);
+        tb = static_cast<int>(b);
+        ta = static_cast<int>(strip * kT16Strip + (in_strip - b * width));
+    };
+    auto fetch = [&](uint32_t t, int stage) {
+        int ta, tb, outer;
+        coordinates(t, ta, tb, outer);
+        t16_barrier_expect(&full[stage], kT16TileBytes);
+        t16_fetch(tiles + stage * kT16TileBytes, &in_map, ta * kT16Tile, tb * kT16Tile, outer, &full[stage]);
+    };
+    if (threadIdx.x == 0) {
+        uint32_t t = blockIdx.x;
+        for (int s = 0; s < kT16Stages && t < args.tiles; ++s, t += gridDim.x) fetch(t, s);
+    }
+    const TB *pb = static_cast<const TB *>(args.b.base);
+    const TC *pc = static_cast<const TC *>(args.c.base);
+    TO *po = static_cast<TO *>(args.out);
+    const bool pairs_aligned = (reinterpret_cast<uintptr_t>(po) % (2 * sizeof(TO))) == 0 && args.out_stride_a % 2 == 0 &&
+                               args.out_stride_outer % 2 == 0;
+    int stage = 0;
+    uint32_t parity = 0;
+    for (uint32_t t = blockIdx.x; t < args.tiles; t += gridDim.x) {
+        if (!t16_barrier_wait(&full[stage], parity)) gave_up = 1;
+        __syncthreads();
+        if (gave_up) {
+            if (threadIdx.x == 0) atomicExch(status, 1);
+            break;
+        }
+        int ta, tb, outer;
+        coordinates(t, ta, tb, outer);
+        const unsigned char *in_tile = tiles + stage * kT16TileBytes;
+#pragma unroll
+        for (int piece = 0; piece < 16 / kT16Warps; ++piece) {
+            const int id = piece * kT16Warps + warp;
+            const int ia = id >> 1, jb = id & 1;
+            const int row_in = jb * 32 + lane;
+            const uint32_t from = t16_shared(in_tile + row_in * 128 + ((ia ^ (row_in & 7)) << 4));
+            uint32_t d[4];
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                         : "r"(from)
+                         : "memory");
+            // this lane's output row, and the first of its two columns in each of the four 8 x 8 blocks; positions
+            // beyond the edges are clamped for the loads (which then need no branches and all go out together)
+            // and skipped by the stores
+            // (sizes are below 2^31 here: the tiles are counted in 32 bits)
+            const int ra = ta * kT16Tile + ia * 8 + (lane >> 2);
+            const int cb = tb * kT16Tile + jb * 32 + 2 * (lane & 3);
+            const int size_a = static_cast<int>(args.size_a), size_b = static_cast<int>(args.size_b);
+            const int ra_safe = ra < size_a ? ra : size_a - 1;
+            const TB *b_row = pb + outer * args.b.stride_outer + ra_safe * args.b.stride_a;
+            const TC *c_row = pc + outer * args.c.stride_outer + ra_safe * args.c.stride_a;
+            TB bv[4][2];
+            TC cv[4][2];
+            // an operand that does not change along b (a value per output row) is read once
+            if (args.b.stride_b == 0) {
+                const TB v = b_row[0];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) bv[m][0] = bv[m][1] = v;
+            } else {
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int col = cb + 8 * m + e;
+                        bv[m][e] = b_row[static_cast<int64_t>(col < size_b ? col : size_b - 1) * args.b.stride_b];
+                    }
+                }
+            }
+            if (args.c.stride_b == 0) {
+                const TC v = c_row[0];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) cv[m][0] = cv[m][1] = v;
+            } else {
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int col = cb + 8 * m + e;
+                        cv[m][e] = c_row[static_cast<int64_t>(col < size_b ? col : size_b - 1) * args.c.stride_b];
+                    }
+                }
+            }
+            TO *out_row = po + outer * args.out_stride_outer + ra_safe * args.out_stride_a;
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const int col = cb + 8 * m;
+                const uint16_t lo = static_cast<uint16_t>(d[m] & 0xFFFFu), hi = static_cast<uint16_t>(d[m] >> 16);
+                TX x0, x1;
+                memcpy(&x0, &lo, 2);
+                memcpy(&x1, &hi, 2);
+                TO y0, y1;
+                if constexpr (std::is_same_v<TO, F16> || std::is_same_v<TO, BF16>) {
+                    down2(y0, y1, f.compute(x0, bv[m][0], cv[m][0]), f.compute(x1, bv[m][1], cv[m][1]));
+                } else {
+                    y0 = down<TO>(f.compute(x0, bv[m][0], cv[m][0]));
+                    y1 = down<TO>(f.compute(x1, bv[m][1], cv[m][1]));
+                }
+                if (ra < size_a && col < size_b) {
+                    const bool second = col + 1 < size_b;
+                    if (second && pairs_aligned) {
+                        Pack<TO, 2> pair;
+                        pair.v[0] = y0;
+                        pair.v[1] = y1;
+                        *reinterpret_cast<Pack<TO, 2> *>(out_row + col) = pair;
+                    } else {
+                        out_row[col] = y0;
+                        if (second) out_row[col + 1] = y1;
+                    }
+                }
+            }
+        }
+        __syncthreads();  // everybody has read the input tile
+        if (threadIdx.x == 0) {
+            const uint64_t next = t + static_cast<uint64_t>(kT16Stages) * gridDim.x;
+            if (next < args.tiles) fetch(static_cast<uint32_t>(next), stage);
+        }
+        if (++stage == kT16Stages) {
+            stage = 0;
+            parity ^= 1;
+        }
+    }
+}
+
 }  // namespace hmc
