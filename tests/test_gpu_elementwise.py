@@ -327,9 +327,15 @@ def test_unsupported_combinations_are_refused(cuda):
 def test_unary_binary_binary_in_one_kernel_has_the_three_kernels_bits(oracle, cuda, dtypes):
     """(unary(x) op b) op c fused: the bits of hmc_unary, hmc_binary and the promoting binary run one after the other
     on the GPU, and of the CPU checker's three steps wherever the unary step has the CPU's bits; contiguous
-    operands, a row and a column broadcast, and a transposed x."""
+    operands, a row and a column broadcast, and a transposed x: with rows whose byte stride is no multiple of 16 (the
+    general tiled kernel), with ragged 64 x 64 tiles (the copy engine's kernel, results stored in pairs), and with an
+    odd number of columns (stored one by one)."""
     t, tc = dtypes
-    rows, cols = 300, 520
+    for rows, cols in ((300, 520), (328, 520), (328, 521)):
+        _chain_case(oracle, cuda, t, tc, rows, cols)
+
+
+def _chain_case(oracle, cuda, t, tc, rows, cols):
     x_raw = f64_to_storage(uniform(rows * cols, 6.0, 71), t)
     b_raw = f64_to_storage(uniform(cols, 2.0, 72), t)
     c_raw = f64_to_storage(uniform(rows, 3.0, 73), tc)
