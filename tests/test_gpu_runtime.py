@@ -78,6 +78,8 @@ def test_memset_and_host_copies(cuda):
 
 
 def test_allocator_on_the_device_caches_and_reports(cuda):
+    if cuda.debug:
+        pytest.skip("guard bands round every block up: the byte counts below are those of a plain run")
     a = cuda.allocator
     a.empty_cache()
     before = a.memory_stats()
