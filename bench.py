@@ -195,6 +195,8 @@ class FusedWorkload:
         n = rows * cols
         self.op_bytes = {"silu_mul_add": 6 * n + 2 * cols + 4 * rows, "silu_mul_add_t": 6 * n + 2 * rows + 4 * cols}
         self.launches_per_step = 2
+        # dram read + write bytes per launch from an ncu capture of this workload at this size
+        self.ncu_traffic = {"silu_mul_add": 345.6e6, "silu_mul_add_t": 350.0e6} if (rows, cols) == (ROWS, COLS) else {}
 
     def ops(self):
         from homura_b200 import ffi
@@ -244,6 +246,10 @@ class C3Workload:
         self.op_bytes = {k: b4 for k in ["sum_rows", "mean_rows", "var_rows", "sum_cols", "mean_cols", "var_cols", "max_rows",
                                          "sum_full", "isum_rows", "isum_cols", "imax_rows", "isum_full"]}
         self.launches_per_step = 12
+        # dram read + write bytes per launch from an ncu capture of this workload (every input is read once)
+        self.ncu_traffic = {"sum_rows": 273.0e6, "mean_rows": 270.0e6, "var_rows": 268.9e6, "sum_cols": 269.5e6, "mean_cols": 269.7e6,
+                            "var_cols": 271.6e6, "max_rows": 270.7e6, "sum_full": 272.2e6, "isum_rows": 268.7e6, "isum_cols": 269.6e6,
+                            "imax_rows": 269.0e6, "isum_full": 268.6e6}
 
     def ops(self):
         from homura_b200 import ffi
@@ -321,6 +327,9 @@ class C4Workload:
         self.op_bytes = {"masked_fill": 8 * m + n * n, "softmax": 8 * m, "log_softmax": 8 * m, "to_f32": 6 * k, "pow2": 8 * k,
                          "mean_rows": 4 * k + 4 * k_rows}
         self.launches_per_step = 6
+        # dram read + write bytes per launch: an ncu capture of a 16-matrix slice (488.4 and 485.2 MB per 16 matrices of
+        # 2048 x 2048), scaled to this batch: rows are independent, so traffic grows in proportion
+        self.ncu_traffic = {"softmax": 488.4e6 * batch / 16, "log_softmax": 485.2e6 * batch / 16}
 
     def ops(self):
         from homura_b200 import ffi
@@ -394,6 +403,9 @@ class C5Workload:
         self.op_bytes = {"mul": 12 * n, "add": 12 * n, "sum": 4 * n, "max": 4 * n,
                          "adamw_291_tensors": 28 * self.params, "grad_norm": 8 * len(self.tensors)}
         self.launches_per_step = 4 + 2 + 2 + (3 if reducer is not None else 0) * 2
+        # dram read + write bytes per launch of the AdamW kernel: an ncu capture at 1/64 of the model's rows (3.457 GB for
+        # 125.5 M parameters: 27.5 bytes a parameter), scaled by the parameters of this launch
+        self.ncu_traffic = {"adamw_291_tensors": 27.55 * self.params}
 
     def ops(self):
         from homura_b200 import ffi
@@ -637,7 +649,7 @@ def workload_record(runner: Runner, w, steps: int, warmup: int) -> dict:
     regions = runner.timed_steps(w, steps, warmup, 3)
     step_bytes = sum(w.op_bytes.values())
     flushed_ms = sum(per_op.values())
-    r = roofline_of(w, per_op)
+    r = roofline_of(w, per_op, getattr(w, "ncu_traffic", None))
     back_ms = float(np.median(regions)) / steps
     # what the flush's read-back is worth: the first op again after a flush that only writes
     first = w.ops()[:1]
