@@ -171,13 +171,34 @@ def merge_dims(shape: Sequence[int], strides: Sequence[Sequence[int]]):
     return dims
 
 
-def descs_with_dims(kernel: str, operands: Sequence[TensorData], offsets: Sequence[int], dims) -> list[hmc_tensor_desc]:
-    """src/backend/rocm/copy.rs:86-115."""
+# Debug runs (HOMURA_CUDA_DEBUG=1) check every description against its storage before the call: the last element a
+# kernel can reach from it must lie inside the allocation. A description that reaches beyond is refused on the host
+# with both numbers, instead of a kernel reading or writing beside its buffer.
+CHECK_REACH = os.environ.get("HOMURA_CUDA_DEBUG", "") not in ("", "0")
+
+
+def check_reach(kernel: str, t: TensorData, offset: int, dims, k: int, extra: int = 0) -> None:
+    """`dims` as merge_dims gives them ([(size, strides per operand)]); `extra`: elements another description of the
+    same operand adds to the farthest one of this (a reduction's kept and reduced parts)."""
+    if any(size == 0 for size, _ in dims):
+        return
+    reach = offset + extra + sum((size - 1) * st[k] for size, st in dims)
+    have = t.storage.nbytes // SIZE[t.dtype]
+    if reach >= have or offset < 0:
+        raise BackendError(ffi.HMC_INVALID, f"debug: {kernel}: an operand of {DTYPE_NAMES[t.dtype]} reaches element {reach} of a "
+                                            f"storage of {have} elements")
+
+
+def descs_with_dims(kernel: str, operands: Sequence[TensorData], offsets: Sequence[int], dims, check: bool = True) -> list[hmc_tensor_desc]:
+    """src/backend/rocm/copy.rs:86-115. `check=False` for descriptions whose sizes are not the operand's own (the indexing
+    kernels describe their source with the output's sizes and find its rows through the index)."""
     if len(dims) > MAX_DIMS:
         raise BackendError(ffi.HMC_INVALID, f"{kernel} on CUDA supports at most {MAX_DIMS} dimensions that can't be "
                                             f"merged, got {len(dims)}")
     out = []
     for k, t in enumerate(operands):
+        if CHECK_REACH and check:
+            check_reach(kernel, t, offsets[k], dims, k)
         d = hmc_tensor_desc()
         d.data = t.storage.address
         d.offset = offsets[k]
@@ -227,8 +248,11 @@ def describe(kernel: str, src: TensorData, mask: Sequence[bool]) -> Optional[Red
     if red_dims is None:
         red_dims = [(0, [0])]  # nothing to fold
     src_dims = [(n, [st[1]]) for n, st in dims]
-    (kept,) = descs_with_dims(kernel, [src], [src.offset], src_dims)
-    (red,) = descs_with_dims(kernel, [src], [0], red_dims)
+    if CHECK_REACH and src.numel > 0:
+        check_reach(kernel, src, src.offset, src_dims, 0, extra=sum((n - 1) * st[0] for n, st in red_dims))
+    # (each half alone says nothing about the reach: the check above covers both together)
+    (kept,) = descs_with_dims(kernel, [src], [src.offset], src_dims, check=False)
+    (red,) = descs_with_dims(kernel, [src], [0], red_dims, check=False)
     return Reduction(dims, kept, red)
 
 
@@ -871,7 +895,7 @@ def around(kernel: str, operands: Sequence[TensorData], shape: Sequence[int], di
     at = len(dims)
     dims.append((shape[dim], [st[dim] for st in strides]))
     dims.extend(part(dim + 1, len(shape)))
-    return descs_with_dims(kernel, operands, [t.offset for t in operands], dims), at
+    return descs_with_dims(kernel, operands, [t.offset for t in operands], dims, check=False), at
 
 
 def index_select_descs(kernel: str, out: TensorData, src: TensorData, dim: int, index: TensorData):

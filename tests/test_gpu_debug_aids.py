@@ -46,9 +46,18 @@ def test_poison_and_guard_bands():
         be.copy(t, x.t())
         be.synchronize()
         be.check_guards()
-        # a destination described four elements longer than its storage: the write lands in the guard band
+        # a destination described four elements longer than its storage is refused before anything is queued ...
+        from homura_b200 import host
         small = be.empty((12,), F32)
         lying = TensorData(small.storage, F32, (16,), (1,))
+        try:
+            be.fill(lying, 1.0)
+            print("not refused")
+        except BackendError as e:
+            assert "reaches element 15 of a storage of 12" in str(e), str(e)
+        # ... and, with that check switched off (a kernel that went beyond its description), the write lands in the
+        # guard band
+        host.CHECK_REACH = False
         be.fill(lying, 1.0)
         be.synchronize()
         try:
@@ -60,7 +69,7 @@ def test_poison_and_guard_bands():
         be._guarded.clear()
         be.close()
     """, HOMURA_CUDA_DEBUG="1")
-    assert "caught" in out
+    assert "caught" in out and "not refused" not in out
 
 
 def test_timing_log(tmp_path):

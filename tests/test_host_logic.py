@@ -83,3 +83,27 @@ def test_adamw_scalars():
     assert sc.decay == float(np.float32(1.0 - 1e-4 * 0.01))
     assert sc.eps == float(np.float32(1e-8))
     assert adamw_scalars(F16, 1e-3, 0.9, 0.999, 1e-8, 0.0, 2.0).eps == 0.0
+
+
+def test_debug_runs_refuse_descriptions_that_reach_beyond_their_storage(monkeypatch):
+    """HOMURA_CUDA_DEBUG=1: the farthest element a description can reach is checked against the storage on the host,
+    for same-shaped operands and for the two halves of a reduction."""
+    from homura_b200 import host
+    from homura_b200.host import F32, BackendError, Storage, TensorData
+
+    monkeypatch.setattr(host, "CHECK_REACH", True)
+    st = Storage(16 * 4, ptr=4096, device=0)
+    good = TensorData(st, F32, (4, 4), (4, 1))
+    assert len(host.descs("fits", [good, good])) == 2
+    assert host.describe("fits", good, [False, True]) is not None
+    assert host.descs("window", [TensorData(st, F32, (2, 2), (4, 1), 10)]) is not None   # reaches element 15
+    with pytest.raises(BackendError, match="reaches element 16 of a storage of 16"):
+        host.descs("wide", [TensorData(st, F32, (4, 5), (4, 1))])
+    with pytest.raises(BackendError, match="reaches element 18"):
+        host.describe("strided rows", TensorData(st, F32, (4, 4), (4, 2)), [False, True])
+    with pytest.raises(BackendError, match="reaches element 16"):
+        host.descs("offset", [TensorData(st, F32, (2, 2), (4, 1), 11)])
+    # empty operands reach nothing
+    assert host.descs("empty", [TensorData(st, F32, (0, 9), (9, 1))]) is None
+    monkeypatch.setattr(host, "CHECK_REACH", False)
+    assert host.descs("unchecked", [TensorData(st, F32, (4, 5), (4, 1))]) is not None
