@@ -64,6 +64,14 @@ def test_elementwise_broadcast_step_at_8192x8192(oracle, cuda):
     assert_bitwise(ytg.raw(), yto.raw(), F32, "silu(x.t()) * scale + bias")
     assert_bitwise(gx.to(F32).raw(), ox.to(F32).raw(), F32, "cast bf16 -> f32")
     assert_bitwise(gx.view(tr).to(F32).raw(), ox.view(tr).to(F32).raw(), F32, "cast of x.t()")
+    # the whole expression in one kernel, contiguous and on x.t(): the bits of the three GPU kernels run in turn
+    three, three_t = sg.mul(gsc).add(gb), stg.mul(scale_t(gsc)).add(bias_t(gb))
+    fused = cuda.empty((n, n), F32)
+    codes = (ffi.HMC_UNARY_SILU, ffi.HMC_BINARY_MUL, ffi.HMC_BINARY_ADD)
+    cuda.unary_binary_binary(*codes, fused, gx.data, gsc.data, gb.data)
+    assert equal_bits(cuda, fused, three.data), "the fused expression differs from its three kernels"
+    cuda.unary_binary_binary(*codes, fused, gx.view(tr).data, scale_t(gsc).data, bias_t(gb).data)
+    assert equal_bits(cuda, fused, three_t.data), "the fused expression on x.t() differs from its three kernels"
     cuda.allocator.empty_cache()
 
 
