@@ -13,16 +13,28 @@
 namespace hmc {
 namespace {
 
+// x op y for op in {ADD, SUB, MUL} chosen at run time: a sum or difference is x + sign * y as one fused operation
+// (the product with +-1 is exact, so the single rounding is that of x +- y), and one select picks it or the product:
+// three instructions where computing all three results and selecting twice takes five.
 template <class Cc>
-__device__ __forceinline__ Cc chain_arith(int op, Cc x, Cc y) {
-    return op == HMC_BINARY_ADD ? x + y : (op == HMC_BINARY_SUB ? x - y : x * y);
+__device__ __forceinline__ Cc chain_arith(bool is_mul, Cc sign, Cc x, Cc y) {
+    Cc sum;
+    if constexpr (std::is_same_v<Cc, float>) sum = __fmaf_rn(y, sign, x);
+    else sum = __fma_rn(y, sign, x);
+    return is_mul ? x * y : sum;
 }
 
 template <class T, class TC, class P, int UOP>
 struct Chain {
     using Out = P; using A = T; using B = T; using C = TC;
     using Compute = typename Comp<P>::C;
-    int first, second;
+    using Ct = typename Comp<T>::C;
+    bool first_is_mul, second_is_mul;
+    Ct first_sign;
+    Compute second_sign;
+    Chain(int first, int second)
+        : first_is_mul(first == HMC_BINARY_MUL), second_is_mul(second == HMC_BINARY_MUL),
+          first_sign(first == HMC_BINARY_SUB ? Ct(-1) : Ct(1)), second_sign(second == HMC_BINARY_SUB ? Compute(-1) : Compute(1)) {}
     static constexpr bool kFast = std::is_same_v<T, F16> || std::is_same_v<T, BF16>;
     // b and c are broadcasts in the expressions this is for (a scale per column, a bias per row): what is in flight
     // per thread is x, 16 bytes a vector
@@ -30,10 +42,9 @@ struct Chain {
     // with a transposed x (and b, c in the output's orientation) the copy engine and ldmatrix do the transposition
     static constexpr bool kTransposedFirst = true;
     __device__ __forceinline__ Compute compute(T x, T b, TC c) const {
-        using Ct = typename Comp<T>::C;
         const T t1 = down<T>(unary_math<UOP, Ct, kFast>(up(x)));
-        const T t2 = down<T>(chain_arith<Ct>(first, up(t1), up(b)));
-        return chain_arith<Compute>(second, up(convert<P, T>(t2)), up(convert<P, TC>(c)));
+        const T t2 = down<T>(chain_arith<Ct>(first_is_mul, first_sign, up(t1), up(b)));
+        return chain_arith<Compute>(second_is_mul, second_sign, up(convert<P, T>(t2)), up(convert<P, TC>(c)));
     }
 };
 
@@ -41,7 +52,7 @@ template <class T, class TC, class P>
 hmc_status chain_unary(hmc_context_t ctx, int32_t unary_op, int first, int second, const hmc_tensor_desc *out, const MapOperand *in) {
     switch (unary_op) {
 #define HMC_CASE(OP) \
-    case OP: return launch_map(ctx, Chain<T, TC, P, OP>{first, second}, out, in, 3);
+    case OP: return launch_map(ctx, Chain<T, TC, P, OP>(first, second), out, in, 3);
         HMC_CASE(HMC_UNARY_RELU)
         HMC_CASE(HMC_UNARY_EXP)
         HMC_CASE(HMC_UNARY_TANH)
