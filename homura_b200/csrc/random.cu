@@ -22,6 +22,7 @@ namespace hmc {
 namespace {
 
 constexpr int kSampleThreads = 256;
+constexpr int kBlocksPerThread = 4;  // Philox blocks a thread of the uniform and the unrejected integer sampler takes
 
 struct Words4 {
     uint32_t w[4];
@@ -77,6 +78,8 @@ __global__ void __launch_bounds__(kSampleThreads) uniform_kernel(T *out, int64_t
     const double width = to - from;
     const T first = from_f64<T>(from);
     const bool aligned = (reinterpret_cast<uintptr_t>(out) & (sizeof(T) * PER - 1)) == 0;
+    // (a thread takes kBlocksPerThread blocks a grid stride apart: their rounds interleave)
+#pragma unroll 4
     for (int64_t b = static_cast<int64_t>(blockIdx.x) * kSampleThreads + threadIdx.x; b < blocks;
          b += static_cast<int64_t>(gridDim.x) * kSampleThreads) {
         const Words4 r = philox_block(offset + static_cast<uint64_t>(b), seed);
@@ -178,6 +181,7 @@ __device__ __forceinline__ uint64_t word_mod(uint64_t w, const Modulus &m) {
 __global__ void __launch_bounds__(kSampleThreads) int_all_kernel(int64_t *out, int64_t n, uint64_t seed, uint64_t offset,
                                                                   uint64_t blocks, int64_t low, const Modulus range) {
     const bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+#pragma unroll 4
     for (uint64_t b = static_cast<uint64_t>(blockIdx.x) * kSampleThreads + threadIdx.x; b < blocks;
          b += static_cast<uint64_t>(gridDim.x) * kSampleThreads) {
         uint64_t w0, w1;
@@ -339,9 +343,9 @@ HMC_API hmc_status hmc_random_uniform(hmc_context_t ctx, const hmc_tensor_desc *
             constexpr int per = std::is_same_v<T, double> ? 2 : 4;
             T *p = static_cast<T *>(out->data) + out->offset;
             if (per == 4 && from == 0.0 && to == 1.0 && !std::signbit(from)) {
-                uniform_kernel<T, true><<<sample_grid(ceil_div(n, per)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, from, to);
+                uniform_kernel<T, true><<<sample_grid(ceil_div(n, per * kBlocksPerThread)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, from, to);
             } else {
-                uniform_kernel<T, false><<<sample_grid(ceil_div(n, per)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, from, to);
+                uniform_kernel<T, false><<<sample_grid(ceil_div(n, per * kBlocksPerThread)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, from, to);
             }
             return launch_status("uniform sampling kernel launch");
         });
@@ -380,7 +384,7 @@ HMC_API hmc_status hmc_random_int(hmc_context_t ctx, const hmc_tensor_desc *out,
         int64_t *p = static_cast<int64_t *>(out->data) + out->offset;
         if (threshold == 0) {
             if (n == 0 || blocks == 0) return HMC_OK;
-            int_all_kernel<<<sample_grid(static_cast<int64_t>(blocks)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, blocks, low,
+            int_all_kernel<<<sample_grid(ceil_div(static_cast<int64_t>(blocks), kBlocksPerThread)), kSampleThreads, 0, ctx->stream>>>(p, n, seed, offset, blocks, low,
                                                                                                        modulus_of(range));
             return launch_status("integer sampling kernel launch");
         }
