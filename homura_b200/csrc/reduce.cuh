@@ -162,9 +162,10 @@ __device__ __forceinline__ Acc load_partial(const Acc *p) {
 // for another: a block that is not the last simply leaves.)
 __device__ __forceinline__ bool drew_last_ticket(unsigned *tickets) {
     __shared__ bool last;
+    __threadfence();  // this thread's partials are visible to the device ...
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence();  // the block's partials (ordered before this by the barrier) are visible to the device before the ticket is
+        __threadfence();  // ... and so are the whole block's, before its ticket is drawn
         const unsigned mine = atomicAdd(&tickets[blockIdx.x], 1u);
         last = mine + 1 == gridDim.y;
         if (last) tickets[blockIdx.x] = 0;  // everybody has drawn: ready for the next kernel
