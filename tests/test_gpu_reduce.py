@@ -182,6 +182,12 @@ def test_reductions_are_reproducible(cuda):
         first = t._red("sum", dims).raw()
         for _ in range(3):
             assert (t._red("sum", dims).raw().view(np.uint32) == first.view(np.uint32)).all()
+    # reductions cut into chunks, whose partials are folded by whichever block finishes last: forty runs, one result
+    tall = T(cuda, cuda.upload(f64_to_storage(normal(1 << 23, 112), F32), F32, (1 << 13, 1 << 10)))
+    for f in (lambda x: x._red("sum", [0]), lambda x: x._red("sum", []), lambda x: x.var_dim([0], 1)):
+        first = f(tall).raw().view(np.uint32)
+        for _ in range(40):
+            assert (f(tall).raw().view(np.uint32) == first).all()
 
 
 def test_wrong_results_are_rejected(oracle, cuda):
